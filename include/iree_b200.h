@@ -1,0 +1,261 @@
+/* C ABI of libiree_b200.so: the B200 (sm_100a) drop-in for IREE's contraction dispatches.
+ *
+ * Two layers, both plain C (pointers and sizes only):
+ *
+ *  1. A mirror of the slice of the HAL C API that a compiled IREE program drives when it
+ *     runs a dispatch that carries an external CUDA object: executable creation from an
+ *     `ExecutableDef` flatbuffer, push constants, descriptor sets, dispatch (cuLaunchKernel
+ *     with "bindings first, then one 32-bit parameter per constant"), transfers, and the
+ *     collective channel. Function names follow the reference's with the driver infix
+ *     `b200`; every declaration cites the reference interface it stands in for. Paths are
+ *     relative to the reference checkout.
+ *
+ *  2. Operator-level entry points, one per contraction dispatch family, that perform what the
+ *     compiler plugin's rewritten host program performs for that dispatch (pick the export,
+ *     fill the push constants, bind the buffers, dispatch). These are what a foreign-function
+ *     binding would call.
+ *
+ * Errors: every function returns an `iree_b200_status_t` whose values are the reference's
+ * `iree_status_code_t` (runtime/src/iree/base/status.h:79-125); 0 is OK. The message of the
+ * most recent failure on the calling thread is available from iree_b200_last_error().
+ * There is no CPU fallback anywhere: without a CUDA device every compute call fails with
+ * IREE_B200_STATUS_UNAVAILABLE.
+ */
+#ifndef IREE_B200_H_
+#define IREE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t iree_b200_status_t;
+enum {
+  IREE_B200_STATUS_OK = 0,
+  IREE_B200_STATUS_UNKNOWN = 2,
+  IREE_B200_STATUS_INVALID_ARGUMENT = 3,
+  IREE_B200_STATUS_DEADLINE_EXCEEDED = 4,
+  IREE_B200_STATUS_NOT_FOUND = 5,
+  IREE_B200_STATUS_RESOURCE_EXHAUSTED = 8,
+  IREE_B200_STATUS_FAILED_PRECONDITION = 9,
+  IREE_B200_STATUS_OUT_OF_RANGE = 11,
+  IREE_B200_STATUS_UNIMPLEMENTED = 12,
+  IREE_B200_STATUS_INTERNAL = 13,
+  IREE_B200_STATUS_UNAVAILABLE = 14,
+};
+
+/* Message of the last non-OK status returned on this thread ("" if none). */
+const char* iree_b200_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Limits of the CUDA HAL driver's pipeline layout
+ * (runtime/src/iree/hal/drivers/cuda/pipeline_layout.h:19-28).
+ * ---------------------------------------------------------------------------------------- */
+#define IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT 4
+#define IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT 16
+#define IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT 64
+
+typedef struct iree_hal_b200_device_t iree_hal_b200_device_t;
+typedef struct iree_hal_b200_executable_t iree_hal_b200_executable_t;
+typedef struct iree_hal_b200_command_buffer_t iree_hal_b200_command_buffer_t;
+typedef struct iree_hal_b200_channel_t iree_hal_b200_channel_t;
+
+/* ---- device -------------------------------------------------------------------------------
+ * Stands in for iree_hal_cuda_driver_create + device creation
+ * (runtime/src/iree/hal/drivers/cuda/api.h:59-125, cuda_device.c). Loads libcuda.so at run
+ * time like cuda_dynamic_symbols.c, retains the device's primary context (so pointers from
+ * other libraries in the process are usable) and creates the dispatch stream. */
+iree_b200_status_t iree_hal_b200_device_create(int32_t ordinal, iree_hal_b200_device_t** out_device);
+void iree_hal_b200_device_release(iree_hal_b200_device_t* device);
+/* Name, SM count, compute capability (major*10+minor) and opt-in shared memory per block. */
+iree_b200_status_t iree_hal_b200_device_query(iree_hal_b200_device_t* device, char* name, size_t name_capacity,
+                                              int32_t* out_sm_count, int32_t* out_compute_capability,
+                                              int32_t* out_max_shared_memory);
+/* Blocks until everything queued on the dispatch stream has finished
+ * (the fence wait of runtime/src/iree/tooling/run_module.c:251-297). */
+iree_b200_status_t iree_hal_b200_device_synchronize(iree_hal_b200_device_t* device);
+/* The dispatch CUstream, for callers that interleave their own work (graph capture, NCCL). */
+void* iree_hal_b200_device_stream(iree_hal_b200_device_t* device);
+
+/* ---- buffers ------------------------------------------------------------------------------
+ * iree_hal_allocator_allocate_buffer / iree_hal_device_transfer_h2d / _d2h
+ * (runtime/src/iree/hal/drivers/cuda/cuda_allocator.c; hal/device.h). Buffers are raw device
+ * pointers, which is what the driver resolves bindings to before a launch
+ * (stream_command_buffer.c:488-491). Transfers are queued on the dispatch stream. */
+iree_b200_status_t iree_hal_b200_buffer_allocate(iree_hal_b200_device_t* device, size_t byte_length,
+                                                 void** out_device_ptr);
+iree_b200_status_t iree_hal_b200_buffer_free(iree_hal_b200_device_t* device, void* device_ptr);
+iree_b200_status_t iree_hal_b200_host_allocate(iree_hal_b200_device_t* device, size_t byte_length,
+                                               void** out_pinned_host_ptr);
+iree_b200_status_t iree_hal_b200_host_free(iree_hal_b200_device_t* device, void* pinned_host_ptr);
+iree_b200_status_t iree_hal_b200_transfer_h2d(iree_hal_b200_device_t* device, const void* source,
+                                              void* target_device_ptr, size_t byte_length);
+iree_b200_status_t iree_hal_b200_transfer_d2h(iree_hal_b200_device_t* device, const void* source_device_ptr,
+                                              void* target, size_t byte_length);
+iree_b200_status_t iree_hal_b200_fill_buffer(iree_hal_b200_device_t* device, void* device_ptr, size_t byte_length,
+                                             uint8_t pattern);
+
+/* ---- executable container -------------------------------------------------------------------
+ * Writer for the `ExecutableDef` flatbuffer (file identifier "CUDA",
+ * runtime/src/iree/schemas/cuda_executable_def.fbs:10-50), i.e. what
+ * CUDATargetBackend::serializeExecutable emits for an external object
+ * (compiler/plugins/target/CUDA/CUDATarget.cpp:523-550,665-699): entry names taken verbatim,
+ * one block size and one dynamic shared-memory size per entry, the cubin bytes as `ptx_image`.
+ * Call with out_data == NULL to query the size. */
+iree_b200_status_t iree_b200_executable_def_build(int32_t entry_count, const char* const* entry_names,
+                                                  const uint32_t* block_sizes_xyz,
+                                                  const uint32_t* shared_memory_sizes, const void* image,
+                                                  size_t image_size, void* out_data, size_t out_capacity,
+                                                  size_t* out_size);
+
+/* iree_hal_executable_cache_prepare_executable for format "PTXE"
+ * (runtime/src/iree/hal/drivers/cuda/nop_executable_cache.c:76-93,
+ * native_executable.c:55-272): verifies the flatbuffer (non-empty entry names, as many block
+ * sizes as entries, non-empty image), loads the image with cuModuleLoadDataEx, resolves every
+ * entry and raises its dynamic shared-memory limit, rejecting sizes above the device maximum. */
+iree_b200_status_t iree_hal_b200_executable_create(iree_hal_b200_device_t* device, const char* executable_format,
+                                                   const void* executable_data, size_t executable_data_size,
+                                                   iree_hal_b200_executable_t** out_executable);
+void iree_hal_b200_executable_release(iree_hal_b200_executable_t* executable);
+int32_t iree_hal_b200_executable_entry_count(const iree_hal_b200_executable_t* executable);
+/* Ordinal of the named entry point, or -1. */
+int32_t iree_hal_b200_executable_lookup(const iree_hal_b200_executable_t* executable, const char* entry_name);
+
+/* ---- command buffer (stream mode) --------------------------------------------------------------
+ * iree_hal_command_buffer_{create,push_constants,push_descriptor_set,dispatch,
+ * execution_barrier,collective} as implemented by the CUDA stream command buffer
+ * (runtime/src/iree/hal/command_buffer.h:658-710;
+ * runtime/src/iree/hal/drivers/cuda/stream_command_buffer.c:427-610). Commands execute on the
+ * device's dispatch stream in recording order. A command buffer is recorded by one thread
+ * at a time. */
+typedef struct {
+  uint32_t binding;   /* slot within the set */
+  void* device_ptr;   /* already offset, as the driver passes it */
+} iree_hal_b200_descriptor_set_binding_t;
+
+iree_b200_status_t iree_hal_b200_command_buffer_create(iree_hal_b200_device_t* device,
+                                                       iree_hal_b200_command_buffer_t** out_command_buffer);
+void iree_hal_b200_command_buffer_release(iree_hal_b200_command_buffer_t* command_buffer);
+/* offset and values_length are in bytes and must be multiples of 4. */
+iree_b200_status_t iree_hal_b200_command_buffer_push_constants(iree_hal_b200_command_buffer_t* command_buffer,
+                                                               size_t offset, const void* values,
+                                                               size_t values_length);
+iree_b200_status_t iree_hal_b200_command_buffer_push_descriptor_set(
+    iree_hal_b200_command_buffer_t* command_buffer, uint32_t set, size_t binding_count,
+    const iree_hal_b200_descriptor_set_binding_t* bindings);
+/* Launches entry_point with kernel parameters = the bound pointers of set 0 (slots
+ * 0..binding_count-1), then constant_count 32-bit constants, each a separate parameter. */
+iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_buffer_t* command_buffer,
+                                                         iree_hal_b200_executable_t* executable, int32_t entry_point,
+                                                         uint32_t binding_count, uint32_t constant_count,
+                                                         uint32_t workgroup_x, uint32_t workgroup_y,
+                                                         uint32_t workgroup_z);
+/* Number of kernel launches this command buffer has issued (for launch accounting). */
+uint64_t iree_hal_b200_command_buffer_launch_count(const iree_hal_b200_command_buffer_t* command_buffer);
+
+/* ---- collective channel -------------------------------------------------------------------------
+ * iree_hal_channel_create with explicit {id, rank, count}
+ * (runtime/src/iree/hal/channel.h:40-108; cuda_device.c:439-530; nccl_channel.c:94-160) over
+ * NCCL loaded at run time (nccl_dynamic_symbols.c). One process drives one device per rank. */
+#define IREE_HAL_B200_CHANNEL_ID_SIZE 128
+iree_b200_status_t iree_hal_b200_channel_create_id(void* out_id, size_t id_capacity); /* ncclGetUniqueId */
+iree_b200_status_t iree_hal_b200_channel_create(iree_hal_b200_device_t* device, const void* id, size_t id_size,
+                                                int32_t rank, int32_t count,
+                                                iree_hal_b200_channel_t** out_channel);
+void iree_hal_b200_channel_release(iree_hal_b200_channel_t* channel);
+int32_t iree_hal_b200_channel_rank(const iree_hal_b200_channel_t* channel);
+int32_t iree_hal_b200_channel_count(const iree_hal_b200_channel_t* channel);
+
+enum { /* element types the contraction path gathers (hal/command_buffer.h collective element types) */
+  IREE_HAL_B200_ELEMENT_TYPE_I8 = 0,
+  IREE_HAL_B200_ELEMENT_TYPE_F16 = 1,
+  IREE_HAL_B200_ELEMENT_TYPE_I32 = 2,
+  IREE_HAL_B200_ELEMENT_TYPE_F32 = 3,
+  IREE_HAL_B200_ELEMENT_TYPE_BF16 = 4,
+};
+/* IREE_HAL_COLLECTIVE_KIND_ALL_GATHER through iree_hal_command_buffer_collective
+ * (hal/command_buffer.h:658-663; nccl_channel.c:342-359): every rank contributes element_count
+ * elements; recv holds count * element_count, ordered by rank. */
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command_buffer_t* command_buffer,
+                                                           iree_hal_b200_channel_t* channel, int32_t element_type,
+                                                           const void* send_device_ptr, void* recv_device_ptr,
+                                                           size_t element_count);
+
+/* ------------------------------------------------------------------------------------------
+ * Operator level: the contraction dispatches.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct iree_b200_context_t iree_b200_context_t;
+
+/* Creates the device, loads the contraction executable (an ExecutableDef wrapped around the
+ * sm_100a cubin found at cubin_path) and a command buffer. */
+iree_b200_status_t iree_b200_context_create(int32_t device_ordinal, const char* cubin_path,
+                                            iree_b200_context_t** out_context);
+void iree_b200_context_release(iree_b200_context_t* context);
+iree_hal_b200_device_t* iree_b200_context_device(iree_b200_context_t* context);
+iree_hal_b200_executable_t* iree_b200_context_executable(iree_b200_context_t* context);
+iree_hal_b200_command_buffer_t* iree_b200_context_command_buffer(iree_b200_context_t* context);
+
+enum { IREE_B200_KIND_F16 = 0, IREE_B200_KIND_BF16 = 1, IREE_B200_KIND_I8 = 2 };
+enum {
+  IREE_B200_EPILOGUE_CAST = 0,        /* accumulator -> input element type (f16 / bf16): truncf consumer */
+  IREE_B200_EPILOGUE_ACCUMULATOR = 1, /* raw f32 / i32 accumulator */
+  IREE_B200_EPILOGUE_REQUANT_F16 = 2, /* i8 only: f16(f32(acc) * row_scale[m] * col_scale[n]) */
+};
+enum {
+  IREE_B200_RHS_KN = 0, /* rhs is [batch, K, N] row-major: linalg.matmul / batch_matmul */
+  IREE_B200_RHS_NK = 1, /* rhs is [batch, N, K] row-major: matmul_transpose_b / mmt */
+};
+enum {
+  IREE_B200_FLAG_FORCE_GENERIC = 1,      /* use the shape-agnostic SIMT kernel */
+  IREE_B200_FLAG_DEVICE_TENSORMAPS = 2,  /* build the tensor maps with the b200_encode_tensormaps dispatch */
+};
+#define IREE_B200_WORKSPACE_BYTES 512
+
+typedef struct {
+  int32_t kind;      /* IREE_B200_KIND_* */
+  int32_t epilogue;  /* IREE_B200_EPILOGUE_* */
+  int32_t M, N, K, batch;
+  int32_t rhs_layout; /* IREE_B200_RHS_* */
+  int32_t tile_n;     /* 0 = choose */
+  int32_t flags;
+} iree_b200_matmul_params_t;
+
+/* linalg.matmul / linalg.batch_matmul dispatch (fill + contraction + elementwise consumer, as
+ * formed by compiler/src/iree/compiler/Dialect/Flow/Transforms/FormDispatchRegions.cpp:224-246,
+ * 534-620); on the reference's CPU path this is pack + iree_uk_mmt4d + unpack
+ * (runtime/src/iree/builtins/ukernel/mmt4d.h:14-21). All pointers are device pointers;
+ * `workspace` is IREE_B200_WORKSPACE_BYTES of device memory, 128-byte aligned, owned by the
+ * caller and not shared between dispatches in flight. Queues work and returns. */
+iree_b200_status_t iree_b200_matmul(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                    const void* lhs, const void* rhs, void* out, const float* row_scale,
+                                    const float* col_scale, void* workspace);
+/* The same in two steps: prepare() writes the tensor maps and clears the status words;
+ * run() only dispatches the kernel and may be repeated while operands stay in place. */
+iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                            const void* lhs, const void* rhs, void* workspace, int32_t* out_tile_n);
+iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                        const void* lhs, const void* rhs, void* out, const float* row_scale,
+                                        const float* col_scale, void* workspace, int32_t tile_n);
+/* Synchronises and returns the device-side status words of a workspace: DEADLINE_EXCEEDED if a
+ * bounded wait inside the kernel ran out, INVALID_ARGUMENT if the kernel refused its arguments. */
+iree_b200_status_t iree_b200_workspace_status(iree_b200_context_t* context, const void* workspace);
+
+/* Host-buffer form of the same dispatch: copies operands in, runs, copies the result out and
+ * waits, i.e. what iree-run-module does around one invocation
+ * (runtime/src/iree/tooling/run_module.c:199-322). */
+iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                         const void* lhs, const void* rhs, void* out, const float* row_scale,
+                                         const float* col_scale);
+
+/* Host-side tensor-map encoding (cuTensorMapEncodeTiled) for a rank-3 row-major tensor
+ * [dim2, dim1, dim0] with 128-byte swizzle; writes 128 bytes to out_map (host memory). */
+iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int32_t elem_bytes, int32_t is_bf16,
+                                               const void* device_ptr, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                               uint32_t box0, uint32_t box1, void* out_map);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IREE_B200_H_ */

@@ -1,0 +1,514 @@
+// Contraction dispatches for sm_100a: matmul / batch_matmul in f16, bf16 and i8 with fused
+// epilogues (cast, raw accumulator, per-row x per-column requantisation).
+//
+// One persistent CTA per SM walks a static list of 128 x BN output tiles:
+//   warp 0     TMA producer: A and B tiles -> 4-stage shared-memory ring (128-byte swizzle)
+//   warp 1     one thread issues tcgen05.mma (kind::f16 / kind::i8), accumulating in TMEM
+//   warp 2     owns the TMEM allocation (512 columns = two 256-column accumulators)
+//   warps 4-7  epilogue: tcgen05.ld -> convert / scale -> 16-byte global stores, overlapped
+//              with the next tile's main loop through the second accumulator
+//
+// Kernel ABI (what the HAL CUDA driver's dispatch passes, in this order,
+// runtime/src/iree/hal/drivers/cuda/stream_command_buffer.c:530-603): every binding as a device
+// pointer, then every push constant as a separate 32-bit value. No CUtensorMap can travel as
+// a parameter, so the tensor maps live in a small workspace binding, written either by the
+// host or by b200_encode_tensormaps below.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int kBM = 128;             // rows of C per tile (= TMEM lanes)
+constexpr int kRowBytes = 128;       // bytes of K per stage row (one swizzle span)
+constexpr int kMaxBN = 256;          // columns of C per tile, at most
+constexpr int kStages = 4;
+constexpr int kAStageBytes = kBM * kRowBytes;       // 16 KiB
+constexpr int kBStageBytes = kMaxBN * kRowBytes;    // 32 KiB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kThreads = 256;
+constexpr int kTmemColumns = 512;
+constexpr int kGemmSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + 256 /*barriers*/;
+
+// Workspace binding: three 128-byte tensor maps followed by status words.
+struct alignas(128) Workspace {
+  uint8_t map_a[128];
+  uint8_t map_b[128];
+  uint8_t map_aux[128];
+  uint32_t status[32];
+};
+
+enum Kind { kF16 = 0, kBF16 = 1, kI8 = 2 };
+enum Epilogue { kEpiCast = 0, kEpiRaw = 1, kEpiRequantF16 = 2 };
+
+// Layout of the right-hand side in memory.
+//   0: [K, N] row-major (linalg.matmul's RHS)      -> "MN-major" operand for the tensor core
+//   1: [N, K] row-major (transposed RHS, mmt-style) -> "K-major" operand
+enum BLayout { kBLayoutKN = 0, kBLayoutNK = 1 };
+
+struct GemmShape {
+  int M, N, K, batch;
+  int b_layout;
+  int bn;  // tile width: a multiple of 32, at most 256; for kBLayoutKN a multiple of the chunk width
+};
+
+__device__ __forceinline__ void report(Workspace* ws, uint32_t code, uint32_t info) {
+  if (atomicCAS(&ws->status[0], 0u, code) == 0u) ws->status[1] = info;
+}
+
+template <int KIND>
+struct KindTraits;
+template <>
+struct KindTraits<kF16> {
+  static constexpr int kElemBytes = 2;
+  static constexpr uint32_t kFormat = 0, kCFormat = 1;
+};
+template <>
+struct KindTraits<kBF16> {
+  static constexpr int kElemBytes = 2;
+  static constexpr uint32_t kFormat = 1, kCFormat = 1;
+};
+template <>
+struct KindTraits<kI8> {
+  static constexpr int kElemBytes = 1;
+  static constexpr uint32_t kFormat = 1, kCFormat = 2;
+};
+
+// The epilogue for one thread: 32 consecutive columns of one output row.
+template <int KIND, int EPI>
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], void* c_base, int64_t row_offset, int col0,
+                                                int N, float row_scale, const float* col_scale, bool vec_ok) {
+  if constexpr (EPI == kEpiRaw) {
+    // Raw 32-bit accumulator (i32 for kind::i8, f32 for kind::f16).
+    uint32_t* out = reinterpret_cast<uint32_t*>(c_base) + row_offset + col0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (vec_ok && col0 + j + 3 < N) {
+        *reinterpret_cast<uint4*>(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+        for (int t = 0; t < 4; ++t)
+          if (col0 + j + t < N) out[j + t] = v[j + t];
+      }
+    }
+  } else {
+    uint16_t h[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float f;
+      if constexpr (EPI == kEpiRequantF16) {
+        // f16( (f32(acc) * a_scale[m]) * w_scale[n] ), same operation order as the consumer generic.
+        f = static_cast<float>(static_cast<int32_t>(v[j])) * row_scale;
+        f = f * ((col0 + j < N) ? col_scale[col0 + j] : 0.f);
+      } else {
+        f = __uint_as_float(v[j]);
+      }
+      if constexpr (KIND == kBF16) {
+        h[j] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+      } else {
+        h[j] = __half_as_ushort(__float2half_rn(f));
+      }
+    }
+    uint16_t* out = reinterpret_cast<uint16_t*>(c_base) + row_offset + col0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (vec_ok && col0 + j + 7 < N) {
+        uint4 q;
+        q.x = h[j] | (uint32_t(h[j + 1]) << 16);
+        q.y = h[j + 2] | (uint32_t(h[j + 3]) << 16);
+        q.z = h[j + 4] | (uint32_t(h[j + 5]) << 16);
+        q.w = h[j + 6] | (uint32_t(h[j + 7]) << 16);
+        *reinterpret_cast<uint4*>(out + j) = q;
+      } else {
+        for (int t = 0; t < 8; ++t)
+          if (col0 + j + t < N) out[j + t] = h[j + t];
+      }
+    }
+  }
+}
+
+template <int KIND, int EPI>
+__device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float* __restrict__ row_scale,
+                                          const float* __restrict__ col_scale, Workspace* __restrict__ ws,
+                                          GemmShape s) {
+  using T = KindTraits<KIND>;
+  constexpr int kElem = T::kElemBytes;
+  constexpr int kBK = kRowBytes / kElem;          // K elements per stage: 64 (16-bit) or 128 (8-bit)
+  constexpr int kUmmaK = 32 / kElem;              // K elements per tcgen05.mma: 16 or 32
+  constexpr int kChunkN = kRowBytes / kElem;      // columns per 128-byte row of a [K,N] tile
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = smem_base + kStages * kStageBytes;
+  // barrier slots (8 bytes each): full[0..3], empty[4..7], tmem_full[8..9], tmem_empty[10..11]
+  auto full_bar = [&](int i) { return bars + 8u * i; };
+  auto empty_bar = [&](int i) { return bars + 8u * (kStages + i); };
+  auto tmem_full_bar = [&](int i) { return bars + 8u * (2 * kStages + i); };
+  auto tmem_empty_bar = [&](int i) { return bars + 8u * (2 * kStages + 2 + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * kStages + 4);
+  const uint32_t abort_slot = tmem_slot + 4;
+  uint8_t* smem_generic = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* abort_flag =
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + 8 * (2 * kStages + 4) + 4);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + 8 * (2 * kStages + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Preconditions the host is expected to honour; checked again here because a misaligned TMA
+  // coordinate or an out-of-range tile width must never reach the hardware.
+  bool bad = s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batch <= 0 || s.bn < 16 || s.bn > kMaxBN || (s.bn & 31) ||
+             (s.K * kElem) % 16 != 0 || (s.b_layout == kBLayoutKN && ((s.N * kElem) % 16 != 0 || s.bn % kChunkN != 0));
+  if (bad) {
+    if (threadIdx.x == 0) report(ws, kStatusBadArgument, 0);
+    return;
+  }
+
+  const int tiles_m = (s.M + kBM - 1) / kBM;
+  const int tiles_n = (s.N + s.bn - 1) / s.bn;
+  const int tiles_per_batch = tiles_m * tiles_n;
+  const int num_tiles = tiles_per_batch * s.batch;
+  const int num_kb = (s.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(full_bar(i), 1);
+      mbar_init(empty_bar(i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full_bar(i), 1);
+      mbar_init(tmem_empty_bar(i), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, kTmemColumns);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // m fastest inside a column of tiles: consecutive CTAs share the B tile and walk down A.
+  auto tile_coords = [&](int t, int& b, int& tm, int& tn) {
+    b = t / tiles_per_batch;
+    int r = t - b * tiles_per_batch;
+    tn = r / tiles_m;
+    tm = r - tn * tiles_m;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tensormap_fence_acquire(ws->map_a);
+      tensormap_fence_acquire(ws->map_b);
+      const uint32_t stage_tx = kAStageBytes + s.bn * kRowBytes;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(t, b, tm, tn);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int st = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(st), ph ^ 1, abort_flag)) {
+            report(ws, kStatusTimeoutEmpty, it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + st * kStageBytes;
+          const uint32_t b_dst = a_dst + kAStageBytes;
+          mbar_arrive_expect_tx(full_bar(st), stage_tx);
+          tma_load_3d(a_dst, ws->map_a, full_bar(st), kb * kBK, tm * kBM, b);
+          if (s.b_layout == kBLayoutNK) {
+            tma_load_3d(b_dst, ws->map_b, full_bar(st), kb * kBK, tn * s.bn, b);
+          } else {
+            // [K,N] tile: one box of (kChunkN columns x kBK rows) per 128-byte column chunk.
+            for (int c = 0; c < s.bn / kChunkN; ++c)
+              tma_load_3d(b_dst + c * (kBK * kRowBytes), ws->map_b, full_bar(st), tn * s.bn + c * kChunkN, kb * kBK,
+                          b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t b_major = (s.b_layout == kBLayoutKN) ? 1u : 0u;
+      const uint32_t idesc = make_instr_desc(T::kCFormat, T::kFormat, T::kFormat, 0u, b_major, kBM, s.bn);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+        const int buf = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar(buf), acc_ph ^ 1, abort_flag)) {
+          report(ws, kStatusTimeoutTmemEmpty, local_tile);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * kMaxBN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int st = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full_bar(st), ph, abort_flag)) {
+            report(ws, kStatusTimeoutFull, it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_src = smem_base + st * kStageBytes;
+          const uint32_t b_src = a_src + kAStageBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // A (K-major, 128-byte swizzle): 8-row groups 1024 bytes apart; K advances 32 bytes.
+            const uint64_t a_desc = make_smem_desc(a_src + k * 32, 16, 1024);
+            uint64_t b_desc;
+            if (s.b_layout == kBLayoutNK) {
+              b_desc = make_smem_desc(b_src + k * 32, 16, 1024);
+            } else {
+              // B (MN-major): rows of K are 128 bytes apart, 8-row groups 1024 bytes apart (stride
+              // offset); the next chunk of columns starts kBK rows later (leading offset).
+              b_desc = make_smem_desc(b_src + k * (kUmmaK * kRowBytes), kBK * kRowBytes, 1024);
+            }
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            if constexpr (KIND == kI8) {
+              mma_i8_ss(d_tmem, a_desc, b_desc, idesc, acc);
+            } else {
+              mma_f16_ss(d_tmem, a_desc, b_desc, idesc, acc);
+            }
+          }
+          tc_commit(empty_bar(st));  // the stage is free once these MMAs have read it
+        }
+        if (ok) tc_commit(tmem_full_bar(buf));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // 16-byte stores need a 16-byte aligned row pitch and base.
+    constexpr int kOutBytes = (EPI == kEpiRaw) ? 4 : 2;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 16 == 0) && ((s.N * kOutBytes) % 16 == 0);
+    uint32_t local_tile = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local_tile) {
+      int b, tm, tn;
+      tile_coords(t, b, tm, tn);
+      const int buf = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      // The warp must take the same branch: tcgen05.ld below is warp-collective.
+      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_ph, abort_flag))) {
+        if (lane == 0) {
+          report(ws, kStatusTimeoutTmemFull, local_tile);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tm * kBM + q * 32 + lane;
+      const int64_t row_offset = (static_cast<int64_t>(b) * s.M + row) * s.N;
+      float rs = 1.f;
+      if constexpr (EPI == kEpiRequantF16) rs = (row < s.M) ? row_scale[row] : 0.f;
+      for (int c = 0; c < s.bn; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxBN + c, v);
+        tc_wait_ld();
+        const int col0 = tn * s.bn + c;
+        if (row < s.M && col0 < s.N) store_row_chunk<KIND, EPI>(v, c_ptr, row_offset, col0, s.N, rs, col_scale, vec_ok);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+    }
+  }
+
+  // Teardown: everyone meets here, also after an abort. After an abort TMA copies may still
+  // be landing in shared memory, so give them a bounded grace period before the CTA exits.
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemColumns);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define B200_GEMM_EXPORT(NAME, KIND, EPI)                                                                     \
+  extern "C" __global__ void __launch_bounds__(kThreads, 1)                                                   \
+      NAME(void* c, void* ws, int M, int N, int K, int batch, int b_layout, int bn) {                         \
+    gemm_body<KIND, EPI>(c, nullptr, nullptr, reinterpret_cast<Workspace*>(ws),                               \
+                         GemmShape{M, N, K, batch, b_layout, bn});                                            \
+  }
+
+// f16 x f16 -> f32 accumulate -> f16   (linalg.matmul + truncf consumer)
+B200_GEMM_EXPORT(b200_matmul_f16_f16, kF16, kEpiCast)
+// f16 x f16 -> f32                     (mmt4d f16f16f32 semantics, row-major operands)
+B200_GEMM_EXPORT(b200_matmul_f16_f32, kF16, kEpiRaw)
+// bf16 x bf16 -> f32 accumulate -> bf16
+B200_GEMM_EXPORT(b200_matmul_bf16_bf16, kBF16, kEpiCast)
+B200_GEMM_EXPORT(b200_matmul_bf16_f32, kBF16, kEpiRaw)
+// i8 x i8 -> i32
+B200_GEMM_EXPORT(b200_matmul_i8_i32, kI8, kEpiRaw)
+
+// i8 x i8 -> i32 -> f16( f32(acc) * a_scale[m] * w_scale[n] )   (W8A8 with its requant consumer fused)
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+    b200_matmul_i8_requant_f16(void* c, const float* a_scale, const float* w_scale, void* ws, int M, int N, int K,
+                               int batch, int b_layout, int bn) {
+  gemm_body<kI8, kEpiRequantF16>(c, a_scale, w_scale, reinterpret_cast<Workspace*>(ws),
+                                 GemmShape{M, N, K, batch, b_layout, bn});
+}
+
+// ---------------------------------------------------------------------------------------------
+// Device-side tensor-map construction for callers that cannot run cuTensorMapEncodeTiled (the
+// stock HAL CUDA driver never does). `templates` holds two 128-byte maps encoded once, on any
+// host, for the right element type, rank 3 and 128-byte swizzle; this kernel patches address,
+// extents, strides and box into copies of them and publishes the result into the workspace.
+//   elem_bytes: 1 or 2.  Operand A is [batch, M, K]; B is [batch, K, N] (b_layout 0) or
+//   [batch, N, K] (b_layout 1).
+// ---------------------------------------------------------------------------------------------
+extern "C" __global__ void __launch_bounds__(32, 1)
+    b200_encode_tensormaps(const void* a, const void* b, const void* templates, void* ws_raw, int M, int N, int K,
+                           int batch, int b_layout, int bn, int elem_bytes) {
+  __shared__ alignas(128) uint8_t maps[2][128];
+  Workspace* ws = reinterpret_cast<Workspace*>(ws_raw);
+  const int lane = threadIdx.x;
+  // 32 lanes x 4 bytes = one 128-byte map per pass.
+  for (int i = 0; i < 2; ++i)
+    reinterpret_cast<uint32_t*>(maps[i])[lane] = reinterpret_cast<const uint32_t*>(templates)[i * 32 + lane];
+  __syncwarp();
+  if (lane == 0) {
+    const int bk = kRowBytes / elem_bytes;
+    const uint32_t ma = smem_u32(maps[0]);
+    tensormap_replace_address(ma, a);
+    tensormap_replace_dim0(ma, K);
+    tensormap_replace_dim1(ma, M);
+    tensormap_replace_dim2(ma, batch);
+    tensormap_replace_stride0(ma, static_cast<uint64_t>(K) * elem_bytes);
+    tensormap_replace_stride1(ma, static_cast<uint64_t>(M) * K * elem_bytes);
+    tensormap_replace_box0(ma, bk);
+    tensormap_replace_box1(ma, kBM);
+    tensormap_replace_box2(ma, 1);
+    const uint32_t mb = smem_u32(maps[1]);
+    tensormap_replace_address(mb, b);
+    if (b_layout == kBLayoutNK) {
+      tensormap_replace_dim0(mb, K);
+      tensormap_replace_dim1(mb, N);
+      tensormap_replace_stride0(mb, static_cast<uint64_t>(K) * elem_bytes);
+      tensormap_replace_box0(mb, bk);
+      tensormap_replace_box1(mb, bn);
+    } else {
+      tensormap_replace_dim0(mb, N);
+      tensormap_replace_dim1(mb, K);
+      tensormap_replace_stride0(mb, static_cast<uint64_t>(N) * elem_bytes);
+      tensormap_replace_box0(mb, bk);  // 128 bytes of columns
+      tensormap_replace_box1(mb, bk);  // one stage of K rows
+    }
+    tensormap_replace_dim2(mb, batch);
+    tensormap_replace_stride1(mb, static_cast<uint64_t>(N) * K * elem_bytes);
+    tensormap_replace_box2(mb, 1);
+  }
+  __syncwarp();
+  tensormap_publish(ws->map_a, smem_u32(maps[0]));
+  tensormap_publish(ws->map_b, smem_u32(maps[1]));
+  if (lane < 32) ws->status[lane] = 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shape-agnostic SIMT contraction: any M, N, K, any alignment. This is the path for operands
+// the TMA preconditions exclude (row pitch not a multiple of 16 bytes), the counterpart of the
+// reference's generic tile functions (builtins/ukernel/mmt4d_tile_generic.c). 16 x 16 threads,
+// one output each, K staged through shared memory 16 at a time.
+//   kind: 0 f16, 1 bf16, 2 i8;  epi: 0 cast to f16/bf16, 1 raw accumulator, 2 requant to f16
+// ---------------------------------------------------------------------------------------------
+template <int KIND>
+__device__ __forceinline__ float load_as_float(const void* p, int64_t i) {
+  if constexpr (KIND == kF16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  if constexpr (KIND == kBF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return 0.f;
+}
+
+template <int KIND, int EPI>
+__device__ __forceinline__ void generic_body(const void* a, const void* b, void* c, const float* row_scale,
+                                             const float* col_scale, int M, int N, int K, int b_layout) {
+  const int batch = blockIdx.z;
+  const int row = blockIdx.y * 16 + threadIdx.y;
+  const int col = blockIdx.x * 16 + threadIdx.x;
+  const int64_t a_off = static_cast<int64_t>(batch) * M * K;
+  const int64_t b_off = static_cast<int64_t>(batch) * N * K;
+  const int64_t c_off = static_cast<int64_t>(batch) * M * N;
+  __shared__ float as[16][17], bs[16][17];
+  __shared__ int ai[16][17], bi[16][17];
+  float accf = 0.f;
+  int acci = 0;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    const int ka = k0 + threadIdx.x;  // A tile: [row][k]
+    const int kb = k0 + threadIdx.y;  // B tile: [k][col]
+    if constexpr (KIND == kI8) {
+      ai[threadIdx.y][threadIdx.x] = (row < M && ka < K) ? reinterpret_cast<const int8_t*>(a)[a_off + int64_t(row) * K + ka] : 0;
+      int v = 0;
+      if (col < N && kb < K)
+        v = (b_layout == kBLayoutKN) ? reinterpret_cast<const int8_t*>(b)[b_off + int64_t(kb) * N + col]
+                                     : reinterpret_cast<const int8_t*>(b)[b_off + int64_t(col) * K + kb];
+      bi[threadIdx.y][threadIdx.x] = v;
+    } else {
+      as[threadIdx.y][threadIdx.x] = (row < M && ka < K) ? load_as_float<KIND>(a, a_off + int64_t(row) * K + ka) : 0.f;
+      float v = 0.f;
+      if (col < N && kb < K)
+        v = (b_layout == kBLayoutKN) ? load_as_float<KIND>(b, b_off + int64_t(kb) * N + col)
+                                     : load_as_float<KIND>(b, b_off + int64_t(col) * K + kb);
+      bs[threadIdx.y][threadIdx.x] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if constexpr (KIND == kI8) {
+        acci += ai[threadIdx.y][k] * bi[k][threadIdx.x];
+      } else {
+        accf = fmaf(as[threadIdx.y][k], bs[k][threadIdx.x], accf);
+      }
+    }
+    __syncthreads();
+  }
+  if (row >= M || col >= N) return;
+  const int64_t o = c_off + int64_t(row) * N + col;
+  if constexpr (EPI == kEpiRaw) {
+    if constexpr (KIND == kI8) reinterpret_cast<int32_t*>(c)[o] = acci;
+    else reinterpret_cast<float*>(c)[o] = accf;
+  } else if constexpr (EPI == kEpiRequantF16) {
+    float f = static_cast<float>(acci) * row_scale[row];
+    f = f * col_scale[col];
+    reinterpret_cast<__half*>(c)[o] = __float2half_rn(f);
+  } else {
+    if constexpr (KIND == kBF16) reinterpret_cast<__nv_bfloat16*>(c)[o] = __float2bfloat16_rn(accf);
+    else reinterpret_cast<__half*>(c)[o] = __float2half_rn(accf);
+  }
+}
+
+#define B200_GENERIC_EXPORT(NAME, KIND, EPI)                                                            \
+  extern "C" __global__ void __launch_bounds__(256)                                                     \
+      NAME(const void* a, const void* b, void* c, int M, int N, int K, int b_layout) {                  \
+    generic_body<KIND, EPI>(a, b, c, nullptr, nullptr, M, N, K, b_layout);                              \
+  }
+B200_GENERIC_EXPORT(b200_matmul_generic_f16_f16, kF16, kEpiCast)
+B200_GENERIC_EXPORT(b200_matmul_generic_f16_f32, kF16, kEpiRaw)
+B200_GENERIC_EXPORT(b200_matmul_generic_bf16_bf16, kBF16, kEpiCast)
+B200_GENERIC_EXPORT(b200_matmul_generic_bf16_f32, kBF16, kEpiRaw)
+B200_GENERIC_EXPORT(b200_matmul_generic_i8_i32, kI8, kEpiRaw)
+extern "C" __global__ void __launch_bounds__(256)
+    b200_matmul_generic_i8_requant_f16(const void* a, const void* b, void* c, const float* a_scale,
+                                       const float* w_scale, int M, int N, int K, int b_layout) {
+  generic_body<kI8, kEpiRequantF16>(a, b, c, a_scale, w_scale, M, N, K, b_layout);
+}

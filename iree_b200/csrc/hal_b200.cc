@@ -1,0 +1,1144 @@
+// Host side of libiree_b200.so: the HAL-shaped runtime slice (device, buffers, ExecutableDef
+// loader, stream command buffer, NCCL channel) and the operator-level contraction entry points
+// declared in include/iree_b200.h. Host code only: the kernels live in a separate sm_100a cubin
+// that enters through the same ExecutableDef container the reference's CUDA driver loads.
+//
+// libcuda.so and libnccl.so are opened at run time, as the reference's
+// cuda_dynamic_symbols.c / nccl_dynamic_symbols.c do, so this library loads (and its symbols
+// can be inspected) on a machine without a GPU; every call that needs the device then
+// returns UNAVAILABLE. There is no CPU execution path.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/iree_b200.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+iree_b200_status_t fail(iree_b200_status_t code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define B200_RETURN_IF_ERROR(expr)                     \
+  do {                                                 \
+    iree_b200_status_t status__ = (expr);              \
+    if (status__ != IREE_B200_STATUS_OK) return status__; \
+  } while (0)
+
+// ------------------------------------------------------------------------------------------
+// Dynamic CUDA driver symbols.
+// ------------------------------------------------------------------------------------------
+struct CudaSymbols {
+  void* handle = nullptr;
+  bool tried = false;
+  std::string error;
+#define CU_FN(name, ...) CUresult (*name)(__VA_ARGS__) = nullptr;
+  CU_FN(cuInit, unsigned)
+  CU_FN(cuDeviceGet, CUdevice*, int)
+  CU_FN(cuDeviceGetCount, int*)
+  CU_FN(cuDeviceGetName, char*, int, CUdevice)
+  CU_FN(cuDeviceGetAttribute, int*, CUdevice_attribute, CUdevice)
+  CU_FN(cuDevicePrimaryCtxRetain, CUcontext*, CUdevice)
+  CU_FN(cuDevicePrimaryCtxRelease, CUdevice)
+  CU_FN(cuCtxSetCurrent, CUcontext)
+  CU_FN(cuStreamCreate, CUstream*, unsigned)
+  CU_FN(cuStreamDestroy, CUstream)
+  CU_FN(cuStreamSynchronize, CUstream)
+  CU_FN(cuMemAlloc, CUdeviceptr*, size_t)
+  CU_FN(cuMemFree, CUdeviceptr)
+  CU_FN(cuMemHostAlloc, void**, size_t, unsigned)
+  CU_FN(cuMemFreeHost, void*)
+  CU_FN(cuMemcpyHtoDAsync, CUdeviceptr, const void*, size_t, CUstream)
+  CU_FN(cuMemcpyDtoHAsync, void*, CUdeviceptr, size_t, CUstream)
+  CU_FN(cuMemsetD8Async, CUdeviceptr, unsigned char, size_t, CUstream)
+  CU_FN(cuModuleLoadDataEx, CUmodule*, const void*, unsigned, CUjit_option*, void**)
+  CU_FN(cuModuleUnload, CUmodule)
+  CU_FN(cuModuleGetFunction, CUfunction*, CUmodule, const char*)
+  CU_FN(cuFuncSetAttribute, CUfunction, CUfunction_attribute, int)
+  CU_FN(cuLaunchKernel, CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+        void**, void**)
+  CU_FN(cuGetErrorName, CUresult, const char**)
+  CU_FN(cuGetErrorString, CUresult, const char**)
+  CU_FN(cuTensorMapEncodeTiled, CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+        CUtensorMapL2promotion, CUtensorMapFloatOOBfill)
+#undef CU_FN
+};
+CudaSymbols g_cu;
+std::mutex g_cu_mutex;
+
+template <typename T>
+bool load_sym(void* handle, const char* name, T& out) {
+  out = reinterpret_cast<T>(dlsym(handle, name));
+  return out != nullptr;
+}
+
+iree_b200_status_t ensure_cuda() {
+  std::lock_guard<std::mutex> lock(g_cu_mutex);
+  if (!g_cu.tried) {
+    g_cu.tried = true;
+    const char* names[] = {"libcuda.so.1", "libcuda.so"};
+    for (const char* n : names) {
+      g_cu.handle = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+      if (g_cu.handle) break;
+    }
+    if (!g_cu.handle) {
+      g_cu.error = "CUDA driver library (libcuda.so.1) could not be loaded; no GPU on this machine?";
+    } else {
+      bool ok = true;
+#define LOAD(field, symbol) ok = load_sym(g_cu.handle, symbol, g_cu.field) && ok;
+      LOAD(cuInit, "cuInit")
+      LOAD(cuDeviceGet, "cuDeviceGet")
+      LOAD(cuDeviceGetCount, "cuDeviceGetCount")
+      LOAD(cuDeviceGetName, "cuDeviceGetName")
+      LOAD(cuDeviceGetAttribute, "cuDeviceGetAttribute")
+      LOAD(cuDevicePrimaryCtxRetain, "cuDevicePrimaryCtxRetain")
+      LOAD(cuDevicePrimaryCtxRelease, "cuDevicePrimaryCtxRelease_v2")
+      LOAD(cuCtxSetCurrent, "cuCtxSetCurrent")
+      LOAD(cuStreamCreate, "cuStreamCreate")
+      LOAD(cuStreamDestroy, "cuStreamDestroy_v2")
+      LOAD(cuStreamSynchronize, "cuStreamSynchronize")
+      LOAD(cuMemAlloc, "cuMemAlloc_v2")
+      LOAD(cuMemFree, "cuMemFree_v2")
+      LOAD(cuMemHostAlloc, "cuMemHostAlloc")
+      LOAD(cuMemFreeHost, "cuMemFreeHost")
+      LOAD(cuMemcpyHtoDAsync, "cuMemcpyHtoDAsync_v2")
+      LOAD(cuMemcpyDtoHAsync, "cuMemcpyDtoHAsync_v2")
+      LOAD(cuMemsetD8Async, "cuMemsetD8Async")
+      LOAD(cuModuleLoadDataEx, "cuModuleLoadDataEx")
+      LOAD(cuModuleUnload, "cuModuleUnload")
+      LOAD(cuModuleGetFunction, "cuModuleGetFunction")
+      LOAD(cuFuncSetAttribute, "cuFuncSetAttribute")
+      LOAD(cuLaunchKernel, "cuLaunchKernel")
+      LOAD(cuGetErrorName, "cuGetErrorName")
+      LOAD(cuGetErrorString, "cuGetErrorString")
+      LOAD(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
+#undef LOAD
+      if (!ok) {
+        g_cu.error = "CUDA driver library is missing required symbols";
+        g_cu.handle = nullptr;
+      } else {
+        CUresult r = g_cu.cuInit(0);
+        if (r != CUDA_SUCCESS) {
+          g_cu.error = "cuInit failed (" + std::to_string(static_cast<int>(r)) + ")";
+          g_cu.handle = nullptr;
+        }
+      }
+    }
+  }
+  if (!g_cu.handle) return fail(IREE_B200_STATUS_UNAVAILABLE, "%s", g_cu.error.c_str());
+  return IREE_B200_STATUS_OK;
+}
+
+// CUresult -> status with the driver's own name and text, like cuda_status_util.c.
+iree_b200_status_t cu_check(CUresult r, const char* what) {
+  if (r == CUDA_SUCCESS) return IREE_B200_STATUS_OK;
+  const char *name = "?", *text = "?";
+  if (g_cu.cuGetErrorName) g_cu.cuGetErrorName(r, &name);
+  if (g_cu.cuGetErrorString) g_cu.cuGetErrorString(r, &text);
+  iree_b200_status_t code = IREE_B200_STATUS_INTERNAL;
+  if (r == CUDA_ERROR_OUT_OF_MEMORY) code = IREE_B200_STATUS_RESOURCE_EXHAUSTED;
+  if (r == CUDA_ERROR_INVALID_VALUE) code = IREE_B200_STATUS_INVALID_ARGUMENT;
+  if (r == CUDA_ERROR_NOT_FOUND) code = IREE_B200_STATUS_NOT_FOUND;
+  return fail(code, "%s: %s (%s)", what, name ? name : "?", text ? text : "?");
+}
+#define CU_RETURN_IF_ERROR(expr, what) B200_RETURN_IF_ERROR(cu_check((expr), what))
+
+// ------------------------------------------------------------------------------------------
+// Dynamic NCCL symbols (only touched when a channel is created).
+// ------------------------------------------------------------------------------------------
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+struct NcclSymbols {
+  void* handle = nullptr;
+  bool tried = false;
+  std::string error;
+  int (*ncclGetVersion)(int*) = nullptr;
+  int (*ncclGetUniqueId)(ncclUniqueId*) = nullptr;
+  int (*ncclCommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*ncclCommDestroy)(ncclComm_t) = nullptr;
+  int (*ncclAllGather)(const void*, void*, size_t, int, ncclComm_t, CUstream) = nullptr;
+  int (*ncclGroupStart)() = nullptr;
+  int (*ncclGroupEnd)() = nullptr;
+  const char* (*ncclGetErrorString)(int) = nullptr;
+};
+NcclSymbols g_nccl;
+
+iree_b200_status_t ensure_nccl() {
+  std::lock_guard<std::mutex> lock(g_cu_mutex);
+  if (!g_nccl.tried) {
+    g_nccl.tried = true;
+    // A copy already loaded into the process (for instance by a Python framework) is preferred,
+    // so that one NCCL instance owns the NVLink resources.
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+      g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_NOLOAD | RTLD_LOCAL);
+      if (g_nccl.handle) break;
+    }
+    const char* env = getenv("IREE_B200_NCCL_LIBRARY");
+    if (!g_nccl.handle && env) g_nccl.handle = dlopen(env, RTLD_NOW | RTLD_LOCAL);
+    for (const char* n : names) {
+      if (g_nccl.handle) break;
+      g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+    }
+    if (!g_nccl.handle) {
+      g_nccl.error = "NCCL library (libnccl.so.2) could not be loaded";
+    } else {
+      bool ok = true;
+      ok = load_sym(g_nccl.handle, "ncclGetVersion", g_nccl.ncclGetVersion) && ok;
+      ok = load_sym(g_nccl.handle, "ncclGetUniqueId", g_nccl.ncclGetUniqueId) && ok;
+      ok = load_sym(g_nccl.handle, "ncclCommInitRank", g_nccl.ncclCommInitRank) && ok;
+      ok = load_sym(g_nccl.handle, "ncclCommDestroy", g_nccl.ncclCommDestroy) && ok;
+      ok = load_sym(g_nccl.handle, "ncclAllGather", g_nccl.ncclAllGather) && ok;
+      ok = load_sym(g_nccl.handle, "ncclGroupStart", g_nccl.ncclGroupStart) && ok;
+      ok = load_sym(g_nccl.handle, "ncclGroupEnd", g_nccl.ncclGroupEnd) && ok;
+      ok = load_sym(g_nccl.handle, "ncclGetErrorString", g_nccl.ncclGetErrorString) && ok;
+      if (!ok) {
+        g_nccl.error = "NCCL library is missing required symbols";
+        g_nccl.handle = nullptr;
+      }
+    }
+  }
+  if (!g_nccl.handle) return fail(IREE_B200_STATUS_UNAVAILABLE, "%s", g_nccl.error.c_str());
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t nccl_check(int r, const char* what) {
+  if (r == 0) return IREE_B200_STATUS_OK;
+  return fail(IREE_B200_STATUS_INTERNAL, "%s: NCCL error %d (%s)", what, r,
+              g_nccl.ncclGetErrorString ? g_nccl.ncclGetErrorString(r) : "?");
+}
+
+// ------------------------------------------------------------------------------------------
+// Minimal flatbuffer reader / writer for ExecutableDef.
+// ------------------------------------------------------------------------------------------
+struct ExecutableDefView {
+  std::vector<std::string> entry_points;
+  std::vector<uint32_t> block_sizes;  // 3 per entry
+  std::vector<uint32_t> shared_memory;
+  const uint8_t* image = nullptr;
+  size_t image_size = 0;
+};
+
+struct FbReader {
+  const uint8_t* data;
+  size_t size;
+  bool in(size_t pos, size_t len) const { return pos <= size && len <= size - pos; }
+  bool u16(size_t pos, uint16_t* v) const {
+    if (!in(pos, 2)) return false;
+    memcpy(v, data + pos, 2);
+    return true;
+  }
+  bool u32(size_t pos, uint32_t* v) const {
+    if (!in(pos, 4)) return false;
+    memcpy(v, data + pos, 4);
+    return true;
+  }
+  bool i32(size_t pos, int32_t* v) const {
+    if (!in(pos, 4)) return false;
+    memcpy(v, data + pos, 4);
+    return true;
+  }
+};
+
+// Resolves table field `index` to the absolute position of its value (0 when absent).
+bool fb_field(const FbReader& r, size_t table, int index, size_t* out_pos) {
+  int32_t soff;
+  if (!r.i32(table, &soff)) return false;
+  int64_t vt = static_cast<int64_t>(table) - soff;
+  if (vt < 0 || !r.in(static_cast<size_t>(vt), 4)) return false;
+  uint16_t vt_size, field_off = 0;
+  if (!r.u16(static_cast<size_t>(vt), &vt_size)) return false;
+  size_t slot = 4 + 2 * static_cast<size_t>(index);
+  if (slot + 2 <= vt_size && !r.u16(static_cast<size_t>(vt) + slot, &field_off)) return false;
+  *out_pos = field_off ? table + field_off : 0;
+  return true;
+}
+// Follows the uoffset stored at pos.
+bool fb_indirect(const FbReader& r, size_t pos, size_t* out) {
+  uint32_t off;
+  if (!r.u32(pos, &off)) return false;
+  *out = pos + off;
+  return r.in(*out, 4);
+}
+
+iree_b200_status_t parse_executable_def(const void* data, size_t size, ExecutableDefView* view) {
+  if (!data) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "flatbuffer data is not present");
+  FbReader r{static_cast<const uint8_t*>(data), size};
+  const char* bad = "flatbuffer verification failed";
+  if (size < 12 || memcmp(r.data + 4, "CUDA", 4) != 0)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: file identifier is not 'CUDA'", bad);
+  size_t table;
+  if (!fb_indirect(r, 0, &table)) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: root out of range", bad);
+  size_t f_entries, f_blocks, f_smem, f_image;
+  if (!fb_field(r, table, 0, &f_entries) || !fb_field(r, table, 1, &f_blocks) || !fb_field(r, table, 2, &f_smem) ||
+      !fb_field(r, table, 3, &f_image))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: vtable out of range", bad);
+  if (f_entries) {
+    size_t vec;
+    uint32_t n;
+    if (!fb_indirect(r, f_entries, &vec) || !r.u32(vec, &n) || !r.in(vec + 4, 4ull * n))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: entry_points out of range", bad);
+    for (uint32_t i = 0; i < n; ++i) {
+      size_t str;
+      uint32_t len;
+      if (!fb_indirect(r, vec + 4 + 4ull * i, &str) || !r.u32(str, &len) || !r.in(str + 4, static_cast<size_t>(len) + 1))
+        return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: entry point %u out of range", bad, i);
+      view->entry_points.emplace_back(reinterpret_cast<const char*>(r.data + str + 4), len);
+    }
+  }
+  if (f_blocks) {
+    size_t vec;
+    uint32_t n;
+    if (!fb_indirect(r, f_blocks, &vec) || !r.u32(vec, &n) || !r.in(vec + 4, 12ull * n))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: block_sizes out of range", bad);
+    view->block_sizes.resize(3ull * n);
+    memcpy(view->block_sizes.data(), r.data + vec + 4, 12ull * n);
+  }
+  if (f_smem) {
+    size_t vec;
+    uint32_t n;
+    if (!fb_indirect(r, f_smem, &vec) || !r.u32(vec, &n) || !r.in(vec + 4, 4ull * n))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: shared_memory_size out of range", bad);
+    view->shared_memory.resize(n);
+    memcpy(view->shared_memory.data(), r.data + vec + 4, 4ull * n);
+  }
+  if (f_image) {
+    size_t str;
+    uint32_t len;
+    if (!fb_indirect(r, f_image, &str) || !r.u32(str, &len) || !r.in(str + 4, static_cast<size_t>(len) + 1))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "%s: ptx_image out of range", bad);
+    view->image = r.data + str + 4;
+    view->image_size = len;
+  }
+  // Content rules of native_executable.c:76-108.
+  for (size_t i = 0; i < view->entry_points.size(); ++i)
+    if (view->entry_points[i].empty())
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "executable entry point %zu has no name", i);
+  if (view->block_sizes.empty()) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "no block sizes present");
+  if (view->entry_points.size() != view->block_sizes.size() / 3)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "entry points (%zu) and block sizes (%zu) count mismatch",
+                view->entry_points.size(), view->block_sizes.size() / 3);
+  if (view->image_size == 0) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "no PTX image present");
+  return IREE_B200_STATUS_OK;
+}
+
+void put_u32(std::vector<uint8_t>& b, size_t pos, uint32_t v) { memcpy(b.data() + pos, &v, 4); }
+size_t align_up(std::vector<uint8_t>& b, size_t a) {
+  while (b.size() % a) b.push_back(0);
+  return b.size();
+}
+
+}  // namespace
+
+// ==========================================================================================
+// Objects
+// ==========================================================================================
+struct iree_hal_b200_device_t {
+  CUdevice device = 0;
+  CUcontext context = nullptr;
+  CUstream stream = nullptr;
+  int sm_count = 0, cc = 0, max_smem = 0;
+  char name[128] = {0};
+};
+
+struct iree_hal_b200_executable_t {
+  iree_hal_b200_device_t* device = nullptr;
+  CUmodule module = nullptr;
+  struct Entry {
+    std::string name;
+    CUfunction fn;
+    uint32_t block[3];
+    uint32_t smem;
+  };
+  std::vector<Entry> entries;
+};
+
+struct iree_hal_b200_command_buffer_t {
+  iree_hal_b200_device_t* device = nullptr;
+  uint32_t constants[IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT] = {0};
+  void* bindings[IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT][IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT] = {{nullptr}};
+  uint64_t launches = 0;
+};
+
+struct iree_hal_b200_channel_t {
+  iree_hal_b200_device_t* device = nullptr;
+  ncclComm_t comm = nullptr;
+  int32_t rank = 0, count = 1;
+};
+
+extern "C" {
+
+const char* iree_b200_last_error(void) { return g_last_error.c_str(); }
+
+// ---- device ----------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_device_create(int32_t ordinal, iree_hal_b200_device_t** out_device) {
+  if (!out_device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_device is NULL");
+  *out_device = nullptr;
+  B200_RETURN_IF_ERROR(ensure_cuda());
+  int count = 0;
+  CU_RETURN_IF_ERROR(g_cu.cuDeviceGetCount(&count), "cuDeviceGetCount");
+  if (ordinal < 0 || ordinal >= count)
+    return fail(IREE_B200_STATUS_NOT_FOUND, "device ordinal %d out of range (%d devices)", ordinal, count);
+  auto* d = new iree_hal_b200_device_t();
+  iree_b200_status_t st = cu_check(g_cu.cuDeviceGet(&d->device, ordinal), "cuDeviceGet");
+  if (!st) st = cu_check(g_cu.cuDevicePrimaryCtxRetain(&d->context, d->device), "cuDevicePrimaryCtxRetain");
+  if (st) {
+    delete d;
+    return st;
+  }
+  st = cu_check(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  if (!st) st = cu_check(g_cu.cuStreamCreate(&d->stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+  int major = 0, minor = 0;
+  if (!st) {
+    g_cu.cuDeviceGetName(d->name, sizeof d->name, d->device);
+    g_cu.cuDeviceGetAttribute(&d->sm_count, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, d->device);
+    g_cu.cuDeviceGetAttribute(&major, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR, d->device);
+    g_cu.cuDeviceGetAttribute(&minor, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MINOR, d->device);
+    g_cu.cuDeviceGetAttribute(&d->max_smem, CU_DEVICE_ATTRIBUTE_MAX_SHARED_MEMORY_PER_BLOCK_OPTIN, d->device);
+    d->cc = major * 10 + minor;
+  }
+  if (st) {
+    g_cu.cuDevicePrimaryCtxRelease(d->device);
+    delete d;
+    return st;
+  }
+  *out_device = d;
+  return IREE_B200_STATUS_OK;
+}
+
+void iree_hal_b200_device_release(iree_hal_b200_device_t* device) {
+  if (!device) return;
+  g_cu.cuCtxSetCurrent(device->context);
+  if (device->stream) {
+    g_cu.cuStreamSynchronize(device->stream);
+    g_cu.cuStreamDestroy(device->stream);
+  }
+  g_cu.cuDevicePrimaryCtxRelease(device->device);
+  delete device;
+}
+
+iree_b200_status_t iree_hal_b200_device_query(iree_hal_b200_device_t* device, char* name, size_t name_capacity,
+                                              int32_t* out_sm_count, int32_t* out_compute_capability,
+                                              int32_t* out_max_shared_memory) {
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  if (name && name_capacity) snprintf(name, name_capacity, "%s", device->name);
+  if (out_sm_count) *out_sm_count = device->sm_count;
+  if (out_compute_capability) *out_compute_capability = device->cc;
+  if (out_max_shared_memory) *out_max_shared_memory = device->max_smem;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_device_synchronize(iree_hal_b200_device_t* device) {
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuStreamSynchronize(device->stream), "cuStreamSynchronize");
+  return IREE_B200_STATUS_OK;
+}
+
+void* iree_hal_b200_device_stream(iree_hal_b200_device_t* device) { return device ? device->stream : nullptr; }
+
+// ---- buffers ---------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_buffer_allocate(iree_hal_b200_device_t* device, size_t byte_length,
+                                                 void** out_device_ptr) {
+  if (!device || !out_device_ptr) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CUdeviceptr p = 0;
+  CU_RETURN_IF_ERROR(g_cu.cuMemAlloc(&p, byte_length ? byte_length : 1), "cuMemAlloc");
+  *out_device_ptr = reinterpret_cast<void*>(p);
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_buffer_free(iree_hal_b200_device_t* device, void* device_ptr) {
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  if (!device_ptr) return IREE_B200_STATUS_OK;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemFree(reinterpret_cast<CUdeviceptr>(device_ptr)), "cuMemFree");
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_host_allocate(iree_hal_b200_device_t* device, size_t byte_length,
+                                               void** out_pinned_host_ptr) {
+  if (!device || !out_pinned_host_ptr) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemHostAlloc(out_pinned_host_ptr, byte_length ? byte_length : 1, 0), "cuMemHostAlloc");
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_host_free(iree_hal_b200_device_t* device, void* pinned_host_ptr) {
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  if (!pinned_host_ptr) return IREE_B200_STATUS_OK;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemFreeHost(pinned_host_ptr), "cuMemFreeHost");
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_transfer_h2d(iree_hal_b200_device_t* device, const void* source,
+                                              void* target_device_ptr, size_t byte_length) {
+  if (!device || (byte_length && (!source || !target_device_ptr)))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (!byte_length) return IREE_B200_STATUS_OK;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemcpyHtoDAsync(reinterpret_cast<CUdeviceptr>(target_device_ptr), source, byte_length,
+                                            device->stream),
+                     "cuMemcpyHtoDAsync");
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_transfer_d2h(iree_hal_b200_device_t* device, const void* source_device_ptr,
+                                              void* target, size_t byte_length) {
+  if (!device || (byte_length && (!source_device_ptr || !target)))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (!byte_length) return IREE_B200_STATUS_OK;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemcpyDtoHAsync(target, reinterpret_cast<CUdeviceptr>(source_device_ptr), byte_length,
+                                            device->stream),
+                     "cuMemcpyDtoHAsync");
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_fill_buffer(iree_hal_b200_device_t* device, void* device_ptr, size_t byte_length,
+                                             uint8_t pattern) {
+  if (!device || (byte_length && !device_ptr)) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (!byte_length) return IREE_B200_STATUS_OK;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemsetD8Async(reinterpret_cast<CUdeviceptr>(device_ptr), pattern, byte_length,
+                                          device->stream),
+                     "cuMemsetD8Async");
+  return IREE_B200_STATUS_OK;
+}
+
+// ---- ExecutableDef writer ----------------------------------------------------------------------
+iree_b200_status_t iree_b200_executable_def_build(int32_t entry_count, const char* const* entry_names,
+                                                  const uint32_t* block_sizes_xyz,
+                                                  const uint32_t* shared_memory_sizes, const void* image,
+                                                  size_t image_size, void* out_data, size_t out_capacity,
+                                                  size_t* out_size) {
+  if (entry_count < 0 || (entry_count && (!entry_names || !block_sizes_xyz || !shared_memory_sizes)) || !out_size)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  // Laid out front to back: header, vtable, table, then the vectors / strings it points at.
+  std::vector<uint8_t> b;
+  b.resize(8, 0);
+  memcpy(b.data() + 4, "CUDA", 4);
+  // vtable: size 14 (4 + 5 fields * 2), table size 24 (soffset + 5 uoffsets), field offsets.
+  const size_t vt = b.size();
+  const uint16_t vtable[7] = {14, 24, 4, 8, 12, 16, 0 /* source_locations absent */};
+  b.insert(b.end(), reinterpret_cast<const uint8_t*>(vtable), reinterpret_cast<const uint8_t*>(vtable) + 14);
+  b.resize(b.size() + 2, 0);  // pad so the table is 4-byte aligned
+  const size_t table = b.size();
+  b.resize(table + 24, 0);
+  const int32_t soff = static_cast<int32_t>(table - vt);
+  memcpy(b.data() + table, &soff, 4);
+  put_u32(b, 0, static_cast<uint32_t>(table));
+
+  // entry_points: vector of offsets to strings.
+  const size_t vec_entries = align_up(b, 4);
+  b.resize(vec_entries + 4 + 4ull * entry_count, 0);
+  put_u32(b, vec_entries, static_cast<uint32_t>(entry_count));
+  put_u32(b, table + 4, static_cast<uint32_t>(vec_entries - (table + 4)));
+  for (int32_t i = 0; i < entry_count; ++i) {
+    const char* name = entry_names[i] ? entry_names[i] : "";
+    const size_t str = align_up(b, 4);
+    const uint32_t len = static_cast<uint32_t>(strlen(name));
+    b.resize(str + 4 + len + 1, 0);
+    put_u32(b, str, len);
+    memcpy(b.data() + str + 4, name, len);
+    const size_t slot = vec_entries + 4 + 4ull * i;
+    put_u32(b, slot, static_cast<uint32_t>(str - slot));
+  }
+  // block_sizes: vector of inline structs {x, y, z}.
+  const size_t vec_blocks = align_up(b, 4);
+  b.resize(vec_blocks + 4 + 12ull * entry_count, 0);
+  put_u32(b, vec_blocks, static_cast<uint32_t>(entry_count));
+  if (entry_count) memcpy(b.data() + vec_blocks + 4, block_sizes_xyz, 12ull * entry_count);
+  put_u32(b, table + 8, static_cast<uint32_t>(vec_blocks - (table + 8)));
+  // shared_memory_size: vector of u32.
+  const size_t vec_smem = align_up(b, 4);
+  b.resize(vec_smem + 4 + 4ull * entry_count, 0);
+  put_u32(b, vec_smem, static_cast<uint32_t>(entry_count));
+  if (entry_count) memcpy(b.data() + vec_smem + 4, shared_memory_sizes, 4ull * entry_count);
+  put_u32(b, table + 12, static_cast<uint32_t>(vec_smem - (table + 12)));
+  // ptx_image: a string with an explicit length, so binary images are safe.
+  const size_t str_image = align_up(b, 4);
+  b.resize(str_image + 4 + image_size + 1, 0);
+  put_u32(b, str_image, static_cast<uint32_t>(image_size));
+  if (image_size) memcpy(b.data() + str_image + 4, image, image_size);
+  put_u32(b, table + 16, static_cast<uint32_t>(str_image - (table + 16)));
+
+  *out_size = b.size();
+  if (!out_data) return IREE_B200_STATUS_OK;
+  if (out_capacity < b.size())
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "output buffer too small: %zu < %zu", out_capacity, b.size());
+  memcpy(out_data, b.data(), b.size());
+  return IREE_B200_STATUS_OK;
+}
+
+// ---- executable ---------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_executable_create(iree_hal_b200_device_t* device, const char* executable_format,
+                                                   const void* executable_data, size_t executable_data_size,
+                                                   iree_hal_b200_executable_t** out_executable) {
+  if (!out_executable) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_executable is NULL");
+  *out_executable = nullptr;
+  if (!executable_format || strcmp(executable_format, "PTXE") != 0)
+    return fail(IREE_B200_STATUS_NOT_FOUND, "no executable implementation registered for the given format '%s'",
+                executable_format ? executable_format : "(null)");
+  ExecutableDefView view;
+  B200_RETURN_IF_ERROR(parse_executable_def(executable_data, executable_data_size, &view));
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  for (size_t i = 0; i < view.entry_points.size(); ++i) {
+    const uint32_t smem = i < view.shared_memory.size() ? view.shared_memory[i] : 0;
+    if (smem > static_cast<uint32_t>(device->max_smem))
+      return fail(IREE_B200_STATUS_RESOURCE_EXHAUSTED,
+                  "function '%s' requested shared memory size of %u bytes larger than allowed size of %d bytes",
+                  view.entry_points[i].c_str(), smem, device->max_smem);
+  }
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  auto* exe = new iree_hal_b200_executable_t();
+  exe->device = device;
+  // The image may be PTX text or a cubin; the driver tells them apart (native_executable.c:174-176).
+  std::vector<uint8_t> image(view.image, view.image + view.image_size);
+  image.push_back(0);
+  iree_b200_status_t st = cu_check(g_cu.cuModuleLoadDataEx(&exe->module, image.data(), 0, nullptr, nullptr),
+                                   "cuModuleLoadDataEx");
+  for (size_t i = 0; !st && i < view.entry_points.size(); ++i) {
+    iree_hal_b200_executable_t::Entry e;
+    e.name = view.entry_points[i];
+    memcpy(e.block, &view.block_sizes[3 * i], 12);
+    e.smem = i < view.shared_memory.size() ? view.shared_memory[i] : 0;
+    st = cu_check(g_cu.cuModuleGetFunction(&e.fn, exe->module, e.name.c_str()), e.name.c_str());
+    if (!st && e.smem)
+      st = cu_check(g_cu.cuFuncSetAttribute(e.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                            static_cast<int>(e.smem)),
+                    "cuFuncSetAttribute(MAX_DYNAMIC_SHARED_SIZE_BYTES)");
+    if (!st) exe->entries.push_back(e);
+  }
+  if (st) {
+    if (exe->module) g_cu.cuModuleUnload(exe->module);
+    delete exe;
+    return st;
+  }
+  *out_executable = exe;
+  return IREE_B200_STATUS_OK;
+}
+
+void iree_hal_b200_executable_release(iree_hal_b200_executable_t* executable) {
+  if (!executable) return;
+  g_cu.cuCtxSetCurrent(executable->device->context);
+  if (executable->module) g_cu.cuModuleUnload(executable->module);
+  delete executable;
+}
+int32_t iree_hal_b200_executable_entry_count(const iree_hal_b200_executable_t* executable) {
+  return executable ? static_cast<int32_t>(executable->entries.size()) : 0;
+}
+int32_t iree_hal_b200_executable_lookup(const iree_hal_b200_executable_t* executable, const char* entry_name) {
+  if (!executable || !entry_name) return -1;
+  for (size_t i = 0; i < executable->entries.size(); ++i)
+    if (executable->entries[i].name == entry_name) return static_cast<int32_t>(i);
+  return -1;
+}
+
+// ---- command buffer -------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_command_buffer_create(iree_hal_b200_device_t* device,
+                                                       iree_hal_b200_command_buffer_t** out_command_buffer) {
+  if (!device || !out_command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  auto* cb = new iree_hal_b200_command_buffer_t();
+  cb->device = device;
+  *out_command_buffer = cb;
+  return IREE_B200_STATUS_OK;
+}
+void iree_hal_b200_command_buffer_release(iree_hal_b200_command_buffer_t* command_buffer) { delete command_buffer; }
+
+iree_b200_status_t iree_hal_b200_command_buffer_push_constants(iree_hal_b200_command_buffer_t* command_buffer,
+                                                               size_t offset, const void* values,
+                                                               size_t values_length) {
+  if (!command_buffer || (values_length && !values)) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if ((offset % 4) || (values_length % 4))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "push constant offset/length must be multiples of 4 bytes");
+  if (offset + values_length > sizeof command_buffer->constants)
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "push constant range [%zu, %zu) exceeds the %d-constant limit", offset,
+                offset + values_length, IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT);
+  memcpy(reinterpret_cast<uint8_t*>(command_buffer->constants) + offset, values, values_length);
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_push_descriptor_set(
+    iree_hal_b200_command_buffer_t* command_buffer, uint32_t set, size_t binding_count,
+    const iree_hal_b200_descriptor_set_binding_t* bindings) {
+  if (!command_buffer || (binding_count && !bindings)) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (set >= IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT)
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "descriptor set %u out of range", set);
+  for (size_t i = 0; i < binding_count; ++i) {
+    if (bindings[i].binding >= IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT)
+      return fail(IREE_B200_STATUS_OUT_OF_RANGE, "binding %u out of range", bindings[i].binding);
+    command_buffer->bindings[set][bindings[i].binding] = bindings[i].device_ptr;
+  }
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_buffer_t* command_buffer,
+                                                         iree_hal_b200_executable_t* executable, int32_t entry_point,
+                                                         uint32_t binding_count, uint32_t constant_count,
+                                                         uint32_t workgroup_x, uint32_t workgroup_y,
+                                                         uint32_t workgroup_z) {
+  if (!command_buffer || !executable) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (entry_point < 0 || entry_point >= static_cast<int32_t>(executable->entries.size()))
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "entry point ordinal %d out of range (%zu entries)", entry_point,
+                executable->entries.size());
+  if (binding_count > IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT ||
+      constant_count > IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT)
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "binding / constant count exceeds the pipeline layout limits");
+  if (!workgroup_x || !workgroup_y || !workgroup_z) return IREE_B200_STATUS_OK;  // empty dispatch
+  const auto& e = executable->entries[entry_point];
+  // Kernel parameters: every binding as a device pointer, then each constant on its own
+  // (stream_command_buffer.c:538-594).
+  void* params[IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT + IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT];
+  for (uint32_t i = 0; i < binding_count; ++i) params[i] = &command_buffer->bindings[0][i];
+  for (uint32_t i = 0; i < constant_count; ++i) params[binding_count + i] = &command_buffer->constants[i];
+  iree_hal_b200_device_t* d = command_buffer->device;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuLaunchKernel(e.fn, workgroup_x, workgroup_y, workgroup_z, e.block[0], e.block[1],
+                                         e.block[2], e.smem, d->stream, params, nullptr),
+                     e.name.c_str());
+  ++command_buffer->launches;
+  return IREE_B200_STATUS_OK;
+}
+
+uint64_t iree_hal_b200_command_buffer_launch_count(const iree_hal_b200_command_buffer_t* command_buffer) {
+  return command_buffer ? command_buffer->launches : 0;
+}
+
+// ---- channel ------------------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_channel_create_id(void* out_id, size_t id_capacity) {
+  if (!out_id || id_capacity < IREE_HAL_B200_CHANNEL_ID_SIZE)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "channel id buffer must hold %d bytes", IREE_HAL_B200_CHANNEL_ID_SIZE);
+  B200_RETURN_IF_ERROR(ensure_nccl());
+  ncclUniqueId id;
+  B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclGetUniqueId(&id), "ncclGetUniqueId"));
+  memcpy(out_id, &id, sizeof id);
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_channel_create(iree_hal_b200_device_t* device, const void* id, size_t id_size,
+                                                int32_t rank, int32_t count,
+                                                iree_hal_b200_channel_t** out_channel) {
+  if (!out_channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_channel is NULL");
+  *out_channel = nullptr;
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  if (!id || id_size != IREE_HAL_B200_CHANNEL_ID_SIZE)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NCCL ID must be %d bytes matching the ncclUniqueId struct but caller provided %zu bytes",
+                IREE_HAL_B200_CHANNEL_ID_SIZE, id_size);
+  if (count < 1 || rank < 0 || rank >= count)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "rank %d out of range for a channel of %d participants", rank, count);
+  B200_RETURN_IF_ERROR(ensure_nccl());
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  ncclUniqueId nid;
+  memcpy(&nid, id, sizeof nid);
+  auto* ch = new iree_hal_b200_channel_t();
+  ch->device = device;
+  ch->rank = rank;
+  ch->count = count;
+  iree_b200_status_t st = nccl_check(g_nccl.ncclCommInitRank(&ch->comm, count, nid, rank), "ncclCommInitRank");
+  if (st) {
+    delete ch;
+    return st;
+  }
+  *out_channel = ch;
+  return IREE_B200_STATUS_OK;
+}
+
+void iree_hal_b200_channel_release(iree_hal_b200_channel_t* channel) {
+  if (!channel) return;
+  if (channel->comm) g_nccl.ncclCommDestroy(channel->comm);
+  delete channel;
+}
+int32_t iree_hal_b200_channel_rank(const iree_hal_b200_channel_t* channel) { return channel ? channel->rank : 0; }
+int32_t iree_hal_b200_channel_count(const iree_hal_b200_channel_t* channel) { return channel ? channel->count : 0; }
+
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command_buffer_t* command_buffer,
+                                                           iree_hal_b200_channel_t* channel, int32_t element_type,
+                                                           const void* send_device_ptr, void* recv_device_ptr,
+                                                           size_t element_count) {
+  if (!command_buffer || !channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  int nccl_type;  // ncclDataType_t values: int8 0, int32 2, float16 6, float32 7, bfloat16 9
+  switch (element_type) {
+    case IREE_HAL_B200_ELEMENT_TYPE_I8: nccl_type = 0; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_I32: nccl_type = 2; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_F16: nccl_type = 6; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_F32: nccl_type = 7; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_BF16: nccl_type = 9; break;
+    default: return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unsupported collective element type %d", element_type);
+  }
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(command_buffer->device->context), "cuCtxSetCurrent");
+  // One collective per flush, inside a group like iree_hal_cuda_nccl_submit_batch (nccl_channel.c:542-585).
+  B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclGroupStart(), "ncclGroupStart"));
+  iree_b200_status_t st = nccl_check(g_nccl.ncclAllGather(send_device_ptr, recv_device_ptr, element_count, nccl_type,
+                                                          channel->comm, command_buffer->device->stream),
+                                     "ncclAllGather");
+  iree_b200_status_t st2 = nccl_check(g_nccl.ncclGroupEnd(), "ncclGroupEnd");
+  return st ? st : st2;
+}
+
+}  // extern "C"
+
+// ==========================================================================================
+// Operator level
+// ==========================================================================================
+namespace {
+
+constexpr uint32_t kGemmThreads = 256;
+constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
+
+struct EntryDecl {
+  const char* name;
+  uint32_t block[3];
+  uint32_t smem;
+};
+// Every export of the contraction cubin with the launch configuration the plugin records on
+// its hal.executable.export (workgroup_size, workgroup_local_memory).
+const EntryDecl kEntries[] = {
+    {"b200_matmul_f16_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_f16_f32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_bf16_bf16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_bf16_f32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_i8_i32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_i8_requant_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_encode_tensormaps", {32, 1, 1}, 0},
+    {"b200_matmul_generic_f16_f16", {16, 16, 1}, 0},
+    {"b200_matmul_generic_f16_f32", {16, 16, 1}, 0},
+    {"b200_matmul_generic_bf16_bf16", {16, 16, 1}, 0},
+    {"b200_matmul_generic_bf16_f32", {16, 16, 1}, 0},
+    {"b200_matmul_generic_i8_i32", {16, 16, 1}, 0},
+    {"b200_matmul_generic_i8_requant_f16", {16, 16, 1}, 0},
+};
+constexpr int kEntryCount = sizeof kEntries / sizeof kEntries[0];
+
+}  // namespace
+
+struct iree_b200_context_t {
+  iree_hal_b200_device_t* device = nullptr;
+  iree_hal_b200_executable_t* executable = nullptr;
+  iree_hal_b200_command_buffer_t* command_buffer = nullptr;
+  void* templates = nullptr;  // device copy of two template tensor maps per element size: [f16 A, f16 B, bf16.., i8..]
+};
+
+namespace {
+
+int elem_bytes_of(int kind) { return kind == IREE_B200_KIND_I8 ? 1 : 2; }
+
+const char* export_name(int kind, int epilogue, bool generic) {
+  if (kind == IREE_B200_KIND_F16 && epilogue == IREE_B200_EPILOGUE_CAST)
+    return generic ? "b200_matmul_generic_f16_f16" : "b200_matmul_f16_f16";
+  if (kind == IREE_B200_KIND_F16 && epilogue == IREE_B200_EPILOGUE_ACCUMULATOR)
+    return generic ? "b200_matmul_generic_f16_f32" : "b200_matmul_f16_f32";
+  if (kind == IREE_B200_KIND_BF16 && epilogue == IREE_B200_EPILOGUE_CAST)
+    return generic ? "b200_matmul_generic_bf16_bf16" : "b200_matmul_bf16_bf16";
+  if (kind == IREE_B200_KIND_BF16 && epilogue == IREE_B200_EPILOGUE_ACCUMULATOR)
+    return generic ? "b200_matmul_generic_bf16_f32" : "b200_matmul_bf16_f32";
+  if (kind == IREE_B200_KIND_I8 && epilogue == IREE_B200_EPILOGUE_ACCUMULATOR)
+    return generic ? "b200_matmul_generic_i8_i32" : "b200_matmul_i8_i32";
+  if (kind == IREE_B200_KIND_I8 && epilogue == IREE_B200_EPILOGUE_REQUANT_F16)
+    return generic ? "b200_matmul_generic_i8_requant_f16" : "b200_matmul_i8_requant_f16";
+  return nullptr;
+}
+
+iree_b200_status_t validate(const iree_b200_matmul_params_t* p) {
+  if (!p) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "params is NULL");
+  if (p->M < 0 || p->N < 0 || p->K < 0 || p->batch < 0)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "negative dimension");
+  if (p->rhs_layout != IREE_B200_RHS_KN && p->rhs_layout != IREE_B200_RHS_NK)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown rhs layout %d", p->rhs_layout);
+  if (!export_name(p->kind, p->epilogue, false))
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "no kernel for kind %d with epilogue %d", p->kind, p->epilogue);
+  return IREE_B200_STATUS_OK;
+}
+
+// The TMA path needs 16-byte aligned bases and row pitches.
+bool tma_eligible(const iree_b200_matmul_params_t* p, const void* lhs, const void* rhs) {
+  const int es = elem_bytes_of(p->kind);
+  if (p->flags & IREE_B200_FLAG_FORCE_GENERIC) return false;
+  if ((reinterpret_cast<uintptr_t>(lhs) % 16) || (reinterpret_cast<uintptr_t>(rhs) % 16)) return false;
+  if ((static_cast<int64_t>(p->K) * es) % 16) return false;
+  if (p->rhs_layout == IREE_B200_RHS_KN && (static_cast<int64_t>(p->N) * es) % 16) return false;
+  return true;
+}
+
+// Tile width: the widest tile that still gives every SM work, weighing wave quantisation
+// against the lower efficiency of narrow tiles.
+int choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_matmul_params_t* p) {
+  const int es = elem_bytes_of(p->kind);
+  const int chunk = (p->rhs_layout == IREE_B200_RHS_KN) ? 128 / es : 32;
+  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const int64_t tiles_m = (p->M + 127) / 128;
+  int best = 0;
+  double best_score = -1;
+  for (int bn = 256; bn >= 32; bn -= 32) {
+    if (bn % chunk) continue;
+    if (p->tile_n && bn != p->tile_n) continue;
+    const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn) * p->batch;
+    const int64_t waves = (tiles + sms - 1) / sms;
+    // Time model: every wave costs (fixed + bn) units; padding columns are wasted work.
+    const double cost = static_cast<double>(waves) * (48.0 + bn);
+    const double score = 1.0 / cost;
+    if (score > best_score * 1.0001) {
+      best_score = score;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+extern "C" {
+
+iree_b200_status_t iree_b200_context_create(int32_t device_ordinal, const char* cubin_path,
+                                            iree_b200_context_t** out_context) {
+  if (!out_context || !cubin_path) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  *out_context = nullptr;
+  FILE* f = fopen(cubin_path, "rb");
+  if (!f) return fail(IREE_B200_STATUS_NOT_FOUND, "cannot open cubin '%s'", cubin_path);
+  std::vector<uint8_t> image;
+  uint8_t chunk[65536];
+  size_t n;
+  while ((n = fread(chunk, 1, sizeof chunk, f)) > 0) image.insert(image.end(), chunk, chunk + n);
+  fclose(f);
+  // Wrap the cubin the way the compiler's CUDA target does for an external object.
+  const char* names[kEntryCount];
+  uint32_t blocks[3 * kEntryCount], smem[kEntryCount];
+  for (int i = 0; i < kEntryCount; ++i) {
+    names[i] = kEntries[i].name;
+    memcpy(&blocks[3 * i], kEntries[i].block, 12);
+    smem[i] = kEntries[i].smem;
+  }
+  size_t fb_size = 0;
+  B200_RETURN_IF_ERROR(iree_b200_executable_def_build(kEntryCount, names, blocks, smem, image.data(), image.size(),
+                                                      nullptr, 0, &fb_size));
+  std::vector<uint8_t> fb(fb_size);
+  B200_RETURN_IF_ERROR(iree_b200_executable_def_build(kEntryCount, names, blocks, smem, image.data(), image.size(),
+                                                      fb.data(), fb.size(), &fb_size));
+  auto* ctx = new iree_b200_context_t();
+  iree_b200_status_t st = iree_hal_b200_device_create(device_ordinal, &ctx->device);
+  if (!st) st = iree_hal_b200_executable_create(ctx->device, "PTXE", fb.data(), fb.size(), &ctx->executable);
+  if (!st) st = iree_hal_b200_command_buffer_create(ctx->device, &ctx->command_buffer);
+  if (st) {
+    iree_b200_context_release(ctx);
+    return st;
+  }
+  *out_context = ctx;
+  return IREE_B200_STATUS_OK;
+}
+
+void iree_b200_context_release(iree_b200_context_t* context) {
+  if (!context) return;
+  if (context->device) iree_hal_b200_device_synchronize(context->device);
+  if (context->templates) iree_hal_b200_buffer_free(context->device, context->templates);
+  iree_hal_b200_command_buffer_release(context->command_buffer);
+  iree_hal_b200_executable_release(context->executable);
+  iree_hal_b200_device_release(context->device);
+  delete context;
+}
+iree_hal_b200_device_t* iree_b200_context_device(iree_b200_context_t* c) { return c ? c->device : nullptr; }
+iree_hal_b200_executable_t* iree_b200_context_executable(iree_b200_context_t* c) { return c ? c->executable : nullptr; }
+iree_hal_b200_command_buffer_t* iree_b200_context_command_buffer(iree_b200_context_t* c) {
+  return c ? c->command_buffer : nullptr;
+}
+
+iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int32_t elem_bytes, int32_t is_bf16,
+                                               const void* device_ptr, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                               uint32_t box0, uint32_t box1, void* out_map) {
+  if (!context || !out_map) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  B200_RETURN_IF_ERROR(ensure_cuda());
+  if (elem_bytes != 1 && elem_bytes != 2) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "element size must be 1 or 2");
+  if (box0 * elem_bytes != 128 || box1 == 0 || box1 > 256)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "box must be 128 bytes wide and 1..256 rows");
+  if ((reinterpret_cast<uintptr_t>(device_ptr) % 16) || (static_cast<uint64_t>(dim0) * elem_bytes) % 16)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tensor base and row pitch must be multiples of 16 bytes");
+  CUtensorMap map;
+  const cuuint64_t dims[3] = {dim0, dim1, dim2};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(dim0) * elem_bytes,
+                                 static_cast<cuuint64_t>(dim0) * dim1 * elem_bytes};
+  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t estrides[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : is_bf16       ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, dt, 3, const_cast<void*>(device_ptr), dims, strides, box,
+                                                 estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                     "cuTensorMapEncodeTiled");
+  memcpy(out_map, &map, 128);
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                            const void* lhs, const void* rhs, void* workspace, int32_t* out_tile_n) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(validate(params));
+  if (out_tile_n) *out_tile_n = 0;
+  if (!params->M || !params->N || !params->batch) return IREE_B200_STATUS_OK;
+  if (!tma_eligible(params, lhs, rhs) || !params->K) return IREE_B200_STATUS_OK;  // generic kernel: nothing to prepare
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 128))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
+  const int es = elem_bytes_of(params->kind);
+  const int bn = choose_tile_n(context, params);
+  if (!bn) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tile_n %d is not usable for this layout", params->tile_n);
+  if (out_tile_n) *out_tile_n = bn;
+  const uint32_t bk = 128 / es;
+  const uint32_t M = params->M, N = params->N, K = params->K, B = params->batch;
+  if (params->flags & IREE_B200_FLAG_DEVICE_TENSORMAPS) {
+    // Templates: maps encoded once for a dummy tensor of the right element type.
+    if (!context->templates) {
+      uint8_t host[6 * 128];
+      B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(context->device, sizeof host, &context->templates));
+      for (int t = 0; t < 3; ++t) {
+        const int tes = t == 2 ? 1 : 2;
+        for (int i = 0; i < 2; ++i)
+          B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, tes, t == 1, context->templates, 128 / tes * 4, 256,
+                                                           1, 128 / tes, 64, host + (2 * t + i) * 128));
+      }
+      B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(context->device, host, context->templates, sizeof host));
+    }
+    const int t = params->kind == IREE_B200_KIND_I8 ? 2 : params->kind == IREE_B200_KIND_BF16 ? 1 : 0;
+    iree_hal_b200_descriptor_set_binding_t bindings[4] = {
+        {0, const_cast<void*>(lhs)},
+        {1, const_cast<void*>(rhs)},
+        {2, static_cast<uint8_t*>(context->templates) + 2 * t * 128},
+        {3, workspace}};
+    const int32_t constants[7] = {params->M, params->N, params->K, params->batch, params->rhs_layout, bn, es};
+    auto* cb = context->command_buffer;
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+    const int32_t ord = iree_hal_b200_executable_lookup(context->executable, "b200_encode_tensormaps");
+    return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 4, 7, 1, 1, 1);
+  }
+  uint8_t host[IREE_B200_WORKSPACE_BYTES];
+  memset(host, 0, sizeof host);
+  const int bf = params->kind == IREE_B200_KIND_BF16;
+  B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, lhs, K, M, B, bk, 128, host));
+  if (params->rhs_layout == IREE_B200_RHS_NK) {
+    B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, K, N, B, bk, bn, host + 128));
+  } else {
+    B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, N, K, B, bk, bk, host + 128));
+  }
+  // The source is pageable, so the driver has consumed it when this returns.
+  return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
+}
+
+iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                        const void* lhs, const void* rhs, void* out, const float* row_scale,
+                                        const float* col_scale, void* workspace, int32_t tile_n) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(validate(params));
+  if (!params->M || !params->N || !params->batch) return IREE_B200_STATUS_OK;  // empty result
+  if (!lhs || !rhs || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
+  const bool requant = params->epilogue == IREE_B200_EPILOGUE_REQUANT_F16;
+  if (requant && (!row_scale || !col_scale))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the requant epilogue needs row and column scales");
+  auto* cb = context->command_buffer;
+  const bool generic = !tma_eligible(params, lhs, rhs) || !params->K;
+  const int32_t ord = iree_hal_b200_executable_lookup(context->executable,
+                                                      export_name(params->kind, params->epilogue, generic));
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export missing from the executable");
+  if (generic) {
+    iree_hal_b200_descriptor_set_binding_t bindings[5] = {{0, const_cast<void*>(lhs)},
+                                                          {1, const_cast<void*>(rhs)},
+                                                          {2, out},
+                                                          {3, const_cast<float*>(row_scale)},
+                                                          {4, const_cast<float*>(col_scale)}};
+    const int32_t constants[4] = {params->M, params->N, params->K, params->rhs_layout};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, requant ? 5 : 3, bindings));
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+    return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, requant ? 5 : 3, 4,
+                                                 (params->N + 15) / 16, (params->M + 15) / 16, params->batch);
+  }
+  if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
+  if (tile_n <= 0) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "run() needs the tile_n that prepare() returned");
+  const int64_t tiles = static_cast<int64_t>((params->M + 127) / 128) * ((params->N + tile_n - 1) / tile_n) * params->batch;
+  const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
+  const uint32_t grid = static_cast<uint32_t>(tiles < sms ? tiles : sms);
+  const int32_t constants[6] = {params->M, params->N, params->K, params->batch, params->rhs_layout, tile_n};
+  if (requant) {
+    iree_hal_b200_descriptor_set_binding_t bindings[4] = {
+        {0, out}, {1, const_cast<float*>(row_scale)}, {2, const_cast<float*>(col_scale)}, {3, workspace}};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+  } else {
+    iree_hal_b200_descriptor_set_binding_t bindings[2] = {{0, out}, {1, workspace}};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 2, bindings));
+  }
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, requant ? 4 : 2, 6, grid, 1, 1);
+}
+
+iree_b200_status_t iree_b200_matmul(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                    const void* lhs, const void* rhs, void* out, const float* row_scale,
+                                    const float* col_scale, void* workspace) {
+  int32_t tile_n = 0;
+  B200_RETURN_IF_ERROR(iree_b200_matmul_prepare(context, params, lhs, rhs, workspace, &tile_n));
+  return iree_b200_matmul_run(context, params, lhs, rhs, out, row_scale, col_scale, workspace, tile_n);
+}
+
+iree_b200_status_t iree_b200_workspace_status(iree_b200_context_t* context, const void* workspace) {
+  if (!context || !workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  uint32_t status[2] = {0, 0};
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(context->device, static_cast<const uint8_t*>(workspace) + 384,
+                                                  status, sizeof status));
+  B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
+  switch (status[0]) {
+    case 0: return IREE_B200_STATUS_OK;
+    case 5: return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "kernel rejected its arguments (shape / alignment)");
+    default:
+      return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[0], status[1]);
+  }
+}
+
+iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                         const void* lhs, const void* rhs, void* out, const float* row_scale,
+                                         const float* col_scale) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(validate(params));
+  const size_t es = elem_bytes_of(params->kind);
+  const size_t os = params->epilogue == IREE_B200_EPILOGUE_ACCUMULATOR ? 4 : 2;
+  const size_t a_bytes = static_cast<size_t>(params->batch) * params->M * params->K * es;
+  const size_t b_bytes = static_cast<size_t>(params->batch) * params->K * params->N * es;
+  const size_t c_bytes = static_cast<size_t>(params->batch) * params->M * params->N * os;
+  if (!c_bytes) return IREE_B200_STATUS_OK;
+  const bool requant = params->epilogue == IREE_B200_EPILOGUE_REQUANT_F16;
+  auto* d = context->device;
+  void *da = nullptr, *db = nullptr, *dc = nullptr, *ws = nullptr, *drs = nullptr, *dcs = nullptr;
+  iree_b200_status_t st = iree_hal_b200_buffer_allocate(d, a_bytes, &da);
+  if (!st) st = iree_hal_b200_buffer_allocate(d, b_bytes, &db);
+  if (!st) st = iree_hal_b200_buffer_allocate(d, c_bytes, &dc);
+  if (!st) st = iree_hal_b200_buffer_allocate(d, IREE_B200_WORKSPACE_BYTES, &ws);
+  if (!st && requant) st = iree_hal_b200_buffer_allocate(d, sizeof(float) * params->M, &drs);
+  if (!st && requant) st = iree_hal_b200_buffer_allocate(d, sizeof(float) * params->N, &dcs);
+  if (!st) st = iree_hal_b200_transfer_h2d(d, lhs, da, a_bytes);
+  if (!st) st = iree_hal_b200_transfer_h2d(d, rhs, db, b_bytes);
+  if (!st && requant) st = iree_hal_b200_transfer_h2d(d, row_scale, drs, sizeof(float) * params->M);
+  if (!st && requant) st = iree_hal_b200_transfer_h2d(d, col_scale, dcs, sizeof(float) * params->N);
+  if (!st) st = iree_hal_b200_fill_buffer(d, ws, IREE_B200_WORKSPACE_BYTES, 0);
+  if (!st)
+    st = iree_b200_matmul(context, params, da, db, dc, static_cast<float*>(drs), static_cast<float*>(dcs), ws);
+  if (!st) st = iree_hal_b200_transfer_d2h(d, dc, out, c_bytes);
+  if (!st) st = iree_b200_workspace_status(context, ws);
+  std::string keep = g_last_error;
+  iree_hal_b200_device_synchronize(d);
+  iree_hal_b200_buffer_free(d, da);
+  iree_hal_b200_buffer_free(d, db);
+  iree_hal_b200_buffer_free(d, dc);
+  iree_hal_b200_buffer_free(d, ws);
+  iree_hal_b200_buffer_free(d, drs);
+  iree_hal_b200_buffer_free(d, dcs);
+  if (st) g_last_error = keep;
+  return st;
+}
+
+}  // extern "C"

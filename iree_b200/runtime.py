@@ -1,0 +1,269 @@
+"""ctypes host side of ``libiree_b200.so`` (declared in ``include/iree_b200.h``).
+
+Mirrors the reference's runtime surface for one dispatch: a context owns the device, the
+loaded executable (an ``ExecutableDef`` flatbuffer wrapped around the sm_100a cubin) and a
+stream command buffer; operators push constants, bind buffers and dispatch. Failures raise
+:class:`IreeB200Error` carrying the reference's status code name.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+KIND_F16, KIND_BF16, KIND_I8 = 0, 1, 2
+EPILOGUE_CAST, EPILOGUE_ACCUMULATOR, EPILOGUE_REQUANT_F16 = 0, 1, 2
+RHS_KN, RHS_NK = 0, 1
+FLAG_FORCE_GENERIC, FLAG_DEVICE_TENSORMAPS = 1, 2
+WORKSPACE_BYTES = 512
+
+_STATUS_NAMES = {0: "OK", 1: "CANCELLED", 2: "UNKNOWN", 3: "INVALID_ARGUMENT", 4: "DEADLINE_EXCEEDED",
+                 5: "NOT_FOUND", 6: "ALREADY_EXISTS", 7: "PERMISSION_DENIED", 8: "RESOURCE_EXHAUSTED",
+                 9: "FAILED_PRECONDITION", 10: "ABORTED", 11: "OUT_OF_RANGE", 12: "UNIMPLEMENTED",
+                 13: "INTERNAL", 14: "UNAVAILABLE", 15: "DATA_LOSS", 16: "UNAUTHENTICATED"}
+
+
+class IreeB200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.code_name = _STATUS_NAMES.get(code, str(code))
+        super().__init__("%s: %s" % (self.code_name, message))
+
+
+class MatmulParams(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("epilogue", C.c_int32), ("M", C.c_int32), ("N", C.c_int32),
+                ("K", C.c_int32), ("batch", C.c_int32), ("rhs_layout", C.c_int32), ("tile_n", C.c_int32),
+                ("flags", C.c_int32)]
+
+
+class W4A16Params(C.Structure):
+    _fields_ = [("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("group_size", C.c_int32),
+                ("n_out", C.c_int32), ("n_offset", C.c_int32), ("variant", C.c_int32), ("flags", C.c_int32)]
+
+
+class _Binding(C.Structure):
+    _fields_ = [("binding", C.c_uint32), ("device_ptr", C.c_void_p)]
+
+
+def library_path() -> str:
+    return os.path.join(_HERE, "libiree_b200.so")
+
+
+def cubin_path() -> str:
+    return os.path.join(_HERE, "csrc", "b200_contraction.cubin")
+
+
+_lib = None
+
+
+def library():
+    """Loads libiree_b200.so. Raises if it was not built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise IreeB200Error(14, "libiree_b200.so is not built (run `python -m iree_b200.build`)")
+        lib = C.CDLL(path)
+        lib.iree_b200_last_error.restype = C.c_char_p
+        lib.iree_hal_b200_device_stream.restype = C.c_void_p
+        lib.iree_b200_context_device.restype = C.c_void_p
+        lib.iree_b200_context_executable.restype = C.c_void_p
+        lib.iree_b200_context_command_buffer.restype = C.c_void_p
+        lib.iree_hal_b200_command_buffer_launch_count.restype = C.c_uint64
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    return library().iree_b200_last_error().decode()
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise IreeB200Error(code, last_error())
+
+
+def _vp(x) -> C.c_void_p:
+    if x is None:
+        return C.c_void_p(0)
+    if isinstance(x, DeviceBuffer):
+        return C.c_void_p(x.ptr)
+    if isinstance(x, int):
+        return C.c_void_p(x)
+    if isinstance(x, np.ndarray):
+        return C.c_void_p(x.ctypes.data)
+    if hasattr(x, "data_ptr"):  # a torch tensor on this device
+        return C.c_void_p(x.data_ptr())
+    raise TypeError(type(x))
+
+
+class DeviceBuffer:
+    """A raw device allocation (what a HAL buffer resolves to before a launch)."""
+
+    def __init__(self, ctx: "Context", nbytes: int):
+        self.ctx, self.nbytes = ctx, int(nbytes)
+        p = C.c_void_p()
+        check(library().iree_hal_b200_buffer_allocate(ctx.device, C.c_size_t(self.nbytes), C.byref(p)))
+        self.ptr = p.value or 0
+
+    def upload(self, host: np.ndarray) -> "DeviceBuffer":
+        host = np.ascontiguousarray(host)
+        assert host.nbytes <= self.nbytes
+        check(library().iree_hal_b200_transfer_h2d(self.ctx.device, _vp(host), C.c_void_p(self.ptr),
+                                                   C.c_size_t(host.nbytes)))
+        self.ctx.synchronize()  # the pageable source may be released by the caller
+        return self
+
+    def download(self, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        assert out.nbytes <= self.nbytes
+        check(library().iree_hal_b200_transfer_d2h(self.ctx.device, C.c_void_p(self.ptr), _vp(out),
+                                                   C.c_size_t(out.nbytes)))
+        self.ctx.synchronize()
+        return out
+
+    def fill(self, byte: int) -> "DeviceBuffer":
+        check(library().iree_hal_b200_fill_buffer(self.ctx.device, C.c_void_p(self.ptr), C.c_size_t(self.nbytes),
+                                                  C.c_uint8(byte)))
+        return self
+
+    def free(self) -> None:
+        if self.ptr:
+            library().iree_hal_b200_buffer_free(self.ctx.device, C.c_void_p(self.ptr))
+            self.ptr = 0
+
+
+class Context:
+    """Device + loaded contraction executable + command buffer (``iree_b200_context_t``)."""
+
+    def __init__(self, device_ordinal: int = 0, cubin: Optional[str] = None):
+        lib = library()
+        cubin = cubin or cubin_path()
+        h = C.c_void_p()
+        check(lib.iree_b200_context_create(C.c_int32(device_ordinal), cubin.encode(), C.byref(h)))
+        self.handle = h
+        self.device = C.c_void_p(lib.iree_b200_context_device(h))
+        self.executable = C.c_void_p(lib.iree_b200_context_executable(h))
+        self.command_buffer = C.c_void_p(lib.iree_b200_context_command_buffer(h))
+        name = C.create_string_buffer(128)
+        sm, cc, smem = C.c_int32(), C.c_int32(), C.c_int32()
+        check(lib.iree_hal_b200_device_query(self.device, name, C.c_size_t(128), C.byref(sm), C.byref(cc),
+                                             C.byref(smem)))
+        self.device_name, self.sm_count, self.compute_capability = name.value.decode(), sm.value, cc.value
+        self.max_shared_memory = smem.value
+
+    # -- plumbing ------------------------------------------------------------------------
+    def close(self) -> None:
+        if self.handle:
+            library().iree_b200_context_release(self.handle)
+            self.handle = None
+
+    def synchronize(self) -> None:
+        check(library().iree_hal_b200_device_synchronize(self.device))
+
+    @property
+    def stream(self) -> int:
+        return library().iree_hal_b200_device_stream(self.device) or 0
+
+    @property
+    def launch_count(self) -> int:
+        return int(library().iree_hal_b200_command_buffer_launch_count(self.command_buffer))
+
+    def alloc(self, nbytes: int) -> DeviceBuffer:
+        return DeviceBuffer(self, nbytes)
+
+    def to_device(self, host: np.ndarray) -> DeviceBuffer:
+        host = np.ascontiguousarray(host)
+        return DeviceBuffer(self, max(host.nbytes, 1)).upload(host)
+
+    def workspace(self) -> DeviceBuffer:
+        return DeviceBuffer(self, WORKSPACE_BYTES).fill(0)
+
+    def workspace_status(self, ws) -> None:
+        check(library().iree_b200_workspace_status(self.handle, _vp(ws)))
+
+    # -- raw HAL-level dispatch ------------------------------------------------------------
+    def lookup(self, entry_name: str) -> int:
+        return library().iree_hal_b200_executable_lookup(self.executable, entry_name.encode())
+
+    def dispatch(self, entry_name: str, bindings, constants, grid) -> None:
+        """push_descriptor_set + push_constants + dispatch, as a compiled host program would."""
+        lib = library()
+        ordinal = self.lookup(entry_name)
+        if ordinal < 0:
+            raise IreeB200Error(5, "no export named " + entry_name)
+        arr = (_Binding * len(bindings))()
+        for i, b in enumerate(bindings):
+            arr[i].binding, arr[i].device_ptr = i, _vp(b).value
+        check(lib.iree_hal_b200_command_buffer_push_descriptor_set(self.command_buffer, C.c_uint32(0),
+                                                                   C.c_size_t(len(bindings)), arr))
+        consts = np.asarray(constants, dtype=np.int32)
+        check(lib.iree_hal_b200_command_buffer_push_constants(self.command_buffer, C.c_size_t(0), _vp(consts),
+                                                              C.c_size_t(consts.nbytes)))
+        gx, gy, gz = grid
+        check(lib.iree_hal_b200_command_buffer_dispatch(self.command_buffer, self.executable, C.c_int32(ordinal),
+                                                        C.c_uint32(len(bindings)), C.c_uint32(len(constants)),
+                                                        C.c_uint32(gx), C.c_uint32(gy), C.c_uint32(gz)))
+
+    # -- operators ---------------------------------------------------------------------------
+    def matmul_prepare(self, params: MatmulParams, lhs, rhs, ws) -> int:
+        tile_n = C.c_int32()
+        check(library().iree_b200_matmul_prepare(self.handle, C.byref(params), _vp(lhs), _vp(rhs), _vp(ws),
+                                                 C.byref(tile_n)))
+        return tile_n.value
+
+    def matmul_run(self, params: MatmulParams, lhs, rhs, out, ws, tile_n: int, row_scale=None,
+                   col_scale=None) -> None:
+        check(library().iree_b200_matmul_run(self.handle, C.byref(params), _vp(lhs), _vp(rhs), _vp(out),
+                                             _vp(row_scale), _vp(col_scale), _vp(ws), C.c_int32(tile_n)))
+
+    def matmul(self, params: MatmulParams, lhs, rhs, out, ws, row_scale=None, col_scale=None) -> None:
+        check(library().iree_b200_matmul(self.handle, C.byref(params), _vp(lhs), _vp(rhs), _vp(out),
+                                         _vp(row_scale), _vp(col_scale), _vp(ws)))
+
+    def matmul_host(self, params: MatmulParams, lhs: np.ndarray, rhs: np.ndarray, out: np.ndarray,
+                    row_scale=None, col_scale=None) -> None:
+        check(library().iree_b200_matmul_host(self.handle, C.byref(params), _vp(lhs), _vp(rhs), _vp(out),
+                                              _vp(row_scale), _vp(col_scale)))
+
+    def encode_tensor_map(self, elem_bytes, is_bf16, ptr, dim0, dim1, dim2, box0, box1) -> bytes:
+        out = C.create_string_buffer(128)
+        check(library().iree_b200_encode_tensor_map(self.handle, C.c_int32(elem_bytes), C.c_int32(int(is_bf16)),
+                                                    _vp(ptr), C.c_uint32(dim0), C.c_uint32(dim1), C.c_uint32(dim2),
+                                                    C.c_uint32(box0), C.c_uint32(box1), out))
+        return out.raw
+
+
+_IN_DTYPE = {KIND_F16: np.float16, KIND_BF16: np.uint16, KIND_I8: np.int8}
+
+
+def out_dtype(kind: int, epilogue: int):
+    if epilogue == EPILOGUE_ACCUMULATOR:
+        return np.int32 if kind == KIND_I8 else np.float32
+    return np.uint16 if (kind == KIND_BF16 and epilogue == EPILOGUE_CAST) else np.float16
+
+
+def matmul_numpy(ctx: Context, kind: int, epilogue: int, lhs: np.ndarray, rhs: np.ndarray, rhs_layout: int = RHS_KN,
+                 row_scale=None, col_scale=None, tile_n: int = 0, flags: int = 0) -> np.ndarray:
+    """Convenience for tests: host arrays in, host array out, through iree_b200_matmul_host.
+
+    lhs is [M,K] or [B,M,K]; rhs is [K,N] / [B,K,N] (RHS_KN) or [N,K] / [B,N,K] (RHS_NK).
+    bf16 travels as raw uint16 bit patterns.
+    """
+    lhs = np.ascontiguousarray(lhs)
+    rhs = np.ascontiguousarray(rhs)
+    assert lhs.dtype == _IN_DTYPE[kind] and rhs.dtype == _IN_DTYPE[kind], (lhs.dtype, rhs.dtype)
+    batched = lhs.ndim == 3
+    B = lhs.shape[0] if batched else 1
+    M, K = lhs.shape[-2:]
+    N = rhs.shape[-1] if rhs_layout == RHS_KN else rhs.shape[-2]
+    p = MatmulParams(kind, epilogue, M, N, K, B, rhs_layout, tile_n, flags)
+    out = np.empty((B, M, N) if batched else (M, N), out_dtype(kind, epilogue))
+    rs = None if row_scale is None else np.ascontiguousarray(row_scale, np.float32)
+    cs = None if col_scale is None else np.ascontiguousarray(col_scale, np.float32)
+    ctx.matmul_host(p, lhs, rhs, out, rs, cs)
+    return out

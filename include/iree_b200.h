@@ -79,6 +79,16 @@ iree_b200_status_t iree_hal_b200_device_synchronize(iree_hal_b200_device_t* devi
 /* The dispatch CUstream, for callers that interleave their own work (graph capture, NCCL). */
 void* iree_hal_b200_device_stream(iree_hal_b200_device_t* device);
 
+/* ---- timing events --------------------------------------------------------------------------
+ * CUevent pairs recorded on the dispatch stream, what the driver's tracing context wraps around
+ * each dispatch (runtime/src/iree/hal/drivers/cuda/tracing.h; stream_command_buffer.c:519-524).
+ * elapsed_ms waits for `end`. */
+iree_b200_status_t iree_hal_b200_event_create(iree_hal_b200_device_t* device, void** out_event);
+void iree_hal_b200_event_release(iree_hal_b200_device_t* device, void* event);
+iree_b200_status_t iree_hal_b200_event_record(iree_hal_b200_device_t* device, void* event);
+iree_b200_status_t iree_hal_b200_event_elapsed_ms(iree_hal_b200_device_t* device, void* start, void* end,
+                                                  float* out_ms);
+
 /* ---- buffers ------------------------------------------------------------------------------
  * iree_hal_allocator_allocate_buffer / iree_hal_device_transfer_h2d / _d2h
  * (runtime/src/iree/hal/drivers/cuda/cuda_allocator.c; hal/device.h). Buffers are raw device

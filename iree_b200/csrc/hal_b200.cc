@@ -72,6 +72,11 @@ struct CudaSymbols {
   CU_FN(cuFuncSetAttribute, CUfunction, CUfunction_attribute, int)
   CU_FN(cuLaunchKernel, CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
         void**, void**)
+  CU_FN(cuEventCreate, CUevent*, unsigned)
+  CU_FN(cuEventDestroy, CUevent)
+  CU_FN(cuEventRecord, CUevent, CUstream)
+  CU_FN(cuEventSynchronize, CUevent)
+  CU_FN(cuEventElapsedTime, float*, CUevent, CUevent)
   CU_FN(cuGetErrorName, CUresult, const char**)
   CU_FN(cuGetErrorString, CUresult, const char**)
   CU_FN(cuTensorMapEncodeTiled, CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -125,6 +130,11 @@ iree_b200_status_t ensure_cuda() {
       LOAD(cuModuleGetFunction, "cuModuleGetFunction")
       LOAD(cuFuncSetAttribute, "cuFuncSetAttribute")
       LOAD(cuLaunchKernel, "cuLaunchKernel")
+      LOAD(cuEventCreate, "cuEventCreate")
+      LOAD(cuEventDestroy, "cuEventDestroy_v2")
+      LOAD(cuEventRecord, "cuEventRecord")
+      LOAD(cuEventSynchronize, "cuEventSynchronize")
+      LOAD(cuEventElapsedTime, "cuEventElapsedTime")
       LOAD(cuGetErrorName, "cuGetErrorName")
       LOAD(cuGetErrorString, "cuGetErrorString")
       LOAD(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
@@ -452,6 +462,32 @@ iree_b200_status_t iree_hal_b200_device_synchronize(iree_hal_b200_device_t* devi
 }
 
 void* iree_hal_b200_device_stream(iree_hal_b200_device_t* device) { return device ? device->stream : nullptr; }
+
+// ---- events ----------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_event_create(iree_hal_b200_device_t* device, void** out_event) {
+  if (!device || !out_event) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CUevent e = nullptr;
+  CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&e, CU_EVENT_DEFAULT), "cuEventCreate");
+  *out_event = e;
+  return IREE_B200_STATUS_OK;
+}
+void iree_hal_b200_event_release(iree_hal_b200_device_t* device, void* event) {
+  if (device && event) g_cu.cuEventDestroy(static_cast<CUevent>(event));
+}
+iree_b200_status_t iree_hal_b200_event_record(iree_hal_b200_device_t* device, void* event) {
+  if (!device || !event) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  CU_RETURN_IF_ERROR(g_cu.cuEventRecord(static_cast<CUevent>(event), device->stream), "cuEventRecord");
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_event_elapsed_ms(iree_hal_b200_device_t* device, void* start, void* end,
+                                                  float* out_ms) {
+  if (!device || !start || !end || !out_ms) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  CU_RETURN_IF_ERROR(g_cu.cuEventSynchronize(static_cast<CUevent>(end)), "cuEventSynchronize");
+  CU_RETURN_IF_ERROR(g_cu.cuEventElapsedTime(out_ms, static_cast<CUevent>(start), static_cast<CUevent>(end)),
+                     "cuEventElapsedTime");
+  return IREE_B200_STATUS_OK;
+}
 
 // ---- buffers ---------------------------------------------------------------------------------
 iree_b200_status_t iree_hal_b200_buffer_allocate(iree_hal_b200_device_t* device, size_t byte_length,
@@ -812,6 +848,7 @@ const EntryDecl kEntries[] = {
     {"b200_matmul_i8_i32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_matmul_i8_requant_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_encode_tensormaps", {32, 1, 1}, 0},
+    {"b200_selftest_wait_timeout", {32, 1, 1}, 0},
     {"b200_matmul_generic_f16_f16", {16, 16, 1}, 0},
     {"b200_matmul_generic_f16_f32", {16, 16, 1}, 0},
     {"b200_matmul_generic_bf16_bf16", {16, 16, 1}, 0},

@@ -54,7 +54,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Waits for the phase with the given parity to complete. Gives up after ~2 s of wall time or
 // as soon as another role has raised the CTA-wide abort flag; returns false then.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint64_t limit_ns = kDefaultWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t polls = 0;
@@ -62,7 +64,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > 2000000000ull) return false;
+      if (global_timer_ns() - t0 > limit_ns) return false;
     }
   }
 }

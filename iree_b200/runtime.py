@@ -137,6 +137,25 @@ class DeviceBuffer:
             self.ptr = 0
 
 
+class Event:
+    """A CUevent on the context's dispatch stream."""
+
+    def __init__(self, ctx: "Context"):
+        self.ctx = ctx
+        h = C.c_void_p()
+        check(library().iree_hal_b200_event_create(ctx.device, C.byref(h)))
+        self.handle = h
+
+    def record(self) -> "Event":
+        check(library().iree_hal_b200_event_record(self.ctx.device, self.handle))
+        return self
+
+    def elapsed_ms(self, end: "Event") -> float:
+        ms = C.c_float()
+        check(library().iree_hal_b200_event_elapsed_ms(self.ctx.device, self.handle, end.handle, C.byref(ms)))
+        return float(ms.value)
+
+
 class Context:
     """Device + loaded contraction executable + command buffer (``iree_b200_context_t``)."""
 
@@ -172,6 +191,9 @@ class Context:
     @property
     def launch_count(self) -> int:
         return int(library().iree_hal_b200_command_buffer_launch_count(self.command_buffer))
+
+    def event(self) -> "Event":
+        return Event(self)
 
     def alloc(self, nbytes: int) -> DeviceBuffer:
         return DeviceBuffer(self, nbytes)

@@ -265,6 +265,46 @@ iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int
                                                const void* device_ptr, uint32_t dim0, uint32_t dim1, uint32_t dim2,
                                                uint32_t box0, uint32_t box1, void* out_map);
 
+/* ---- fused int4 dequant + matmul (W4A16) -------------------------------------------------------
+ * The dispatch that dispatch formation builds by cloning the dequantisation generic into its
+ * consumer contraction (compiler/src/iree/compiler/Dialect/Flow/Transforms/RegionOpUtils.cpp:530-610,
+ * pinned by Dialect/Flow/Transforms/test/pipeline_tests.mlir:53-99): group-wise scaled int4
+ * weights [N, K/2] bytes (element 2i in the low nibble of byte i,
+ * runtime/src/iree/builtins/ukernel/mmt4d_tile_generic.c:35-44), f16 scales [N, K/group], f16
+ * activations [M, K], f16 result. The result is written at out[m * ldo + n_offset + n], so a rank
+ * that owns a slice of N writes into the full-width buffer (ldo = N, n_offset = 0 otherwise). */
+enum {
+  IREE_B200_W4A16_AUTO = 0,
+  IREE_B200_W4A16_DECODE = 1,  /* M <= 16, N % 16 == 0, K % 256 == 0, group 128: weight streaming */
+  IREE_B200_W4A16_GEMM = 2,    /* group 128, K % 128 == 0: tcgen05 with in-kernel dequantisation */
+  IREE_B200_W4A16_GENERIC = 3, /* anything else */
+};
+typedef struct {
+  int32_t M, N, K;
+  int32_t group_size;
+  int32_t ldo;       /* output row pitch in elements */
+  int32_t n_offset;  /* first output column */
+  int32_t variant;   /* IREE_B200_W4A16_* */
+  int32_t tile_n;    /* 0 = choose (tensor-core kernel only) */
+} iree_b200_w4a16_params_t;
+/* Device workspace the dispatch needs for an N-column weight matrix: tensor maps, status words
+ * and the f32 scratch of the decode kernel's split-K reduction. It must be zero-filled once
+ * after allocation; the kernels leave the scratch zeroed. One workspace serves one dispatch in
+ * flight. */
+size_t iree_b200_w4a16_workspace_bytes(int32_t N);
+iree_b200_status_t iree_b200_w4a16(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                   const void* a, const void* wq, const void* scales, void* out, void* workspace);
+iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                           const void* a, const void* wq, const void* scales, const void* out,
+                                           void* workspace, int32_t* out_variant, int32_t* out_tile_n);
+iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                       const void* a, const void* wq, const void* scales, void* out, void* workspace,
+                                       int32_t variant, int32_t tile_n);
+/* Host-buffer form (copies in, runs, copies out, waits). With ldo != N the existing contents of
+ * `out` are uploaded first so that columns outside the slice survive. */
+iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                        const void* a, const void* wq, const void* scales, void* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -832,6 +832,7 @@ namespace {
 
 constexpr uint32_t kGemmThreads = 256;
 constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
+constexpr uint32_t kW4SmemBytes = 1024 + 3 * (128 * 128 + 256 * 128) + 2 * (256 * 64) + 256;
 
 struct EntryDecl {
   const char* name;
@@ -855,6 +856,10 @@ const EntryDecl kEntries[] = {
     {"b200_matmul_generic_bf16_f32", {16, 16, 1}, 0},
     {"b200_matmul_generic_i8_i32", {16, 16, 1}, 0},
     {"b200_matmul_generic_i8_requant_f16", {16, 16, 1}, 0},
+    {"b200_w4a16_decode_m8", {512, 1, 1}, 0},
+    {"b200_w4a16_decode_m16", {512, 1, 1}, 0},
+    {"b200_w4a16_gemm", {512, 1, 1}, kW4SmemBytes},
+    {"b200_w4a16_generic", {256, 1, 1}, 0},
 };
 constexpr int kEntryCount = sizeof kEntries / sizeof kEntries[0];
 
@@ -865,6 +870,11 @@ struct iree_b200_context_t {
   iree_hal_b200_executable_t* executable = nullptr;
   iree_hal_b200_command_buffer_t* command_buffer = nullptr;
   void* templates = nullptr;  // device copy of two template tensor maps per element size: [f16 A, f16 B, bf16.., i8..]
+  // Grow-only device staging area for the host-buffer entry points, so that repeated calls do
+  // not pay for cuMemAlloc / cuMemFree.
+  void* arena = nullptr;
+  size_t arena_size = 0;
+  bool arena_w4_clean = true;
 };
 
 namespace {
@@ -978,6 +988,7 @@ void iree_b200_context_release(iree_b200_context_t* context) {
   if (!context) return;
   if (context->device) iree_hal_b200_device_synchronize(context->device);
   if (context->templates) iree_hal_b200_buffer_free(context->device, context->templates);
+  if (context->arena) iree_hal_b200_buffer_free(context->device, context->arena);
   iree_hal_b200_command_buffer_release(context->command_buffer);
   iree_hal_b200_executable_release(context->executable);
   iree_hal_b200_device_release(context->device);
@@ -989,14 +1000,13 @@ iree_hal_b200_command_buffer_t* iree_b200_context_command_buffer(iree_b200_conte
   return c ? c->command_buffer : nullptr;
 }
 
-iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int32_t elem_bytes, int32_t is_bf16,
-                                               const void* device_ptr, uint32_t dim0, uint32_t dim1, uint32_t dim2,
-                                               uint32_t box0, uint32_t box1, void* out_map) {
-  if (!context || !out_map) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+// Rank-3 row-major tensor [dim2, dim1, dim0]; the box is box0 x box1 x 1 elements.
+static iree_b200_status_t encode_map(CUtensorMapDataType dt, int elem_bytes, CUtensorMapSwizzle swizzle,
+                                     uint32_t swizzle_bytes, const void* device_ptr, uint32_t dim0, uint32_t dim1,
+                                     uint32_t dim2, uint32_t box0, uint32_t box1, void* out_map) {
   B200_RETURN_IF_ERROR(ensure_cuda());
-  if (elem_bytes != 1 && elem_bytes != 2) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "element size must be 1 or 2");
-  if (box0 * elem_bytes != 128 || box1 == 0 || box1 > 256)
-    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "box must be 128 bytes wide and 1..256 rows");
+  if (box0 * elem_bytes != swizzle_bytes || box1 == 0 || box1 > 256)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "box must be %u bytes wide and 1..256 rows", swizzle_bytes);
   if ((reinterpret_cast<uintptr_t>(device_ptr) % 16) || (static_cast<uint64_t>(dim0) * elem_bytes) % 16)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tensor base and row pitch must be multiples of 16 bytes");
   CUtensorMap map;
@@ -1005,15 +1015,23 @@ iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int
                                  static_cast<cuuint64_t>(dim0) * dim1 * elem_bytes};
   const cuuint32_t box[3] = {box0, box1, 1};
   const cuuint32_t estrides[3] = {1, 1, 1};
-  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                 : is_bf16       ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, dt, 3, const_cast<void*>(device_ptr), dims, strides, box,
-                                                 estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                 estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
                      "cuTensorMapEncodeTiled");
   memcpy(out_map, &map, 128);
   return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int32_t elem_bytes, int32_t is_bf16,
+                                               const void* device_ptr, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                               uint32_t box0, uint32_t box1, void* out_map) {
+  if (!context || !out_map) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (elem_bytes != 1 && elem_bytes != 2) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "element size must be 1 or 2");
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : is_bf16       ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return encode_map(dt, elem_bytes, CU_TENSOR_MAP_SWIZZLE_128B, 128, device_ptr, dim0, dim1, dim2, box0, box1, out_map);
 }
 
 iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
@@ -1150,32 +1168,211 @@ iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const ire
   if (!c_bytes) return IREE_B200_STATUS_OK;
   const bool requant = params->epilogue == IREE_B200_EPILOGUE_REQUANT_F16;
   auto* d = context->device;
-  void *da = nullptr, *db = nullptr, *dc = nullptr, *ws = nullptr, *drs = nullptr, *dcs = nullptr;
-  iree_b200_status_t st = iree_hal_b200_buffer_allocate(d, a_bytes, &da);
-  if (!st) st = iree_hal_b200_buffer_allocate(d, b_bytes, &db);
-  if (!st) st = iree_hal_b200_buffer_allocate(d, c_bytes, &dc);
-  if (!st) st = iree_hal_b200_buffer_allocate(d, IREE_B200_WORKSPACE_BYTES, &ws);
-  if (!st && requant) st = iree_hal_b200_buffer_allocate(d, sizeof(float) * params->M, &drs);
-  if (!st && requant) st = iree_hal_b200_buffer_allocate(d, sizeof(float) * params->N, &dcs);
-  if (!st) st = iree_hal_b200_transfer_h2d(d, lhs, da, a_bytes);
-  if (!st) st = iree_hal_b200_transfer_h2d(d, rhs, db, b_bytes);
-  if (!st && requant) st = iree_hal_b200_transfer_h2d(d, row_scale, drs, sizeof(float) * params->M);
-  if (!st && requant) st = iree_hal_b200_transfer_h2d(d, col_scale, dcs, sizeof(float) * params->N);
-  if (!st) st = iree_hal_b200_fill_buffer(d, ws, IREE_B200_WORKSPACE_BYTES, 0);
-  if (!st)
-    st = iree_b200_matmul(context, params, da, db, dc, static_cast<float*>(drs), static_cast<float*>(dcs), ws);
-  if (!st) st = iree_hal_b200_transfer_d2h(d, dc, out, c_bytes);
-  if (!st) st = iree_b200_workspace_status(context, ws);
-  std::string keep = g_last_error;
-  iree_hal_b200_device_synchronize(d);
-  iree_hal_b200_buffer_free(d, da);
-  iree_hal_b200_buffer_free(d, db);
-  iree_hal_b200_buffer_free(d, dc);
-  iree_hal_b200_buffer_free(d, ws);
-  iree_hal_b200_buffer_free(d, drs);
-  iree_hal_b200_buffer_free(d, dcs);
-  if (st) g_last_error = keep;
-  return st;
+  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  const size_t rs_bytes = requant ? sizeof(float) * params->M : 0, cs_bytes = requant ? sizeof(float) * params->N : 0;
+  const size_t need = up(IREE_B200_WORKSPACE_BYTES) + up(a_bytes) + up(b_bytes) + up(c_bytes) + up(rs_bytes) + up(cs_bytes);
+  if (need > context->arena_size) {
+    B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
+    if (context->arena) B200_RETURN_IF_ERROR(iree_hal_b200_buffer_free(d, context->arena));
+    context->arena = nullptr;
+    context->arena_size = 0;
+    B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(d, need, &context->arena));
+    context->arena_size = need;
+  }
+  uint8_t* base = static_cast<uint8_t*>(context->arena);
+  void* ws = base;
+  void* da = base + up(IREE_B200_WORKSPACE_BYTES);
+  void* db = static_cast<uint8_t*>(da) + up(a_bytes);
+  void* dc = static_cast<uint8_t*>(db) + up(b_bytes);
+  float* drs = reinterpret_cast<float*>(static_cast<uint8_t*>(dc) + up(c_bytes));
+  float* dcs = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(drs) + up(rs_bytes));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, lhs, da, a_bytes));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, rhs, db, b_bytes));
+  if (requant) {
+    if (!row_scale || !col_scale)
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the requant epilogue needs row and column scales");
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, row_scale, drs, rs_bytes));
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, col_scale, dcs, cs_bytes));
+  }
+  B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, ws, IREE_B200_WORKSPACE_BYTES, 0));
+  B200_RETURN_IF_ERROR(iree_b200_matmul(context, params, da, db, dc, requant ? drs : nullptr, requant ? dcs : nullptr, ws));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(d, dc, out, c_bytes));
+  // Reads the status words back and waits for the stream: the result is in `out` on return.
+  return iree_b200_workspace_status(context, ws);
+}
+
+// ---- fused int4 dequant + matmul ---------------------------------------------------------------------
+static int w4_variant(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p, const void* a, const void* wq,
+                      const void* scales, const void* out) {
+  if (p->variant != IREE_B200_W4A16_AUTO) return p->variant;
+  const bool aligned = !(reinterpret_cast<uintptr_t>(a) % 16) && !(reinterpret_cast<uintptr_t>(wq) % 16) &&
+                       !(reinterpret_cast<uintptr_t>(scales) % 2) && !(reinterpret_cast<uintptr_t>(out) % 2);
+  if (p->group_size == 128 && aligned && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0) return IREE_B200_W4A16_DECODE;
+  if (p->group_size == 128 && aligned && p->K % 128 == 0) return IREE_B200_W4A16_GEMM;
+  return IREE_B200_W4A16_GENERIC;
+}
+
+static iree_b200_status_t w4_validate(const iree_b200_w4a16_params_t* p) {
+  if (!p) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "params is NULL");
+  if (p->M < 0 || p->N < 0 || p->K < 0) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "negative dimension");
+  if (p->group_size <= 0 || (p->group_size & 1) || p->K % p->group_size)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "K (%d) must be a multiple of an even group size (%d)", p->K,
+                p->group_size);
+  if (p->ldo < p->n_offset + p->N || p->n_offset < 0)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "output pitch %d cannot hold columns [%d, %d)", p->ldo, p->n_offset,
+                p->n_offset + p->N);
+  return IREE_B200_STATUS_OK;
+}
+
+size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
+  const size_t n = N > 0 ? static_cast<size_t>(N) : 0;
+  const size_t scratch = 16 * n * 4 + (n / 16 + 1) * 4;
+  return (IREE_B200_WORKSPACE_BYTES + scratch + 255) & ~static_cast<size_t>(255);
+}
+
+static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p) {
+  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const int64_t tiles_m = (p->M + 127) / 128;
+  int best = 0;
+  double best_cost = 0;
+  for (int bn = 256; bn >= 32; bn -= 32) {
+    if (p->tile_n && bn != p->tile_n) continue;
+    const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * (48.0 + bn);
+    if (!best || cost < best_cost * 0.9999) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                           const void* a, const void* wq, const void* scales, const void* out,
+                                           void* workspace, int32_t* out_variant, int32_t* out_tile_n) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(w4_validate(params));
+  const int variant = w4_variant(context, params, a, wq, scales, out);
+  if (out_variant) *out_variant = variant;
+  if (out_tile_n) *out_tile_n = 0;
+  if (variant != IREE_B200_W4A16_GEMM || !params->M || !params->N) return IREE_B200_STATUS_OK;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 128))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
+  if (params->group_size != 128 || params->K % 128)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the tensor-core kernel needs group size 128 and K %% 128 == 0");
+  const int bn = w4_choose_tile_n(context, params);
+  if (!bn) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tile_n %d is not usable", params->tile_n);
+  if (out_tile_n) *out_tile_n = bn;
+  uint8_t host[IREE_B200_WORKSPACE_BYTES];
+  memset(host, 0, sizeof host);
+  B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, 128, a, params->K,
+                                  params->M, 1, 64, 128, host));
+  B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_64B, 64, wq, params->K / 2,
+                                  params->N, 1, 64, bn, host + 128));
+  return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
+}
+
+iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                       const void* a, const void* wq, const void* scales, void* out, void* workspace,
+                                       int32_t variant, int32_t tile_n) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(w4_validate(params));
+  if (!params->M || !params->N) return IREE_B200_STATUS_OK;
+  if (!a || !wq || !scales || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
+  auto* cb = context->command_buffer;
+  auto* exe = context->executable;
+  const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
+  if (variant == IREE_B200_W4A16_DECODE) {
+    if (params->group_size != 128 || params->M > 16 || params->N % 16 || params->K % 256)
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the decode kernel needs M <= 16, N %% 16 == 0, K %% 256 == 0, group 128");
+    const int ksplit = (params->K + 4095) / 4096;
+    if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
+    void* scratch = static_cast<uint8_t*>(workspace) + IREE_B200_WORKSPACE_BYTES;
+    iree_hal_b200_descriptor_set_binding_t bindings[5] = {{0, const_cast<void*>(a)},
+                                                          {1, const_cast<void*>(wq)},
+                                                          {2, const_cast<void*>(scales)},
+                                                          {3, out},
+                                                          {4, scratch}};
+    const int32_t constants[5] = {params->M, params->N, params->K, params->ldo, params->n_offset};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 5, bindings));
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+    const int32_t ord = iree_hal_b200_executable_lookup(exe, params->M <= 8 ? "b200_w4a16_decode_m8" : "b200_w4a16_decode_m16");
+    const int tiles = params->N / 16;
+    int gx = sms / ksplit;
+    if (gx < 1) gx = 1;
+    if (gx > tiles) gx = tiles;
+    return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 5, 5, gx, ksplit, 1);
+  }
+  if (variant == IREE_B200_W4A16_GEMM) {
+    if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
+    if (tile_n <= 0) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "run() needs the tile_n that prepare() returned");
+    iree_hal_b200_descriptor_set_binding_t bindings[3] = {{0, const_cast<void*>(scales)}, {1, out}, {2, workspace}};
+    const int32_t constants[6] = {params->M, params->N, params->K, params->ldo, params->n_offset, tile_n};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 3, bindings));
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+    const int64_t tiles = static_cast<int64_t>((params->M + 127) / 128) * ((params->N + tile_n - 1) / tile_n);
+    const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_gemm");
+    return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 3, 6, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);
+  }
+  if (variant == IREE_B200_W4A16_GENERIC) {
+    iree_hal_b200_descriptor_set_binding_t bindings[4] = {
+        {0, const_cast<void*>(a)}, {1, const_cast<void*>(wq)}, {2, const_cast<void*>(scales)}, {3, out}};
+    const int32_t constants[6] = {params->M, params->N, params->K, params->group_size, params->ldo, params->n_offset};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+    const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_generic");
+    return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 4, 6, (params->N + 255) / 256, params->M, 1);
+  }
+  return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown W4A16 variant %d", variant);
+}
+
+iree_b200_status_t iree_b200_w4a16(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                   const void* a, const void* wq, const void* scales, void* out, void* workspace) {
+  int32_t variant = 0, tile_n = 0;
+  B200_RETURN_IF_ERROR(iree_b200_w4a16_prepare(context, params, a, wq, scales, out, workspace, &variant, &tile_n));
+  return iree_b200_w4a16_run(context, params, a, wq, scales, out, workspace, variant, tile_n);
+}
+
+iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                        const void* a, const void* wq, const void* scales, void* out) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(w4_validate(params));
+  const size_t a_bytes = static_cast<size_t>(params->M) * params->K * 2;
+  const size_t w_bytes = static_cast<size_t>(params->N) * (params->K / 2);
+  const size_t s_bytes = static_cast<size_t>(params->N) * (params->K / params->group_size) * 2;
+  const size_t c_bytes = static_cast<size_t>(params->M) * params->ldo * 2;
+  if (!params->M || !params->N) return IREE_B200_STATUS_OK;
+  auto* d = context->device;
+  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  const size_t ws_bytes = iree_b200_w4a16_workspace_bytes(params->N);
+  const size_t need = up(ws_bytes) + up(a_bytes) + up(w_bytes) + up(s_bytes) + up(c_bytes);
+  if (need > context->arena_size || !context->arena_w4_clean) {
+    B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
+    if (need > context->arena_size) {
+      if (context->arena) B200_RETURN_IF_ERROR(iree_hal_b200_buffer_free(d, context->arena));
+      context->arena = nullptr;
+      context->arena_size = 0;
+      B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(d, need, &context->arena));
+      context->arena_size = need;
+    }
+  }
+  uint8_t* base = static_cast<uint8_t*>(context->arena);
+  void* ws = base;
+  void* da = base + up(ws_bytes);
+  void* dw = static_cast<uint8_t*>(da) + up(a_bytes);
+  void* ds = static_cast<uint8_t*>(dw) + up(w_bytes);
+  void* dc = static_cast<uint8_t*>(ds) + up(s_bytes);
+  // The split-K scratch must start at zero; the kernel leaves it zero afterwards, but the arena
+  // is shared with other entry points, so it is cleared on every call here (a few hundred KiB).
+  B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, ws, ws_bytes, 0));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, a, da, a_bytes));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, wq, dw, w_bytes));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, scales, ds, s_bytes));
+  if (params->ldo != params->N) B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, out, dc, c_bytes));
+  B200_RETURN_IF_ERROR(iree_b200_w4a16(context, params, da, dw, ds, dc, ws));
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(d, dc, out, c_bytes));
+  return iree_b200_workspace_status(context, ws);
 }
 
 }  // extern "C"

@@ -1,0 +1,597 @@
+// Fused "dequantise int4 weights, then contract" dispatch (group-wise scales, no zero point):
+//   w_f16[n,k] = f16( f16(sext(wq[n,k])) * scale[n, k/128] )
+//   out[m,n]   = f16( sum_k f32(a[m,k]) * f32(w_f16[n,k]) )
+// wq is [N, K/2] bytes, element 2i in the low nibble of byte i; scales are [N, K/128] f16;
+// a is [M, K] f16; out is f16 with row pitch `ldo` and column offset `n_off` (so a rank that
+// owns a slice of N can write straight into the full-width result).
+//
+// Three kernels:
+//   b200_w4a16_decode_m8 / _m16  M <= 8 / 16: HBM-bound weight streaming. 16 warps each own a
+//       256-wide slice of K and keep the activations of that slice in registers for the whole
+//       kernel; weights go global -> registers -> f16 fragments -> mma.sync (f32 accumulate);
+//       the per-group scale is applied to the f32 group sum. One 32 KiB contiguous block of
+//       weights (16 rows) per tile. K beyond 4096 is split over gridDim.y with an f32 scratch
+//       reduction that cleans up after itself.
+//   b200_w4a16_gemm             larger M: tcgen05. Raw int4 tiles and activation tiles arrive by
+//       TMA; 8 warps expand the weights to f16 (exactly the dequant arithmetic above) into the
+//       128-byte-swizzled operand layout; one thread issues kind::f16 MMAs into TMEM.
+//   b200_w4a16_generic          any shape with K % group == 0: one thread per output.
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------------
+// int4 -> f16 helpers. A 32-bit word holds 8 weights; nibble j (bits 4j..4j+3) is weight j.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lop3_and_xor(uint32_t v, uint32_t mask, uint32_t x) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(r) : "r"(v), "r"(mask), "r"(x));  // (v & mask) ^ x
+  return r;
+}
+__device__ __forceinline__ __half2 as_half2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+// Exact signed values of weights (j, j+4) for j = 0..3 of one word, as four half2:
+//   p[0] = (w0, w4), p[1] = (w1, w5), p[2] = (w2, w6), p[3] = (w3, w7).
+// 0x6400 | x is the f16 1024 + x; flipping the nibble's top bit turns two's complement into
+// "value + 8", so 1024 + (n ^ 8) - 1032 = w, and for the nibble four bits up
+// (1024 + 16 (n ^ 8)) / 16 - 72 = w. Both are exact in f16.
+__device__ __forceinline__ void unpack8_strided(uint32_t v, __half2 (&p)[4]) {
+  const __half2 k1032 = __floats2half2_rn(1032.f, 1032.f);
+  const __half2 k16th = __floats2half2_rn(0.0625f, 0.0625f);
+  const __half2 km72 = __floats2half2_rn(-72.f, -72.f);
+  const uint32_t v8 = v >> 8;
+  p[0] = __hsub2(as_half2(lop3_and_xor(v, 0x000f000fu, 0x64086408u)), k1032);
+  p[1] = __hfma2(as_half2(lop3_and_xor(v, 0x00f000f0u, 0x64806480u)), k16th, km72);
+  p[2] = __hsub2(as_half2(lop3_and_xor(v8, 0x000f000fu, 0x64086408u)), k1032);
+  p[3] = __hfma2(as_half2(lop3_and_xor(v8, 0x00f000f0u, 0x64806480u)), k16th, km72);
+}
+
+// Exact signed values of weights in memory order: q[j] = (w(2j), w(2j+1)), j = 0..3 (byte j).
+__device__ __forceinline__ void unpack8_ordered(uint32_t v, __half2 (&q)[4]) {
+  const __half2 mul = __halves2half2(__float2half_rn(1.f), __float2half_rn(0.0625f));
+  const __half2 add = __halves2half2(__float2half_rn(-1032.f), __float2half_rn(-72.f));
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t rep;
+    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(rep) : "r"(v), "r"(0x1111u * j));  // byte j in every byte
+    // low half: 1024 + (n_lo ^ 8); high half: 1024 + 16 (n_hi ^ 8)
+    q[j] = __hfma2(as_half2(lop3_and_xor(rep, 0x00f0000fu, 0x64806408u)), mul, add);
+  }
+}
+
+__device__ __forceinline__ int sext4(uint32_t nib) { return static_cast<int>((nib ^ 8u) & 0xfu) - 8; }
+
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// =============================================================================================
+// Decode kernel
+// =============================================================================================
+constexpr int kDecodeThreads = 512;
+constexpr int kDecodeWarps = 16;
+constexpr int kDecodeChunkK = 256;                          // K per warp
+constexpr int kDecodeSliceK = kDecodeWarps * kDecodeChunkK;  // K per CTA: 4096
+constexpr int kDecodeTileRows = 16;                         // weight rows per tile
+constexpr int kDecodePrefetch = 2;                          // tiles of weights in flight per thread
+
+// Scratch for the split-K reduction: f32 partial sums [16][n_pad] followed by one arrival
+// counter per 16-row tile. Must be zero before the first launch; the last-arriving CTA of a
+// tile reads the sums, writes the result and zeroes what it used.
+struct DecodeScratchLayout {
+  __host__ __device__ static size_t partial_floats(int N) { return static_cast<size_t>(16) * N; }
+  __host__ __device__ static size_t bytes(int N) { return partial_floats(N) * 4 + static_cast<size_t>(N / 16) * 4; }
+};
+
+template <int MH>
+__device__ __forceinline__ void decode_body(const __half* __restrict__ a, const uint8_t* __restrict__ wq,
+                                            const __half* __restrict__ scales, __half* __restrict__ out,
+                                            float* __restrict__ scratch, int M, int N, int K, int ldo, int n_off) {
+  __shared__ float red[2][kDecodeWarps][32][4 * MH];
+  __shared__ int last_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int ksplit = gridDim.y;
+  const int k_slice0 = blockIdx.y * kDecodeSliceK;
+  const int kc = k_slice0 + warp * kDecodeChunkK;  // this warp's K chunk
+  const bool active = kc < K;                      // K is a multiple of 256
+  const int groups_per_row = K >> 7;
+  const int row_bytes = K >> 1;
+  const int num_tiles = N / kDecodeTileRows;
+
+  // ---- activations of this warp's chunk, kept in registers in the order the MMAs want -------------
+  // For step s, word i: the thread's eight k are k0 = kc + 128 s + 32 q + 8 i .. k0 + 7. The weight
+  // unpack yields pairs (0,4), (1,5), (2,6), (3,7); the activations are paired the same way.
+  uint32_t bfrag[MH][2][4][4];  // [m half][step][word][(0,4), (1,5), (2,6), (3,7)]
+#pragma unroll
+  for (int mh = 0; mh < MH; ++mh) {
+    const int m = g + 8 * mh;
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (active && m < M) x = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(m) * K + kc + 128 * s + 32 * q + 8 * i);
+        // x.x = (e0,e1), x.y = (e2,e3), x.z = (e4,e5), x.w = (e6,e7)
+        bfrag[mh][s][i][0] = __byte_perm(x.x, x.z, 0x5410);  // (e0, e4)
+        bfrag[mh][s][i][1] = __byte_perm(x.x, x.z, 0x7632);  // (e1, e5)
+        bfrag[mh][s][i][2] = __byte_perm(x.y, x.w, 0x5410);  // (e2, e6)
+        bfrag[mh][s][i][3] = __byte_perm(x.y, x.w, 0x7632);  // (e3, e7)
+      }
+  }
+
+  // ---- weight prefetch ring --------------------------------------------------------------------
+  uint4 wreg[kDecodePrefetch][2][2];      // [slot][step][row g / row g+8]
+  uint16_t sreg[kDecodePrefetch][2][2];   // matching scales
+  auto issue = [&](int slot, int tile) {
+    if (!active || tile >= num_tiles) return;
+    const int r0 = tile * kDecodeTileRows + g;
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const size_t row = static_cast<size_t>(r0 + 8 * h);
+        wreg[slot][s][h] = ld_stream_v4(wq + row * row_bytes + (kc >> 1) + 64 * s + 16 * q);
+        sreg[slot][s][h] = __ldg(reinterpret_cast<const uint16_t*>(scales) + row * groups_per_row + (kc >> 7) + s);
+      }
+  };
+
+#pragma unroll
+  for (int p = 0; p < kDecodePrefetch; ++p) issue(p, blockIdx.x + p * gridDim.x);
+
+  int iter = 0;
+  for (int tile0 = blockIdx.x; tile0 < num_tiles; tile0 += kDecodePrefetch * gridDim.x) {
+#pragma unroll
+    for (int p = 0; p < kDecodePrefetch; ++p) {
+      const int tile = tile0 + p * gridDim.x;
+      if (tile >= num_tiles) break;
+      float acc[MH][4];
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[mh][c] = 0.f;
+      if (active) {
+        uint4 w[2][2];
+        uint16_t sc[2][2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            w[s][h] = wreg[p][s][h];
+            sc[s][h] = sreg[p][s][h];
+          }
+        issue(p, tile + kDecodePrefetch * gridDim.x);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          float d[MH][4];
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) d[mh][c] = 0.f;
+          const uint32_t wl[4] = {w[s][0].x, w[s][0].y, w[s][0].z, w[s][0].w};
+          const uint32_t wh[4] = {w[s][1].x, w[s][1].y, w[s][1].z, w[s][1].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __half2 pl[4], ph[4];
+            unpack8_strided(wl[i], pl);  // weight row g
+            unpack8_strided(wh[i], ph);  // weight row g + 8
+#pragma unroll
+            for (int mh = 0; mh < MH; ++mh) {
+              mma_m16n8k16(d[mh], as_u32(pl[0]), as_u32(ph[0]), as_u32(pl[1]), as_u32(ph[1]), bfrag[mh][s][i][0],
+                           bfrag[mh][s][i][1]);
+              mma_m16n8k16(d[mh], as_u32(pl[2]), as_u32(ph[2]), as_u32(pl[3]), as_u32(ph[3]), bfrag[mh][s][i][2],
+                           bfrag[mh][s][i][3]);
+            }
+          }
+          // One step is exactly one scale group of rows g and g + 8.
+          const float s_lo = __half2float(__ushort_as_half(sc[s][0]));
+          const float s_hi = __half2float(__ushort_as_half(sc[s][1]));
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh) {
+            acc[mh][0] = fmaf(s_lo, d[mh][0], acc[mh][0]);
+            acc[mh][1] = fmaf(s_lo, d[mh][1], acc[mh][1]);
+            acc[mh][2] = fmaf(s_hi, d[mh][2], acc[mh][2]);
+            acc[mh][3] = fmaf(s_hi, d[mh][3], acc[mh][3]);
+          }
+        }
+      }
+      // ---- reduce the 16 K-chunks through shared memory ----------------------------------------
+      const int buf = iter & 1;
+      ++iter;
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh)
+        *reinterpret_cast<float4*>(&red[buf][warp][lane][4 * mh]) =
+            make_float4(acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
+      __syncthreads();
+      // Thread t < 128 * MH owns output (m = t / 16, weight row r = t % 16) of this tile.
+      const int t = threadIdx.x;
+      const bool owner = t < 128 * MH;
+      const int m = t >> 4, r = t & 15;
+      float sum = 0.f;
+      if (owner) {
+        const int src_lane = (r & 7) * 4 + ((m & 7) >> 1);
+        const int src_reg = (m >> 3) * 4 + (r >> 3) * 2 + (m & 1);
+#pragma unroll
+        for (int w2 = 0; w2 < kDecodeWarps; ++w2) sum += red[buf][w2][src_lane][src_reg];
+      }
+      const int n = tile * kDecodeTileRows + r;
+      if (ksplit == 1) {
+        if (owner && m < M) out[static_cast<size_t>(m) * ldo + n_off + n] = __float2half_rn(sum);
+      } else {
+        float* partial = scratch;
+        int* counters = reinterpret_cast<int*>(scratch + DecodeScratchLayout::partial_floats(N));
+        if (owner) atomicAdd(&partial[static_cast<size_t>(m) * N + n], sum);
+        __threadfence();
+        __syncthreads();
+        if (t == 0) last_flag = (atomicAdd(&counters[tile], 1) == ksplit - 1);
+        __syncthreads();
+        if (last_flag) {
+          __threadfence();
+          if (owner) {
+            float* cell = &partial[static_cast<size_t>(m) * N + n];
+            const float total = __ldcg(cell);
+            if (m < M) out[static_cast<size_t>(m) * ldo + n_off + n] = __float2half_rn(total);
+            __stcg(cell, 0.f);  // leave the scratch clean for the next launch
+          }
+          if (t == 0) counters[tile] = 0;
+        }
+      }
+    }
+  }
+}
+
+// =============================================================================================
+// tcgen05 kernel for larger M
+// =============================================================================================
+constexpr int kW4BM = 128;
+constexpr int kW4MaxBN = 256;
+constexpr int kW4Stages = 3;                        // f16 operand stages (A tile + expanded B tile)
+constexpr int kW4RawStages = 2;                     // raw int4 stages, each 128 K = one scale group
+constexpr int kW4AStageBytes = kW4BM * 128;         // 16 KiB: 128 rows x 64 f16
+constexpr int kW4BStageBytes = kW4MaxBN * 128;      // 32 KiB
+constexpr int kW4StageBytes = kW4AStageBytes + kW4BStageBytes;
+constexpr int kW4RawStageBytes = kW4MaxBN * 64;     // 16 KiB: 256 rows x 128 int4
+constexpr int kW4Threads = 512;
+constexpr int kW4DequantWarps = 8;
+constexpr int kW4SmemBytes = 1024 + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes + 256;
+
+struct alignas(128) W4Workspace {
+  uint8_t map_a[128];    // f16 [M, K], 128-byte swizzle, box 64 x 128
+  uint8_t map_w[128];    // u8 [N, K/2], 64-byte swizzle, box 64 x bn
+  uint8_t map_aux[128];
+  uint32_t status[32];
+};
+
+__device__ __forceinline__ void w4_report(W4Workspace* ws, uint32_t code, uint32_t info) {
+  if (atomicCAS(&ws->status[0], 0u, code) == 0u) ws->status[1] = info;
+}
+
+__device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, __half* __restrict__ out,
+                                            W4Workspace* __restrict__ ws, int M, int N, int K, int ldo, int n_off,
+                                            int bn) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t raw_base = smem_base + kW4Stages * kW4StageBytes;
+  const uint32_t bars = raw_base + kW4RawStages * kW4RawStageBytes;
+  uint8_t* bars_gen = smem_gen + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes;
+  // barriers: full[3], empty[3], raw_full[2], raw_empty[2], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int i) { return bars + 8u * i; };
+  auto empty_bar = [&](int i) { return bars + 8u * (3 + i); };
+  auto raw_full_bar = [&](int i) { return bars + 8u * (6 + i); };
+  auto raw_empty_bar = [&](int i) { return bars + 8u * (8 + i); };
+  auto tmem_full_bar = [&](int i) { return bars + 8u * (10 + i); };
+  auto tmem_empty_bar = [&](int i) { return bars + 8u * (12 + i); };
+  const uint32_t tmem_slot = bars + 8u * 14;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * 14);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * 14 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || bn < 32 || bn > kW4MaxBN || (bn & 31);
+  if (bad) {
+    if (threadIdx.x == 0) w4_report(ws, kStatusBadArgument, 0);
+    return;
+  }
+  const int tiles_m = (M + kW4BM - 1) / kW4BM;
+  const int tiles_n = (N + bn - 1) / bn;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = K / 64;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kW4Stages; ++i) {
+      mbar_init(full_bar(i), 1 + kW4DequantWarps);  // TMA producer + one arrival per dequant warp
+      mbar_init(empty_bar(i), 1);
+    }
+    for (int i = 0; i < kW4RawStages; ++i) {
+      mbar_init(raw_full_bar(i), 1);
+      mbar_init(raw_empty_bar(i), kW4DequantWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full_bar(i), 1);
+      mbar_init(tmem_empty_bar(i), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  auto tile_coords = [&](int t, int& tm, int& tn) {
+    tn = t / tiles_m;
+    tm = t - tn * tiles_m;
+  };
+
+  if (warp == 0) {
+    // -------- TMA producer: activation tiles every K block, raw weights every second one --------
+    if (lane == 0) {
+      tensormap_fence_acquire(ws->map_a);
+      tensormap_fence_acquire(ws->map_w);
+      uint32_t it = 0, raw_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tm, tn);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          if ((kb & 1) == 0) {
+            const int rs = raw_it % kW4RawStages;
+            const uint32_t rph = (raw_it / kW4RawStages) & 1;
+            if (!mbar_wait(raw_empty_bar(rs), rph ^ 1, abort_flag)) {
+              w4_report(ws, kStatusTimeoutEmpty, 0x10000u | raw_it);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(raw_full_bar(rs), bn * 64);
+            tma_load_3d(raw_base + rs * kW4RawStageBytes, ws->map_w, raw_full_bar(rs), (kb >> 1) * 64, tn * bn, 0);
+            ++raw_it;
+          }
+          const int st = it % kW4Stages;
+          const uint32_t ph = (it / kW4Stages) & 1;
+          if (!mbar_wait(empty_bar(st), ph ^ 1, abort_flag)) {
+            w4_report(ws, kStatusTimeoutEmpty, it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(full_bar(st), kW4AStageBytes);
+          tma_load_3d(smem_base + st * kW4StageBytes, ws->map_a, full_bar(st), kb * 64, tm * kW4BM, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------- MMA issuer ---------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc(1u, 0u, 0u, 0u, 0u, kW4BM, bn);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+        const int buf = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar(buf), acc_ph ^ 1, abort_flag)) {
+          w4_report(ws, kStatusTimeoutTmemEmpty, local_tile);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * kW4MaxBN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int st = it % kW4Stages;
+          const uint32_t ph = (it / kW4Stages) & 1;
+          if (!mbar_wait(full_bar(st), ph, abort_flag)) {
+            w4_report(ws, kStatusTimeoutDequant, it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_src = smem_base + st * kW4StageBytes;
+          const uint32_t b_src = a_src + kW4AStageBytes;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t a_desc = make_smem_desc(a_src + k * 32, 16, 1024);
+            const uint64_t b_desc = make_smem_desc(b_src + k * 32, 16, 1024);
+            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(st));
+        }
+        if (ok) tc_commit(tmem_full_bar(buf));
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // -------- epilogue -----------------------------------------------------------------------
+    const int qd = warp & 3;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && ((ldo * 2) % 16 == 0) && ((n_off * 2) % 16 == 0);
+    uint32_t local_tile = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local_tile) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int buf = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_ph, abort_flag))) {
+        if (lane == 0) {
+          w4_report(ws, kStatusTimeoutTmemFull, local_tile);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tm * kW4BM + qd * 32 + lane;
+      for (int c = 0; c < bn; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + buf * kW4MaxBN + c, v);
+        tc_wait_ld();
+        const int col0 = tn * bn + c;
+        if (row < M && col0 < N) {
+          __half* dst = out + static_cast<size_t>(row) * ldo + n_off + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (vec_ok && col0 + j + 7 < N) {
+              uint4 o;
+              o.x = as_u32(__floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
+              o.y = as_u32(__floats2half2_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])));
+              o.z = as_u32(__floats2half2_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])));
+              o.w = as_u32(__floats2half2_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
+              *reinterpret_cast<uint4*>(dst + j) = o;
+            } else {
+              for (int e = 0; e < 8; ++e)
+                if (col0 + j + e < N) dst[j + e] = __float2half_rn(__uint_as_float(v[j + e]));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+    }
+  } else if (warp >= 8) {
+    // -------- dequant: raw int4 (64-byte swizzled rows) -> f16 K-major 128-byte swizzled tile -----
+    // Thread r of the 256 handles weight row r of the tile: 64 K per block = 32 raw bytes in,
+    // one 128-byte operand row out.
+    const int r = threadIdx.x - 256;
+    uint32_t it = 0, raw_it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int n = tn * bn + r;
+      const bool row_live = r < bn;
+      const __half* srow = scales + static_cast<size_t>(n < N ? n : 0) * (K >> 7);
+      __half2 s2 = __half2half2(__float2half_rn(0.f));
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int rs = raw_it % kW4RawStages;
+        if ((kb & 1) == 0) {
+          const uint32_t rph = (raw_it / kW4RawStages) & 1;
+          if (!__all_sync(0xffffffffu, mbar_wait(raw_full_bar(rs), rph, abort_flag))) {
+            if (lane == 0) {
+              w4_report(ws, kStatusTimeoutFull, 0x10000u | raw_it);
+              *abort_flag = 1;
+            }
+            ok = false;
+            break;
+          }
+          if (row_live && n < N) s2 = __half2half2(srow[kb >> 1]);
+        }
+        const int st = it % kW4Stages;
+        const uint32_t ph = (it / kW4Stages) & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(st), ph ^ 1, abort_flag))) {
+          if (lane == 0) {
+            w4_report(ws, kStatusTimeoutEmpty, 0x20000u | it);
+            *abort_flag = 1;
+          }
+          ok = false;
+          break;
+        }
+        if (row_live) {
+          // Raw stage: row r is 64 bytes; its four 16-byte chunks are XOR-swizzled by (r / 2) % 4.
+          const uint8_t* raw_row = smem_gen + kW4Stages * kW4StageBytes + rs * kW4RawStageBytes + r * 64;
+          uint8_t* b_row = smem_gen + st * kW4StageBytes + kW4AStageBytes + r * 128;
+          const int sw_raw = (r >> 1) & 3, sw_b = r & 7;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int chunk = (kb & 1) * 2 + c;  // 16-byte chunk of the 64-byte raw row
+            const uint4 w = *reinterpret_cast<const uint4*>(raw_row + ((chunk ^ sw_raw) << 4));
+            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              __half2 qv[4];
+              unpack8_ordered(words[i], qv);
+              uint4 o;
+              o.x = as_u32(__hmul2(qv[0], s2));  // f16(w) * scale, one rounding: the reference's dequant
+              o.y = as_u32(__hmul2(qv[1], s2));
+              o.z = as_u32(__hmul2(qv[2], s2));
+              o.w = as_u32(__hmul2(qv[3], s2));
+              const int out_chunk = c * 4 + i;  // 8 f16 = 16 bytes of the 128-byte operand row
+              *reinterpret_cast<uint4*>(b_row + ((out_chunk ^ sw_b) << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();  // make the generic-proxy writes visible to the tensor core
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(full_bar(st));
+          if (kb & 1) mbar_arrive(raw_empty_bar(rs));
+        }
+        if (kb & 1) ++raw_it;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
+    b200_w4a16_decode_m8(const __half* a, const uint8_t* wq, const __half* scales, __half* out, float* scratch, int M,
+                         int N, int K, int ldo, int n_off) {
+  decode_body<1>(a, wq, scales, out, scratch, M, N, K, ldo, n_off);
+}
+extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
+    b200_w4a16_decode_m16(const __half* a, const uint8_t* wq, const __half* scales, __half* out, float* scratch, int M,
+                          int N, int K, int ldo, int n_off) {
+  decode_body<2>(a, wq, scales, out, scratch, M, N, K, ldo, n_off);
+}
+
+extern "C" __global__ void __launch_bounds__(kW4Threads, 1)
+    b200_w4a16_gemm(const __half* scales, __half* out, void* ws, int M, int N, int K, int ldo, int n_off, int bn) {
+  w4gemm_body(scales, out, reinterpret_cast<W4Workspace*>(ws), M, N, K, ldo, n_off, bn);
+}
+
+// Any M, N and any K that is a multiple of the (even) group size. One thread per output
+// element, sequential over K like the reference's generated loop nest.
+extern "C" __global__ void __launch_bounds__(256)
+    b200_w4a16_generic(const __half* a, const uint8_t* wq, const __half* scales, __half* out, int M, int N, int K,
+                       int group, int ldo, int n_off) {
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  const int m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  const int G = K / group;
+  float acc = 0.f;
+  for (int gi = 0; gi < G; ++gi) {
+    const __half s = scales[static_cast<size_t>(n) * G + gi];
+    for (int k = gi * group; k < (gi + 1) * group; ++k) {
+      const uint8_t byte = wq[static_cast<size_t>(n) * (K >> 1) + (k >> 1)];
+      const int w = sext4((k & 1) ? (byte >> 4) : (byte & 0xf));
+      const __half wd = __hmul(__int2half_rn(w), s);
+      acc += __half2float(a[static_cast<size_t>(m) * K + k]) * __half2float(wd);
+    }
+  }
+  out[static_cast<size_t>(m) * ldo + n_off + n] = __float2half_rn(acc);
+}

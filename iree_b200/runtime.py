@@ -42,7 +42,10 @@ class MatmulParams(C.Structure):
 
 class W4A16Params(C.Structure):
     _fields_ = [("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("group_size", C.c_int32),
-                ("n_out", C.c_int32), ("n_offset", C.c_int32), ("variant", C.c_int32), ("flags", C.c_int32)]
+                ("ldo", C.c_int32), ("n_offset", C.c_int32), ("variant", C.c_int32), ("tile_n", C.c_int32)]
+
+
+W4A16_AUTO, W4A16_DECODE, W4A16_GEMM, W4A16_GENERIC = 0, 1, 2, 3
 
 
 class _Binding(C.Structure):
@@ -74,6 +77,7 @@ def library():
         lib.iree_b200_context_executable.restype = C.c_void_p
         lib.iree_b200_context_command_buffer.restype = C.c_void_p
         lib.iree_hal_b200_command_buffer_launch_count.restype = C.c_uint64
+        lib.iree_b200_w4a16_workspace_bytes.restype = C.c_size_t
         _lib = lib
     return _lib
 
@@ -202,6 +206,19 @@ class Context:
         host = np.ascontiguousarray(host)
         return DeviceBuffer(self, max(host.nbytes, 1)).upload(host)
 
+    def pinned_empty(self, shape, dtype) -> np.ndarray:
+        """A numpy array over page-locked host memory (freed with the context's device)."""
+        nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        check(library().iree_hal_b200_host_allocate(self.device, C.c_size_t(max(nbytes, 1)), C.byref(p)))
+        buf = (C.c_uint8 * max(nbytes, 1)).from_address(p.value)
+        return np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+
+    def pinned_copy(self, host: np.ndarray) -> np.ndarray:
+        out = self.pinned_empty(host.shape, host.dtype)
+        out[...] = host
+        return out
+
     def workspace(self) -> DeviceBuffer:
         return DeviceBuffer(self, WORKSPACE_BYTES).fill(0)
 
@@ -251,6 +268,27 @@ class Context:
                     row_scale=None, col_scale=None) -> None:
         check(library().iree_b200_matmul_host(self.handle, C.byref(params), _vp(lhs), _vp(rhs), _vp(out),
                                               _vp(row_scale), _vp(col_scale)))
+
+    # fused int4 dequant + matmul
+    def w4a16_workspace(self, N: int) -> DeviceBuffer:
+        nbytes = int(library().iree_b200_w4a16_workspace_bytes(C.c_int32(N)))
+        return DeviceBuffer(self, nbytes).fill(0)
+
+    def w4a16_prepare(self, params: W4A16Params, a, wq, scales, out, ws):
+        variant, tile_n = C.c_int32(), C.c_int32()
+        check(library().iree_b200_w4a16_prepare(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out),
+                                                _vp(ws), C.byref(variant), C.byref(tile_n)))
+        return variant.value, tile_n.value
+
+    def w4a16_run(self, params: W4A16Params, a, wq, scales, out, ws, variant: int, tile_n: int) -> None:
+        check(library().iree_b200_w4a16_run(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out),
+                                            _vp(ws), C.c_int32(variant), C.c_int32(tile_n)))
+
+    def w4a16(self, params: W4A16Params, a, wq, scales, out, ws) -> None:
+        check(library().iree_b200_w4a16(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out), _vp(ws)))
+
+    def w4a16_host(self, params: W4A16Params, a, wq, scales, out) -> None:
+        check(library().iree_b200_w4a16_host(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out)))
 
     def encode_tensor_map(self, elem_bytes, is_bf16, ptr, dim0, dim1, dim2, box0, box1) -> bytes:
         out = C.create_string_buffer(128)

@@ -1,0 +1,116 @@
+"""Parity of the fused int4 dequant + matmul kernels with the CPU oracle, through the C ABI.
+Tolerance rtol = atol = 1e-2 (f16 out, f32 accumulate); the nibble order and group indexing
+are additionally checked exactly on small-integer data."""
+import numpy as np
+import pytest
+
+import iree_b200 as ib
+import oracle
+from iree_b200 import workloads
+from iree_b200.w4a16 import w4a16_numpy
+
+pytestmark = pytest.mark.gpu
+RTOL = ATOL = 1e-2
+import os
+THREADS = os.cpu_count() or 1
+
+
+def exact_case(rng, M, N, K, group=128):
+    """Integer activations, power-of-two scales: every product and partial sum is exact in f32
+    and every result fits f16, so all kernels must agree bit for bit with the oracle."""
+    a = rng.integers(-2, 3, (M, K)).astype(np.float16)
+    wq = workloads.pack_int4(rng.integers(-8, 8, (N, K), dtype=np.int8))
+    s = (2.0 ** rng.integers(-3, 1, (N, K // group))).astype(np.float16)
+    return a, wq, s
+
+
+@pytest.mark.parametrize("variant", [ib.W4A16_GENERIC, ib.W4A16_DECODE, ib.W4A16_GEMM])
+def test_exact_on_integer_data(ctx, variant):
+    rng = np.random.default_rng(21)
+    shapes = [(1, 16, 256), (8, 64, 512), (16, 256, 4096), (3, 48, 1024), (16, 32, 8192)]
+    if variant == ib.W4A16_GEMM:
+        shapes += [(128, 256, 256), (200, 384, 1024), (130, 264, 128)]
+    if variant == ib.W4A16_GENERIC:
+        shapes += [(5, 7, 128), (2, 33, 384)]
+    for (M, N, K) in shapes:
+        a, wq, s = exact_case(rng, M, N, K)
+        got = w4a16_numpy(ctx, a, wq, s, variant=variant)
+        want = oracle.w4a16(a, wq, s, threads=THREADS)
+        assert (got == want).all(), (variant, M, N, K, np.abs(got.astype(np.float32) - want.astype(np.float32)).max())
+
+
+def test_generic_other_group_sizes(ctx):
+    rng = np.random.default_rng(22)
+    for group in (32, 64, 256):
+        a, wq, s = exact_case(rng, 3, 40, 512, group)
+        got = w4a16_numpy(ctx, a, wq, s, group=group)
+        assert (got == oracle.w4a16(a, wq, s, group=group)).all(), group
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 128, 2048])
+def test_c4_w4a16(ctx, M):
+    a, wq, s = workloads.c4_w4a16(M)
+    got = w4a16_numpy(ctx, a, wq, s)
+    if M <= 128:
+        want = oracle.w4a16(a, wq, s, threads=THREADS)
+        np.testing.assert_allclose(got.astype(np.float32), want.astype(np.float32), rtol=RTOL, atol=ATOL)
+    else:  # a strided subset of rows keeps the CPU side to seconds
+        rows = np.arange(0, M, 61)
+        want = oracle.w4a16(a[rows], wq, s, threads=THREADS)
+        np.testing.assert_allclose(got[rows].astype(np.float32), want.astype(np.float32), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("M", [16, 4096])
+def test_c5_w4a16_70b_shape(ctx, M):
+    a, wq, s = workloads.c5_w4a16_sharded(M)
+    got = w4a16_numpy(ctx, a, wq, s)
+    cols = np.arange(0, wq.shape[0], 37)
+    rows = np.arange(0, M, 257) if M > 16 else np.arange(M)
+    want = oracle.w4a16(a[rows], wq[cols], s[cols], threads=THREADS)
+    np.testing.assert_allclose(got[np.ix_(rows, cols)].astype(np.float32), want.astype(np.float32), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("M", [8, 256])
+def test_sharded_slices_assemble_the_full_result(ctx, M):
+    """N-sharding as the multi-GPU path does it: each rank's slice written at its column offset
+    of the full-width buffer equals the unsharded result."""
+    a, wq, s = workloads.c4_w4a16(M, N=1024, K=1024, seed=9)
+    full = w4a16_numpy(ctx, a, wq, s)
+    world = 4
+    out = np.zeros((M, 1024), np.float16)
+    for r in range(world):
+        n0, n1 = r * 256, (r + 1) * 256
+        w4a16_numpy(ctx, a, wq[n0:n1], s[n0:n1], out=out, n_offset=n0)
+    assert (out == full).all()
+
+
+def test_decode_split_k_scratch_is_left_clean(ctx):
+    """K > 4096 goes through the f32 scratch reduction; a second call on the same workspace
+    must give the same answer (the kernel zeroes what it used)."""
+    rng = np.random.default_rng(23)
+    a, wq, s = exact_case(rng, 16, 64, 8192)
+    da, dw, ds = ctx.to_device(a), ctx.to_device(wq), ctx.to_device(s)
+    dc = ctx.alloc(16 * 64 * 2)
+    ws = ctx.w4a16_workspace(64)
+    p = ib.W4A16Params(16, 64, 8192, 128, 64, 0, ib.W4A16_DECODE, 0)
+    want = oracle.w4a16(a, wq, s)
+    for _ in range(3):
+        dc.fill(0x7E)
+        ctx.w4a16(p, da, dw, ds, dc, ws)
+        assert (dc.download(np.float16, (16, 64)) == want).all()
+    leftover = ws.download(np.uint8, (ws.nbytes,))[512:]
+    assert not leftover.any()
+    for x in (da, dw, ds, dc, ws):
+        x.free()
+
+
+def test_argument_errors(ctx):
+    a = np.zeros((2, 100), np.float16)
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.w4a16_host(ib.W4A16Params(2, 8, 100, 128, 8, 0, 0, 0), a, np.zeros((8, 50), np.uint8),
+                       np.zeros((8, 1), np.float16), np.zeros((2, 8), np.float16))
+    assert e.value.code_name == "INVALID_ARGUMENT"      # K not a multiple of the group size
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.w4a16_host(ib.W4A16Params(17, 16, 256, 128, 16, 0, ib.W4A16_DECODE, 0), np.zeros((17, 256), np.float16),
+                       np.zeros((16, 128), np.uint8), np.zeros((16, 2), np.float16), np.zeros((17, 16), np.float16))
+    assert e.value.code_name == "INVALID_ARGUMENT"      # decode kernel limit

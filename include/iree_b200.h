@@ -305,6 +305,27 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out);
 
+/* ---- W4A16 decode without any allocation ---------------------------------------------------------
+ * No counterpart in the reference: added for hosts that cannot allocate device memory where
+ * they dispatch (inside a stream capture, after handing all memory to their own pool, or on a
+ * path that must not take the driver's allocation lock). Same arithmetic and the same kernel
+ * body as IREE_B200_W4A16_DECODE, but the split-K scratch is a fixed array inside the
+ * library's device image, so only inputs and outputs are passed; nothing is allocated or freed,
+ * here or in any library this calls.
+ *   - runs on the CUDA device that is current on the calling thread, on `stream` (a
+ *     cudaStream_t; NULL = the default stream); all pointers are device pointers;
+ *   - 1 <= M <= 16, N a multiple of 16 and at most IREE_B200_NOALLOC_MAX_N (OUT_OF_RANGE beyond
+ *     it), K a multiple of 256, group size 128; out[m * ldo + n_offset + n] receives the result;
+ *   - the first call on each device looks up the scratch array's address; make that first call
+ *     before starting any stream capture;
+ *   - every call on a device shares the one scratch array (about 2 MiB, held by every GPU that
+ *     loads the library until the process exits): calls that overlap on the GPU race, so keep
+ *     them on one stream or order them yourself. */
+#define IREE_B200_NOALLOC_MAX_N 32768
+iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, const void* wq, const void* scales, void* out,
+                                                  int32_t M, int32_t N, int32_t K, int32_t ldo, int32_t n_offset,
+                                                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

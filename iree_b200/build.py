@@ -21,8 +21,8 @@ LIB = os.path.join(HERE, "libiree_b200.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 KERNEL_SOURCES = ["contraction_sm100.cu", "w4a16_sm100.cu", "data_tiling_sm100.cu"]
-HOST_SOURCES = ["hal_b200.cc"]
-HEADERS = ["sm100_ptx.cuh", os.path.join("..", "..", "include", "iree_b200.h")]
+HOST_SOURCES = ["hal_b200.cc", "w4a16_noalloc.cu"]
+HEADERS = ["sm100_ptx.cuh", "w4a16_decode.cuh", "hal_b200_internal.h", os.path.join("..", "..", "include", "iree_b200.h")]
 
 
 def _newer(target: str, sources) -> bool:
@@ -71,13 +71,16 @@ def build_host(force: bool = False, verbose: bool = False) -> str:
     deps = srcs + [os.path.join(CSRC, h) for h in HEADERS]
     if not force and _newer(LIB, deps):
         return LIB
-    cxx = shutil.which("g++")
-    if cxx is None:
+    nvcc = shutil.which("nvcc") or os.path.join(CUDA_HOME, "bin", "nvcc")
+    if not os.path.exists(nvcc):
         if os.path.exists(LIB):
             return LIB
-        raise RuntimeError("g++ not found and no prebuilt " + LIB)
-    _run([cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-I", os.path.join(CUDA_HOME, "include"),
-          "-o", LIB] + srcs + ["-ldl", "-lpthread"], verbose)
+        raise RuntimeError("nvcc not found and no prebuilt " + LIB)
+    # nvcc drives g++ for hal_b200.cc and compiles the one .cu that carries host code. The CUDA
+    # runtime is linked statically; it opens the driver library lazily, so the result still
+    # loads on a machine without a GPU.
+    _run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17", "-shared",
+          "-cudart", "static", "-Xcompiler", "-fPIC,-Wall", "-o", LIB] + srcs + ["-ldl", "-lpthread"], verbose)
     return LIB
 
 

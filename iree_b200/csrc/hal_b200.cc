@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../../include/iree_b200.h"
+#include "hal_b200_internal.h"
 
 namespace {
 
@@ -395,6 +396,11 @@ struct iree_hal_b200_channel_t {
 extern "C" {
 
 const char* iree_b200_last_error(void) { return g_last_error.c_str(); }
+
+int32_t iree_b200_internal_set_error(int32_t code, const char* message) {
+  g_last_error = message ? message : "";
+  return code;
+}
 
 // ---- device ----------------------------------------------------------------------------------
 iree_b200_status_t iree_hal_b200_device_create(int32_t ordinal, iree_hal_b200_device_t** out_device) {

@@ -305,6 +305,21 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out);
 
+/* ---- sequences of dispatches ----------------------------------------------------------------------
+ * `count` dispatches over rotating operand sets issued by one call, i.e. what the reference does
+ * when a queue action replays a command buffer that holds that many dispatches
+ * (runtime/src/iree/hal/drivers/cuda/pending_queue_actions.c:729-742). Step i uses set
+ * (first + i) % set_count; every array has set_count entries (scale arrays may be NULL). */
+iree_b200_status_t iree_b200_matmul_run_sequence(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                                 int32_t set_count, const void* const* lhs, const void* const* rhs,
+                                                 void* const* out, const float* const* row_scale,
+                                                 const float* const* col_scale, void* const* workspace,
+                                                 int32_t tile_n, int32_t first, int32_t count);
+iree_b200_status_t iree_b200_w4a16_run_sequence(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                                int32_t set_count, const void* const* a, const void* const* wq,
+                                                const void* const* scales, void* const* out, void* const* workspace,
+                                                int32_t variant, int32_t tile_n, int32_t first, int32_t count);
+
 /* ---- W4A16 decode without any allocation ---------------------------------------------------------
  * No counterpart in the reference: added for hosts that cannot allocate device memory where
  * they dispatch (inside a stream capture, after handing all memory to their own pool, or on a

@@ -838,6 +838,9 @@ namespace {
 
 constexpr uint32_t kGemmThreads = 256;
 constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
+// weight ring (3 stages of 16 rows x 2048 B), scale ring (3 x 4 KiB), 4 slots of 16 per-warp partials, barriers
+constexpr uint32_t kDecodeSmemM8 = 3 * 16 * 2048 + 3 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 3 + 8) * 8 + 16;
+constexpr uint32_t kDecodeSmemM16 = 3 * 16 * 2048 + 3 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 3 + 8) * 8 + 16;
 constexpr uint32_t kW4SmemBytes = 1024 + 3 * (128 * 128 + 256 * 128) + 2 * (256 * 64) + 256;
 
 struct EntryDecl {
@@ -862,8 +865,8 @@ const EntryDecl kEntries[] = {
     {"b200_matmul_generic_bf16_f32", {16, 16, 1}, 0},
     {"b200_matmul_generic_i8_i32", {16, 16, 1}, 0},
     {"b200_matmul_generic_i8_requant_f16", {16, 16, 1}, 0},
-    {"b200_w4a16_decode_m8", {512, 1, 1}, 0},
-    {"b200_w4a16_decode_m16", {512, 1, 1}, 0},
+    {"b200_w4a16_decode_m8", {512, 1, 1}, kDecodeSmemM8},
+    {"b200_w4a16_decode_m16", {512, 1, 1}, kDecodeSmemM16},
     {"b200_w4a16_gemm", {512, 1, 1}, kW4SmemBytes},
     {"b200_w4a16_generic", {256, 1, 1}, 0},
 };
@@ -1213,7 +1216,8 @@ static int w4_variant(const iree_b200_context_t* ctx, const iree_b200_w4a16_para
   if (p->variant != IREE_B200_W4A16_AUTO) return p->variant;
   const bool aligned = !(reinterpret_cast<uintptr_t>(a) % 16) && !(reinterpret_cast<uintptr_t>(wq) % 16) &&
                        !(reinterpret_cast<uintptr_t>(scales) % 2) && !(reinterpret_cast<uintptr_t>(out) % 2);
-  if (p->group_size == 128 && aligned && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0) return IREE_B200_W4A16_DECODE;
+  if (p->group_size == 128 && aligned && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0 && p->K <= 16384)
+    return IREE_B200_W4A16_DECODE;
   if (p->group_size == 128 && aligned && p->K % 128 == 0) return IREE_B200_W4A16_GEMM;
   return IREE_B200_W4A16_GENERIC;
 }
@@ -1290,8 +1294,9 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
   auto* exe = context->executable;
   const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
   if (variant == IREE_B200_W4A16_DECODE) {
-    if (params->group_size != 128 || params->M > 16 || params->N % 16 || params->K % 256)
-      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the decode kernel needs M <= 16, N %% 16 == 0, K %% 256 == 0, group 128");
+    if (params->group_size != 128 || params->M > 16 || params->N % 16 || params->K % 256 || params->K > 16384)
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT,
+                  "the decode kernel needs M <= 16, N %% 16 == 0, K %% 256 == 0, K <= 16384, group 128");
     const int ksplit = (params->K + 4095) / 4096;
     if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
     void* scratch = static_cast<uint8_t*>(workspace) + IREE_B200_WORKSPACE_BYTES;
@@ -1379,6 +1384,38 @@ iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree
   B200_RETURN_IF_ERROR(iree_b200_w4a16(context, params, da, dw, ds, dc, ws));
   B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(d, dc, out, c_bytes));
   return iree_b200_workspace_status(context, ws);
+}
+
+// ---- command sequences -------------------------------------------------------------------------------
+// A recorded run of `count` dispatches over rotating operand sets, issued from C in one call:
+// what replaying a command buffer that holds `count` dispatches does in the reference
+// (runtime/src/iree/hal/drivers/cuda/pending_queue_actions.c:729-742). Step i uses operand set
+// (first + i) % set_count.
+iree_b200_status_t iree_b200_matmul_run_sequence(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                                 int32_t set_count, const void* const* lhs, const void* const* rhs,
+                                                 void* const* out, const float* const* row_scale,
+                                                 const float* const* col_scale, void* const* workspace,
+                                                 int32_t tile_n, int32_t first, int32_t count) {
+  if (set_count < 1 || !lhs || !rhs || !out || !workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  for (int32_t i = 0; i < count; ++i) {
+    const int32_t s = (first + i) % set_count;
+    B200_RETURN_IF_ERROR(iree_b200_matmul_run(context, params, lhs[s], rhs[s], out[s], row_scale ? row_scale[s] : nullptr,
+                                              col_scale ? col_scale[s] : nullptr, workspace[s], tile_n));
+  }
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_b200_w4a16_run_sequence(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                                int32_t set_count, const void* const* a, const void* const* wq,
+                                                const void* const* scales, void* const* out, void* const* workspace,
+                                                int32_t variant, int32_t tile_n, int32_t first, int32_t count) {
+  if (set_count < 1 || !a || !wq || !scales || !out || !workspace)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  for (int32_t i = 0; i < count; ++i) {
+    const int32_t s = (first + i) % set_count;
+    B200_RETURN_IF_ERROR(iree_b200_w4a16_run(context, params, a[s], wq[s], scales[s], out[s], workspace[s], variant, tile_n));
+  }
+  return IREE_B200_STATUS_OK;
 }
 
 }  // extern "C"

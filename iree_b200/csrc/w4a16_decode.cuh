@@ -72,10 +72,27 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
 // =============================================================================================
 constexpr int kDecodeThreads = 512;
 constexpr int kDecodeWarps = 16;
-constexpr int kDecodeChunkK = 256;                          // K per warp
+constexpr int kDecodeChunkK = 256;                           // K per warp
 constexpr int kDecodeSliceK = kDecodeWarps * kDecodeChunkK;  // K per CTA: 4096
-constexpr int kDecodeTileRows = 16;                         // weight rows per tile
-constexpr int kDecodePrefetch = 2;                          // tiles of weights in flight per thread
+constexpr int kDecodeTileRows = 16;                          // weight rows per tile
+// Weight tiles resident in shared memory: one being read, two in flight. More in flight does not
+// help: the memory system completes everything outstanding at about the same time, so a deeper
+// ring only delays the first tile instead of overlapping the stream with the arithmetic.
+__host__ __device__ constexpr int decode_stages(int mh) { return 3; }
+constexpr int kDecodeSlots = 4;                              // tiles being reduced at the same time
+constexpr int kDecodeRowPitch = kDecodeSliceK / 2;           // 2048 B: a full-width tile is one contiguous 32 KiB copy
+constexpr int kDecodeMaxScaleBytes = 16 * 128 * 2;          // scale tile: 16 rows x up to 128 groups (K <= 16384)
+
+// Dynamic shared memory of the decode kernel:
+//   weight ring  [stage][row][2048 B]      whole rows of the CTA's K slice (one bulk copy per tile
+//                                          when the slice is the whole row, else one per row)
+//   scale ring   [stage][row][K / 128] f16 the tile's scale rows, one bulk copy
+//   partial sums [slot][warp][lane][4 MH] f32   (MMA fragment order, one per K chunk)
+//   mbarriers: weights full / empty per stage, partials full / empty per slot; abort word
+__host__ __device__ constexpr int decode_smem_bytes(int mh) {
+  return decode_stages(mh) * kDecodeTileRows * kDecodeRowPitch + decode_stages(mh) * kDecodeMaxScaleBytes +
+         kDecodeSlots * kDecodeWarps * 32 * 4 * mh * 4 + (2 * decode_stages(mh) + 2 * kDecodeSlots) * 8 + 16;
+}
 
 // Scratch for the split-K reduction: f32 partial sums [16][n_pad] followed by one arrival
 // counter per 16-row tile. Must be zero before the first launch; the last-arriving CTA of a
@@ -85,162 +102,313 @@ struct DecodeScratchLayout {
   __host__ __device__ static size_t bytes(int N) { return partial_floats(N) * 4 + static_cast<size_t>(N / 16) * 4; }
 };
 
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// Untiled bulk copy global -> shared, completion reported to an mbarrier as transaction bytes.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// The weights enter the MMA as the biased halves the bit trick produces, without a subtract:
+//   low nibbles  -> 1032 + w        (0x6400 | (n ^ 8))
+//   high nibbles -> 1152 + 16 w     (0x6400 | ((n ^ 8) << 4))
+// Low- and high-nibble weights accumulate separately; with S = sum of the activations that met
+// them, the group sum is (d_lo - 1032 S_lo) + (d_hi / 16 - 72 S_hi). All of this is exact for
+// integer data and loses < 1e-4 relative on normal data (f32 accumulation of terms ~1e3 |a|).
 template <int MH>
 __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const uint8_t* __restrict__ wq,
                                             const __half* __restrict__ scales, __half* __restrict__ out,
                                             float* __restrict__ scratch, int M, int N, int K, int ldo, int n_off) {
-  __shared__ float red[2][kDecodeWarps][32][4 * MH];
-  __shared__ int last_flag;
+  constexpr int kDecodeStages = decode_stages(MH);
+  constexpr int kDecodeWRingBytes = kDecodeStages * kDecodeTileRows * kDecodeRowPitch;
+  constexpr int kDecodeSRingBytes = kDecodeStages * kDecodeMaxScaleBytes;
+  extern __shared__ __align__(128) uint8_t decode_smem[];
+  uint8_t* wring = decode_smem;
+  uint8_t* sring = wring + kDecodeWRingBytes;
+  float* accs = reinterpret_cast<float*>(sring + kDecodeSRingBytes);
+  uint8_t* bar_mem = reinterpret_cast<uint8_t*>(accs + kDecodeSlots * kDecodeWarps * 32 * 4 * MH);
+  const uint32_t bars = smem_u32(bar_mem);
+  auto wfull_bar = [&](int i) { return bars + 8u * i; };
+  auto wempty_bar = [&](int i) { return bars + 8u * (kDecodeStages + i); };
+  auto pfull_bar = [&](int i) { return bars + 8u * (2 * kDecodeStages + i); };
+  auto pempty_bar = [&](int i) { return bars + 8u * (2 * kDecodeStages + kDecodeSlots + i); };
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bar_mem + (2 * kDecodeStages + 2 * kDecodeSlots) * 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int ksplit = gridDim.y;
   const int k_slice0 = blockIdx.y * kDecodeSliceK;
-  const int kc = k_slice0 + warp * kDecodeChunkK;  // this warp's K chunk
-  const bool active = kc < K;                      // K is a multiple of 256
+  const int kc = k_slice0 + warp * kDecodeChunkK;  // this warp's K chunk (K is a multiple of 256)
   const int groups_per_row = K >> 7;
   const int row_bytes = K >> 1;
   const int num_tiles = N / kDecodeTileRows;
+  int active_warps = (K - k_slice0) / kDecodeChunkK;  // K chunks in this CTA's slice
+  if (active_warps > kDecodeWarps) active_warps = kDecodeWarps;
+  const uint32_t slice_row_bytes = active_warps * (kDecodeChunkK / 2);
 
-  // ---- activations of this warp's chunk, kept in registers in the order the MMAs want -------------
-  // For step s, word i: the thread's eight k are k0 = kc + 128 s + 32 q + 8 i .. k0 + 7. The weight
-  // unpack yields pairs (0,4), (1,5), (2,6), (3,7); the activations are paired the same way.
-  uint32_t bfrag[MH][2][4][4];  // [m half][step][word][(0,4), (1,5), (2,6), (3,7)]
-#pragma unroll
-  for (int mh = 0; mh < MH; ++mh) {
-    const int m = g + 8 * mh;
-#pragma unroll
-    for (int s = 0; s < 2; ++s)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 x = make_uint4(0, 0, 0, 0);
-        if (active && m < M) x = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(m) * K + kc + 128 * s + 32 * q + 8 * i);
-        // x.x = (e0,e1), x.y = (e2,e3), x.z = (e4,e5), x.w = (e6,e7)
-        bfrag[mh][s][i][0] = __byte_perm(x.x, x.z, 0x5410);  // (e0, e4)
-        bfrag[mh][s][i][1] = __byte_perm(x.x, x.z, 0x7632);  // (e1, e5)
-        bfrag[mh][s][i][2] = __byte_perm(x.y, x.w, 0x5410);  // (e2, e6)
-        bfrag[mh][s][i][3] = __byte_perm(x.y, x.w, 0x7632);  // (e3, e7)
-      }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kDecodeStages; ++i) {
+      mbar_init(wfull_bar(i), 1);
+      mbar_init(wempty_bar(i), active_warps);
+    }
+    for (int i = 0; i < kDecodeSlots; ++i) {
+      mbar_init(pfull_bar(i), active_warps);
+      mbar_init(pempty_bar(i), 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
   }
+  __syncthreads();
+  if (warp >= active_warps) return;  // nothing below synchronises the whole CTA
 
-  // ---- weight prefetch ring --------------------------------------------------------------------
-  uint4 wreg[kDecodePrefetch][2][2];      // [slot][step][row g / row g+8]
-  uint16_t sreg[kDecodePrefetch][2][2];   // matching scales
-  auto issue = [&](int slot, int tile) {
-    if (!active || tile >= num_tiles) return;
-    const int r0 = tile * kDecodeTileRows + g;
-#pragma unroll
-    for (int s = 0; s < 2; ++s)
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const size_t row = static_cast<size_t>(r0 + 8 * h);
-        wreg[slot][s][h] = ld_stream_v4(wq + row * row_bytes + (kc >> 1) + 64 * s + 16 * q);
-        sreg[slot][s][h] = __ldg(reinterpret_cast<const uint16_t*>(scales) + row * groups_per_row + (kc >> 7) + s);
-      }
+  const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  // Feeding the weight ring is a side job that rotates over the warps (tile jp is fetched by warp
+  // jp % active_warps): bulk copies are asynchronous, so nobody blocks on issuing loads. A tile is
+  // one contiguous 32 KiB copy when the CTA's slice is the whole row, else one copy per row; its
+  // scale rows are one more copy.
+  const uint32_t scale_tile_bytes = kDecodeTileRows * groups_per_row * 2;
+  auto produce = [&](int jp) -> bool {
+    if (jp >= my_tiles) return true;
+    const int st = jp % kDecodeStages;
+    if (!__all_sync(0xffffffffu, mbar_wait(wempty_bar(st), ((jp / kDecodeStages) & 1) ^ 1, abort_flag))) {
+      *abort_flag = 1;
+      return false;
+    }
+    const size_t row0 = static_cast<size_t>(blockIdx.x + jp * gridDim.x) * kDecodeTileRows;
+    const uint32_t dst = smem_u32(wring) + st * kDecodeTileRows * kDecodeRowPitch;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(wfull_bar(st), kDecodeTileRows * slice_row_bytes + scale_tile_bytes);
+      bulk_load(smem_u32(sring) + st * kDecodeMaxScaleBytes, scales + row0 * groups_per_row, scale_tile_bytes,
+                wfull_bar(st));
+      if (slice_row_bytes == static_cast<uint32_t>(row_bytes) && slice_row_bytes == kDecodeRowPitch)
+        bulk_load(dst, wq + row0 * row_bytes, kDecodeTileRows * slice_row_bytes, wfull_bar(st));
+    }
+    __syncwarp();
+    if (!(slice_row_bytes == static_cast<uint32_t>(row_bytes) && slice_row_bytes == kDecodeRowPitch) &&
+        lane < kDecodeTileRows)
+      bulk_load(dst + lane * kDecodeRowPitch, wq + (row0 + lane) * row_bytes + (k_slice0 >> 1), slice_row_bytes,
+                wfull_bar(st));
+    return true;
   };
 
-#pragma unroll
-  for (int p = 0; p < kDecodePrefetch; ++p) issue(p, blockIdx.x + p * gridDim.x);
+  for (int jp = 0; jp < kDecodeStages - 1; ++jp)
+    if (warp == jp % active_warps) produce(jp);
 
-  int iter = 0;
-  for (int tile0 = blockIdx.x; tile0 < num_tiles; tile0 += kDecodePrefetch * gridDim.x) {
+  // ---- activations of this warp's chunk, kept in registers in the order the MMAs want -------------
+  // For step s, word i: the thread's eight k are k0 = kc + 128 s + 32 q + 8 i .. k0 + 7, paired
+  // (0,4), (1,5), (2,6), (3,7) like the nibbles of a weight word. Each warp reads its chunk of every
+  // activation row with coalesced 256-byte requests, parks it in the last ring stage (not in use
+  // yet) and picks up the 64 bytes per row and step it needs.
+  uint32_t bfrag[MH][2][4][4];
+  float bias[MH][2][2];  // 1032 S_lo + 72 S_hi per step and output column (2q, 2q + 1)
+  {
+    uint8_t* tmp = wring + (kDecodeStages - 1) * kDecodeTileRows * kDecodeRowPitch + warp * 2048;
+    // All global loads first (they land in the registers that will hold the fragments), then the
+    // per-step shuffles through shared memory, so the load latency is paid once.
 #pragma unroll
-    for (int p = 0; p < kDecodePrefetch; ++p) {
-      const int tile = tile0 + p * gridDim.x;
-      if (tile >= num_tiles) break;
-      float acc[MH][4];
+    for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
-      for (int mh = 0; mh < MH; ++mh)
+      for (int s = 0; s < 2; ++s)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) acc[mh][c] = 0.f;
-      if (active) {
-        uint4 w[2][2];
-        uint16_t sc[2][2];
-#pragma unroll
-        for (int s = 0; s < 2; ++s)
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            w[s][h] = wreg[p][s][h];
-            sc[s][h] = sreg[p][s][h];
-          }
-        issue(p, tile + kDecodePrefetch * gridDim.x);
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          float d[MH][4];
-#pragma unroll
-          for (int mh = 0; mh < MH; ++mh)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) d[mh][c] = 0.f;
-          const uint32_t wl[4] = {w[s][0].x, w[s][0].y, w[s][0].z, w[s][0].w};
-          const uint32_t wh[4] = {w[s][1].x, w[s][1].y, w[s][1].z, w[s][1].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            __half2 pl[4], ph[4];
-            unpack8_strided(wl[i], pl);  // weight row g
-            unpack8_strided(wh[i], ph);  // weight row g + 8
-#pragma unroll
-            for (int mh = 0; mh < MH; ++mh) {
-              mma_m16n8k16(d[mh], as_u32(pl[0]), as_u32(ph[0]), as_u32(pl[1]), as_u32(ph[1]), bfrag[mh][s][i][0],
-                           bfrag[mh][s][i][1]);
-              mma_m16n8k16(d[mh], as_u32(pl[2]), as_u32(ph[2]), as_u32(pl[3]), as_u32(ph[3]), bfrag[mh][s][i][2],
-                           bfrag[mh][s][i][3]);
-            }
-          }
-          // One step is exactly one scale group of rows g and g + 8.
-          const float s_lo = __half2float(__ushort_as_half(sc[s][0]));
-          const float s_hi = __half2float(__ushort_as_half(sc[s][1]));
-#pragma unroll
-          for (int mh = 0; mh < MH; ++mh) {
-            acc[mh][0] = fmaf(s_lo, d[mh][0], acc[mh][0]);
-            acc[mh][1] = fmaf(s_lo, d[mh][1], acc[mh][1]);
-            acc[mh][2] = fmaf(s_hi, d[mh][2], acc[mh][2]);
-            acc[mh][3] = fmaf(s_hi, d[mh][3], acc[mh][3]);
-          }
+        for (int it = 0; it < 4; ++it) {  // 8 rows x 256 bytes, half a warp per row
+          const int m = 2 * it + (lane >> 4) + 8 * mh;
+          uint4 x = make_uint4(0, 0, 0, 0);
+          if (m < M) x = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(m) * K + kc + 128 * s + 8 * (lane & 15));
+          bfrag[mh][s][it][0] = x.x;
+          bfrag[mh][s][it][1] = x.y;
+          bfrag[mh][s][it][2] = x.z;
+          bfrag[mh][s][it][3] = x.w;
         }
-      }
-      // ---- reduce the 16 K-chunks through shared memory ----------------------------------------
-      const int buf = iter & 1;
-      ++iter;
 #pragma unroll
-      for (int mh = 0; mh < MH; ++mh)
-        *reinterpret_cast<float4*>(&red[buf][warp][lane][4 * mh]) =
-            make_float4(acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
-      __syncthreads();
-      // Thread t < 128 * MH owns output (m = t / 16, weight row r = t % 16) of this tile.
-      const int t = threadIdx.x;
-      const bool owner = t < 128 * MH;
-      const int m = t >> 4, r = t & 15;
-      float sum = 0.f;
-      if (owner) {
-        const int src_lane = (r & 7) * 4 + ((m & 7) >> 1);
-        const int src_reg = (m >> 3) * 4 + (r >> 3) * 2 + (m & 1);
+    for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
-        for (int w2 = 0; w2 < kDecodeWarps; ++w2) sum += red[buf][w2][src_lane][src_reg];
-      }
-      const int n = tile * kDecodeTileRows + r;
-      if (ksplit == 1) {
-        if (owner && m < M) out[static_cast<size_t>(m) * ldo + n_off + n] = __float2half_rn(sum);
-      } else {
-        float* partial = scratch;
-        int* counters = reinterpret_cast<int*>(scratch + DecodeScratchLayout::partial_floats(N));
-        if (owner) atomicAdd(&partial[static_cast<size_t>(m) * N + n], sum);
-        __threadfence();
-        __syncthreads();
-        if (t == 0) last_flag = (atomicAdd(&counters[tile], 1) == ksplit - 1);
-        __syncthreads();
-        if (last_flag) {
-          __threadfence();
-          if (owner) {
-            float* cell = &partial[static_cast<size_t>(m) * N + n];
-            const float total = __ldcg(cell);
-            if (m < M) out[static_cast<size_t>(m) * ldo + n_off + n] = __float2half_rn(total);
-            __stcg(cell, 0.f);  // leave the scratch clean for the next launch
-          }
-          if (t == 0) counters[tile] = 0;
+      for (int s = 0; s < 2; ++s) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it)
+          *reinterpret_cast<uint4*>(tmp + (2 * it + (lane >> 4)) * 256 + (lane & 15) * 16) =
+              make_uint4(bfrag[mh][s][it][0], bfrag[mh][s][it][1], bfrag[mh][s][it][2], bfrag[mh][s][it][3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 x = *reinterpret_cast<const uint4*>(tmp + g * 256 + 64 * q + 16 * i);
+          // x = (e0,e1), y = (e2,e3), z = (e4,e5), w = (e6,e7) of the thread's eight k
+          bfrag[mh][s][i][0] = __byte_perm(x.x, x.z, 0x5410);  // (e0, e4)
+          bfrag[mh][s][i][1] = __byte_perm(x.x, x.z, 0x7632);  // (e1, e5)
+          bfrag[mh][s][i][2] = __byte_perm(x.y, x.w, 0x5410);  // (e2, e6)
+          bfrag[mh][s][i][3] = __byte_perm(x.y, x.w, 0x7632);  // (e3, e7)
         }
+        __syncwarp();
+        float s_lo[4] = {0.f, 0.f, 0.f, 0.f}, s_hi[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t ones = 0x3c003c00u;  // (1.0, 1.0)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mma_m16n8k16(s_lo, ones, ones, ones, ones, bfrag[mh][s][i][0], bfrag[mh][s][i][2]);
+          mma_m16n8k16(s_hi, ones, ones, ones, ones, bfrag[mh][s][i][1], bfrag[mh][s][i][3]);
+        }
+        bias[mh][s][0] = 1032.f * s_lo[0] + 72.f * s_hi[0];
+        bias[mh][s][1] = 1032.f * s_lo[1] + 72.f * s_hi[1];
+      }
+  }
+  // The staging area becomes a ring stage again only after every active warp is done with it.
+  asm volatile("bar.sync 1, %0;" ::"r"(active_warps * 32) : "memory");
+
+  // Adds the K chunks of tile jf in warp order (so the result does not depend on arrival order),
+  // frees the slot and writes the 16 x M results. Fragment order: vals[4 mh + c] is weight row
+  // g + 8 (c / 2), activation row 2 q + (c & 1) + 8 mh.
+  auto finalize = [&](int jf) -> bool {
+    const int slot = jf % kDecodeSlots;
+    const int tile = blockIdx.x + jf * gridDim.x;
+    if (!__all_sync(0xffffffffu, mbar_wait(pfull_bar(slot), (jf / kDecodeSlots) & 1, abort_flag))) {
+      *abort_flag = 1;
+      return false;
+    }
+    float vals[4 * MH];
+#pragma unroll
+    for (int c = 0; c < 4 * MH; ++c) vals[c] = 0.f;
+    for (int w2 = 0; w2 < active_warps; ++w2) {
+      const float4* src = reinterpret_cast<const float4*>(accs + ((slot * kDecodeWarps + w2) * 32 + lane) * 4 * MH);
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh) {
+        const float4 v = src[mh];
+        vals[4 * mh + 0] += v.x;
+        vals[4 * mh + 1] += v.y;
+        vals[4 * mh + 2] += v.z;
+        vals[4 * mh + 3] += v.w;
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(pempty_bar(slot));  // hand the slot to tile jf + kDecodeSlots
+    float* partial = scratch;
+    int* counters = reinterpret_cast<int*>(scratch + DecodeScratchLayout::partial_floats(N));
+    if (ksplit == 1) {
+#pragma unroll
+      for (int it = 0; it < 4 * MH; ++it) {
+        const int r = g + 8 * ((it >> 1) & 1), m = 2 * q + (it & 1) + 8 * (it >> 2);
+        if (m < M) out[static_cast<size_t>(m) * ldo + n_off + tile * kDecodeTileRows + r] = __float2half_rn(vals[it]);
+      }
+    } else {
+#pragma unroll
+      for (int it = 0; it < 4 * MH; ++it) {
+        const int r = g + 8 * ((it >> 1) & 1), m = 2 * q + (it & 1) + 8 * (it >> 2);
+        atomicAdd(&partial[static_cast<size_t>(m) * N + tile * kDecodeTileRows + r], vals[it]);
+      }
+      __threadfence();
+      __syncwarp();
+      int prior = 0;
+      if (lane == 0) prior = atomicAdd(&counters[tile], 1);
+      prior = __shfl_sync(0xffffffffu, prior, 0);
+      if (prior == ksplit - 1) {  // every K slice of this tile has been added
+        __threadfence();
+#pragma unroll
+        for (int it = 0; it < 4 * MH; ++it) {
+          const int r = g + 8 * ((it >> 1) & 1), m = 2 * q + (it & 1) + 8 * (it >> 2);
+          float* cell = &partial[static_cast<size_t>(m) * N + tile * kDecodeTileRows + r];
+          const float total = __ldcg(cell);
+          if (m < M) out[static_cast<size_t>(m) * ldo + n_off + tile * kDecodeTileRows + r] = __float2half_rn(total);
+          __stcg(cell, 0.f);  // leave the scratch clean for the next launch
+        }
+        if (lane == 0) counters[tile] = 0;
+      }
+    }
+    return true;
+  };
+
+  for (int j = 0; j < my_tiles; ++j) {
+    const int st = j % kDecodeStages;
+    if (!__all_sync(0xffffffffu, mbar_wait(wfull_bar(st), (j / kDecodeStages) & 1, abort_flag))) {
+      *abort_flag = 1;
+      break;
+    }
+    uint4 w[2][2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        w[s][h] = *reinterpret_cast<const uint4*>(wring + (st * kDecodeTileRows + g + 8 * h) * kDecodeRowPitch +
+                                                  warp * (kDecodeChunkK / 2) + 64 * s + 16 * q);
+    // the chunk's two groups are adjacent f16 in the row's scale vector
+    const uint8_t* stile = sring + st * kDecodeMaxScaleBytes + ((kc >> 7) << 1);
+    const uint32_t sc_lo = *reinterpret_cast<const uint32_t*>(stile + g * (groups_per_row << 1));
+    const uint32_t sc_hi = *reinterpret_cast<const uint32_t*>(stile + (g + 8) * (groups_per_row << 1));
+    __syncwarp();  // the whole warp has read this stage
+    if (lane == 0) mbar_arrive(wempty_bar(st));
+    // Refill: the stage that tile j - 1 used is free once every warp has read it, which is
+    // almost always already the case here.
+    if (warp == (j + kDecodeStages - 1) % active_warps && !produce(j + kDecodeStages - 1)) break;
+
+    float acc[MH][4];
+#pragma unroll
+    for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[mh][c] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      float dlo[MH][4], dhi[MH][4];
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dlo[mh][c] = dhi[mh][c] = 0.f;
+      const uint32_t wl[4] = {w[s][0].x, w[s][0].y, w[s][0].z, w[s][0].w};  // weight row g
+      const uint32_t wh[4] = {w[s][1].x, w[s][1].y, w[s][1].z, w[s][1].w};  // weight row g + 8
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t l8 = wl[i] >> 8, h8 = wh[i] >> 8;
+        const uint32_t lo_a = lop3_and_xor(wl[i], 0x000f000fu, 0x64086408u);  // (w0, w4) + 1032
+        const uint32_t lo_b = lop3_and_xor(wh[i], 0x000f000fu, 0x64086408u);
+        const uint32_t lo_c = lop3_and_xor(l8, 0x000f000fu, 0x64086408u);     // (w2, w6) + 1032
+        const uint32_t lo_d = lop3_and_xor(h8, 0x000f000fu, 0x64086408u);
+        const uint32_t hi_a = lop3_and_xor(wl[i], 0x00f000f0u, 0x64806480u);  // 16 (w1, w5) + 1152
+        const uint32_t hi_b = lop3_and_xor(wh[i], 0x00f000f0u, 0x64806480u);
+        const uint32_t hi_c = lop3_and_xor(l8, 0x00f000f0u, 0x64806480u);     // 16 (w3, w7) + 1152
+        const uint32_t hi_d = lop3_and_xor(h8, 0x00f000f0u, 0x64806480u);
+#pragma unroll
+        for (int mh = 0; mh < MH; ++mh) {
+          mma_m16n8k16(dlo[mh], lo_a, lo_b, lo_c, lo_d, bfrag[mh][s][i][0], bfrag[mh][s][i][2]);
+          mma_m16n8k16(dhi[mh], hi_a, hi_b, hi_c, hi_d, bfrag[mh][s][i][1], bfrag[mh][s][i][3]);
+        }
+      }
+      // One step is exactly one scale group of rows g and g + 8.
+      const float s_lo = __half2float(__ushort_as_half(static_cast<uint16_t>(s ? (sc_lo >> 16) : (sc_lo & 0xffff))));
+      const float s_hi = __half2float(__ushort_as_half(static_cast<uint16_t>(s ? (sc_hi >> 16) : (sc_hi & 0xffff))));
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float group_sum = fmaf(dhi[mh][c], 0.0625f, dlo[mh][c]) - bias[mh][s][c & 1];
+          acc[mh][c] = fmaf(c < 2 ? s_lo : s_hi, group_sum, acc[mh][c]);
+        }
+    }
+
+    // ---- leave this K chunk's partial sums in the tile's slot ------------------------------------
+    {
+      const int slot = j % kDecodeSlots;
+      if (!__all_sync(0xffffffffu, mbar_wait(pempty_bar(slot), ((j / kDecodeSlots) & 1) ^ 1, abort_flag))) {
+        *abort_flag = 1;
+        break;
+      }
+      float* part = accs + ((slot * kDecodeWarps + warp) * 32 + lane) * 4 * MH;
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh)
+        *reinterpret_cast<float4*>(part + 4 * mh) = make_float4(acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pfull_bar(slot));
+    }
+    // Tile j - 2 is finished off by warp (j - 2) % active_warps: by now every chunk has usually
+    // arrived, so the wait is short, and no warp needs an atomic's answer on its critical path.
+    if (j >= 2 && warp == (j - 2) % active_warps && !finalize(j - 2)) break;
   }
+  for (int jf = my_tiles > 2 ? my_tiles - 2 : 0; jf < my_tiles; ++jf)
+    if (warp == jf % active_warps && !finalize(jf)) break;
 }
 
 }  // namespace b200

@@ -54,10 +54,10 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
                                                              int32_t n_offset, void* stream) {
   if (!a || !wq || !scales || !out)
     return iree_b200_internal_set_error(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
-  if (M < 1 || M > 16 || N < 16 || (N % 16) || K < 256 || (K % 256)) {
+  if (M < 1 || M > 16 || N < 16 || (N % 16) || K < 256 || (K % 256) || K > 16384) {
     return iree_b200_internal_set_error(IREE_B200_STATUS_INVALID_ARGUMENT,
                                         "the no-allocation decode entry point needs 1 <= M <= 16, N a positive "
-                                        "multiple of 16 and K a positive multiple of 256 (group size 128)");
+                                        "multiple of 16 and K a multiple of 256 up to 16384 (group size 128)");
   }
   if (N > kMaxN) {
     char msg[256];
@@ -86,6 +86,13 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
       e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
       if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
       g_sm_count[device] = n > 0 ? n : 148;
+      // Raising the dynamic shared-memory limit is a function attribute, not an allocation.
+      e = cudaFuncSetAttribute(decode_noalloc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               b200::decode_smem_bytes(1));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(decode_noalloc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 b200::decode_smem_bytes(2));
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
       g_scratch_ptr[device] = p;
     }
     scratch = g_scratch_ptr[device];
@@ -108,11 +115,11 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
   if (gx > tiles) gx = tiles;
   const dim3 grid(gx, ksplit, 1), block(b200::kDecodeThreads, 1, 1);
   if (M <= 8) {
-    decode_noalloc_kernel<1><<<grid, block, 0, s>>>(static_cast<const __half*>(a), static_cast<const uint8_t*>(wq),
+    decode_noalloc_kernel<1><<<grid, block, b200::decode_smem_bytes(1), s>>>(static_cast<const __half*>(a), static_cast<const uint8_t*>(wq),
                                                     static_cast<const __half*>(scales), static_cast<__half*>(out),
                                                     static_cast<float*>(scratch), M, N, K, ldo, n_offset);
   } else {
-    decode_noalloc_kernel<2><<<grid, block, 0, s>>>(static_cast<const __half*>(a), static_cast<const uint8_t*>(wq),
+    decode_noalloc_kernel<2><<<grid, block, b200::decode_smem_bytes(2), s>>>(static_cast<const __half*>(a), static_cast<const uint8_t*>(wq),
                                                     static_cast<const __half*>(scales), static_cast<__half*>(out),
                                                     static_cast<float*>(scratch), M, N, K, ldo, n_offset);
   }

@@ -290,6 +290,31 @@ class Context:
     def w4a16_host(self, params: W4A16Params, a, wq, scales, out) -> None:
         check(library().iree_b200_w4a16_host(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out)))
 
+    @staticmethod
+    def _ptr_array(items):
+        arr = (C.c_void_p * len(items))()
+        for i, x in enumerate(items):
+            arr[i] = _vp(x).value
+        return arr
+
+    def matmul_run_sequence(self, params: MatmulParams, sets, tile_n: int, first: int, count: int) -> None:
+        """sets: list of (lhs, rhs, out, workspace, row_scale, col_scale); issued from C in one call."""
+        cols = list(zip(*sets))
+        scales = cols[4][0] is not None
+        check(library().iree_b200_matmul_run_sequence(
+            self.handle, C.byref(params), C.c_int32(len(sets)), self._ptr_array(cols[0]), self._ptr_array(cols[1]),
+            self._ptr_array(cols[2]), self._ptr_array(cols[4]) if scales else None,
+            self._ptr_array(cols[5]) if scales else None, self._ptr_array(cols[3]), C.c_int32(tile_n), C.c_int32(first),
+            C.c_int32(count)))
+
+    def w4a16_run_sequence(self, params: W4A16Params, sets, variant: int, tile_n: int, first: int, count: int) -> None:
+        """sets: list of (a, wq, scales, out, workspace)."""
+        cols = list(zip(*sets))
+        check(library().iree_b200_w4a16_run_sequence(
+            self.handle, C.byref(params), C.c_int32(len(sets)), self._ptr_array(cols[0]), self._ptr_array(cols[1]),
+            self._ptr_array(cols[2]), self._ptr_array(cols[3]), self._ptr_array(cols[4]), C.c_int32(variant),
+            C.c_int32(tile_n), C.c_int32(first), C.c_int32(count)))
+
     def encode_tensor_map(self, elem_bytes, is_bf16, ptr, dim0, dim1, dim2, box0, box1) -> bytes:
         out = C.create_string_buffer(128)
         check(library().iree_b200_encode_tensor_map(self.handle, C.c_int32(elem_bytes), C.c_int32(int(is_bf16)),

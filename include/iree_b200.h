@@ -61,6 +61,7 @@ typedef struct iree_hal_b200_device_t iree_hal_b200_device_t;
 typedef struct iree_hal_b200_executable_t iree_hal_b200_executable_t;
 typedef struct iree_hal_b200_command_buffer_t iree_hal_b200_command_buffer_t;
 typedef struct iree_hal_b200_channel_t iree_hal_b200_channel_t;
+typedef struct iree_hal_b200_graph_t iree_hal_b200_graph_t;
 
 /* ---- device -------------------------------------------------------------------------------
  * Stands in for iree_hal_cuda_driver_create + device creation
@@ -165,6 +166,19 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
 /* Number of kernel launches this command buffer has issued (for launch accounting). */
 uint64_t iree_hal_b200_command_buffer_launch_count(const iree_hal_b200_command_buffer_t* command_buffer);
 
+/* ---- graph mode ------------------------------------------------------------------------------------
+ * The CUDA-graph command buffer of the reference (--cuda_use_streams=false,
+ * runtime/src/iree/hal/drivers/cuda/graph_command_buffer.c:747-829): between begin_graph and
+ * end_graph every dispatch is recorded as a kernel node (same parameter packing), each node
+ * depending on the previous one; graph_execute replays the whole recording on the dispatch stream
+ * with one cuGraphLaunch. Collectives are not recordable here. */
+iree_b200_status_t iree_hal_b200_command_buffer_begin_graph(iree_hal_b200_command_buffer_t* command_buffer);
+iree_b200_status_t iree_hal_b200_command_buffer_end_graph(iree_hal_b200_command_buffer_t* command_buffer,
+                                                          iree_hal_b200_graph_t** out_graph);
+iree_b200_status_t iree_hal_b200_graph_execute(iree_hal_b200_command_buffer_t* command_buffer,
+                                               iree_hal_b200_graph_t* graph);
+void iree_hal_b200_graph_release(iree_hal_b200_graph_t* graph);
+
 /* ---- collective channel -------------------------------------------------------------------------
  * iree_hal_channel_create with explicit {id, rank, count}
  * (runtime/src/iree/hal/channel.h:40-108; cuda_device.c:439-530; nccl_channel.c:94-160) over
@@ -192,6 +206,17 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command
                                                            iree_hal_b200_channel_t* channel, int32_t element_type,
                                                            const void* send_device_ptr, void* recv_device_ptr,
                                                            size_t element_count);
+
+/* The same collective on the device's second stream: it starts when everything recorded before it
+ * has run, and dispatches recorded after it do not wait for it (the reference keeps a second
+ * stream beside the dispatch stream as well, cuda_device.c). join_collectives makes the dispatch
+ * stream wait for every overlapped collective issued so far; call it before a buffer that a
+ * collective reads or writes is reused, and before reading results. */
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather_overlapped(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                      iree_hal_b200_channel_t* channel,
+                                                                      int32_t element_type, const void* send_device_ptr,
+                                                                      void* recv_device_ptr, size_t element_count);
+iree_b200_status_t iree_hal_b200_command_buffer_join_collectives(iree_hal_b200_command_buffer_t* command_buffer);
 
 /* ------------------------------------------------------------------------------------------
  * Operator level: the contraction dispatches.

@@ -60,6 +60,7 @@ struct CudaSymbols {
   CU_FN(cuStreamCreate, CUstream*, unsigned)
   CU_FN(cuStreamDestroy, CUstream)
   CU_FN(cuStreamSynchronize, CUstream)
+  CU_FN(cuStreamWaitEvent, CUstream, CUevent, unsigned)
   CU_FN(cuMemAlloc, CUdeviceptr*, size_t)
   CU_FN(cuMemFree, CUdeviceptr)
   CU_FN(cuMemHostAlloc, void**, size_t, unsigned)
@@ -78,6 +79,12 @@ struct CudaSymbols {
   CU_FN(cuEventRecord, CUevent, CUstream)
   CU_FN(cuEventSynchronize, CUevent)
   CU_FN(cuEventElapsedTime, float*, CUevent, CUevent)
+  CU_FN(cuGraphCreate, CUgraph*, unsigned)
+  CU_FN(cuGraphDestroy, CUgraph)
+  CU_FN(cuGraphAddKernelNode, CUgraphNode*, CUgraph, const CUgraphNode*, size_t, const CUDA_KERNEL_NODE_PARAMS*)
+  CU_FN(cuGraphInstantiateWithFlags, CUgraphExec*, CUgraph, unsigned long long)
+  CU_FN(cuGraphLaunch, CUgraphExec, CUstream)
+  CU_FN(cuGraphExecDestroy, CUgraphExec)
   CU_FN(cuGetErrorName, CUresult, const char**)
   CU_FN(cuGetErrorString, CUresult, const char**)
   CU_FN(cuTensorMapEncodeTiled, CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -119,6 +126,7 @@ iree_b200_status_t ensure_cuda() {
       LOAD(cuStreamCreate, "cuStreamCreate")
       LOAD(cuStreamDestroy, "cuStreamDestroy_v2")
       LOAD(cuStreamSynchronize, "cuStreamSynchronize")
+      LOAD(cuStreamWaitEvent, "cuStreamWaitEvent")
       LOAD(cuMemAlloc, "cuMemAlloc_v2")
       LOAD(cuMemFree, "cuMemFree_v2")
       LOAD(cuMemHostAlloc, "cuMemHostAlloc")
@@ -136,6 +144,12 @@ iree_b200_status_t ensure_cuda() {
       LOAD(cuEventRecord, "cuEventRecord")
       LOAD(cuEventSynchronize, "cuEventSynchronize")
       LOAD(cuEventElapsedTime, "cuEventElapsedTime")
+      LOAD(cuGraphCreate, "cuGraphCreate")
+      LOAD(cuGraphDestroy, "cuGraphDestroy")
+      LOAD(cuGraphAddKernelNode, "cuGraphAddKernelNode_v2")
+      LOAD(cuGraphInstantiateWithFlags, "cuGraphInstantiateWithFlags")
+      LOAD(cuGraphLaunch, "cuGraphLaunch")
+      LOAD(cuGraphExecDestroy, "cuGraphExecDestroy")
       LOAD(cuGetErrorName, "cuGetErrorName")
       LOAD(cuGetErrorString, "cuGetErrorString")
       LOAD(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
@@ -364,6 +378,10 @@ struct iree_hal_b200_device_t {
   CUdevice device = 0;
   CUcontext context = nullptr;
   CUstream stream = nullptr;
+  // Second stream for collectives that may overlap later dispatches, with the two events that
+  // order it against the dispatch stream (created on first use).
+  CUstream collective_stream = nullptr;
+  CUevent dispatch_done = nullptr, collective_done = nullptr;
   int sm_count = 0, cc = 0, max_smem = 0;
   char name[128] = {0};
 };
@@ -380,8 +398,19 @@ struct iree_hal_b200_executable_t {
   std::vector<Entry> entries;
 };
 
+struct iree_hal_b200_graph_t {
+  iree_hal_b200_device_t* device = nullptr;
+  CUgraph graph = nullptr;
+  CUgraphExec exec = nullptr;
+  uint64_t kernel_nodes = 0;
+};
+
 struct iree_hal_b200_command_buffer_t {
   iree_hal_b200_device_t* device = nullptr;
+  // Graph mode: dispatches become kernel nodes chained one after the other instead of launches.
+  CUgraph recording = nullptr;
+  CUgraphNode last_node = nullptr;
+  uint64_t recorded_nodes = 0;
   uint32_t constants[IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT] = {0};
   void* bindings[IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT][IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT] = {{nullptr}};
   uint64_t launches = 0;
@@ -441,6 +470,12 @@ iree_b200_status_t iree_hal_b200_device_create(int32_t ordinal, iree_hal_b200_de
 void iree_hal_b200_device_release(iree_hal_b200_device_t* device) {
   if (!device) return;
   g_cu.cuCtxSetCurrent(device->context);
+  if (device->collective_stream) {
+    g_cu.cuStreamSynchronize(device->collective_stream);
+    g_cu.cuStreamDestroy(device->collective_stream);
+    g_cu.cuEventDestroy(device->dispatch_done);
+    g_cu.cuEventDestroy(device->collective_done);
+  }
   if (device->stream) {
     g_cu.cuStreamSynchronize(device->stream);
     g_cu.cuStreamDestroy(device->stream);
@@ -747,6 +782,29 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
   for (uint32_t i = 0; i < constant_count; ++i) params[binding_count + i] = &command_buffer->constants[i];
   iree_hal_b200_device_t* d = command_buffer->device;
   CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  if (command_buffer->recording) {
+    // Same parameter packing, recorded as a graph node (graph_command_buffer.c:747-829); the
+    // driver copies the parameter values when the node is added.
+    CUDA_KERNEL_NODE_PARAMS np;
+    memset(&np, 0, sizeof np);
+    np.func = e.fn;
+    np.gridDimX = workgroup_x;
+    np.gridDimY = workgroup_y;
+    np.gridDimZ = workgroup_z;
+    np.blockDimX = e.block[0];
+    np.blockDimY = e.block[1];
+    np.blockDimZ = e.block[2];
+    np.sharedMemBytes = e.smem;
+    np.kernelParams = params;
+    CUgraphNode node = nullptr;
+    CU_RETURN_IF_ERROR(g_cu.cuGraphAddKernelNode(&node, command_buffer->recording,
+                                                 command_buffer->last_node ? &command_buffer->last_node : nullptr,
+                                                 command_buffer->last_node ? 1 : 0, &np),
+                       "cuGraphAddKernelNode");
+    command_buffer->last_node = node;
+    ++command_buffer->recorded_nodes;
+    return IREE_B200_STATUS_OK;
+  }
   CU_RETURN_IF_ERROR(g_cu.cuLaunchKernel(e.fn, workgroup_x, workgroup_y, workgroup_z, e.block[0], e.block[1],
                                          e.block[2], e.smem, d->stream, params, nullptr),
                      e.name.c_str());
@@ -756,6 +814,55 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
 
 uint64_t iree_hal_b200_command_buffer_launch_count(const iree_hal_b200_command_buffer_t* command_buffer) {
   return command_buffer ? command_buffer->launches : 0;
+}
+
+// ---- graph mode -----------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_command_buffer_begin_graph(iree_hal_b200_command_buffer_t* command_buffer) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command buffer is NULL");
+  if (command_buffer->recording) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "a graph is already being recorded");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(command_buffer->device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuGraphCreate(&command_buffer->recording, 0), "cuGraphCreate");
+  command_buffer->last_node = nullptr;
+  command_buffer->recorded_nodes = 0;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_end_graph(iree_hal_b200_command_buffer_t* command_buffer,
+                                                          iree_hal_b200_graph_t** out_graph) {
+  if (!command_buffer || !out_graph) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  *out_graph = nullptr;
+  if (!command_buffer->recording) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "no graph is being recorded");
+  auto* g = new iree_hal_b200_graph_t();
+  g->device = command_buffer->device;
+  g->graph = command_buffer->recording;
+  g->kernel_nodes = command_buffer->recorded_nodes;
+  command_buffer->recording = nullptr;
+  command_buffer->last_node = nullptr;
+  iree_b200_status_t st = cu_check(g_cu.cuGraphInstantiateWithFlags(&g->exec, g->graph, 0), "cuGraphInstantiate");
+  if (st) {
+    g_cu.cuGraphDestroy(g->graph);
+    delete g;
+    return st;
+  }
+  *out_graph = g;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_graph_execute(iree_hal_b200_command_buffer_t* command_buffer,
+                                               iree_hal_b200_graph_t* graph) {
+  if (!command_buffer || !graph) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(graph->device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuGraphLaunch(graph->exec, graph->device->stream), "cuGraphLaunch");
+  command_buffer->launches += graph->kernel_nodes;
+  return IREE_B200_STATUS_OK;
+}
+
+void iree_hal_b200_graph_release(iree_hal_b200_graph_t* graph) {
+  if (!graph) return;
+  g_cu.cuCtxSetCurrent(graph->device->context);
+  if (graph->exec) g_cu.cuGraphExecDestroy(graph->exec);
+  if (graph->graph) g_cu.cuGraphDestroy(graph->graph);
+  delete graph;
 }
 
 // ---- channel ------------------------------------------------------------------------------------------
@@ -805,11 +912,9 @@ void iree_hal_b200_channel_release(iree_hal_b200_channel_t* channel) {
 int32_t iree_hal_b200_channel_rank(const iree_hal_b200_channel_t* channel) { return channel ? channel->rank : 0; }
 int32_t iree_hal_b200_channel_count(const iree_hal_b200_channel_t* channel) { return channel ? channel->count : 0; }
 
-iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command_buffer_t* command_buffer,
-                                                           iree_hal_b200_channel_t* channel, int32_t element_type,
-                                                           const void* send_device_ptr, void* recv_device_ptr,
-                                                           size_t element_count) {
-  if (!command_buffer || !channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+static iree_b200_status_t all_gather_on(iree_hal_b200_command_buffer_t* command_buffer, iree_hal_b200_channel_t* channel,
+                                        int32_t element_type, const void* send_device_ptr, void* recv_device_ptr,
+                                        size_t element_count, CUstream stream) {
   int nccl_type;  // ncclDataType_t values: int8 0, int32 2, float16 6, float32 7, bfloat16 9
   switch (element_type) {
     case IREE_HAL_B200_ELEMENT_TYPE_I8: nccl_type = 0; break;
@@ -819,14 +924,56 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command
     case IREE_HAL_B200_ELEMENT_TYPE_BF16: nccl_type = 9; break;
     default: return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unsupported collective element type %d", element_type);
   }
-  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(command_buffer->device->context), "cuCtxSetCurrent");
   // One collective per flush, inside a group like iree_hal_cuda_nccl_submit_batch (nccl_channel.c:542-585).
   B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclGroupStart(), "ncclGroupStart"));
-  iree_b200_status_t st = nccl_check(g_nccl.ncclAllGather(send_device_ptr, recv_device_ptr, element_count, nccl_type,
-                                                          channel->comm, command_buffer->device->stream),
-                                     "ncclAllGather");
+  iree_b200_status_t st = nccl_check(
+      g_nccl.ncclAllGather(send_device_ptr, recv_device_ptr, element_count, nccl_type, channel->comm, stream),
+      "ncclAllGather");
   iree_b200_status_t st2 = nccl_check(g_nccl.ncclGroupEnd(), "ncclGroupEnd");
   return st ? st : st2;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command_buffer_t* command_buffer,
+                                                           iree_hal_b200_channel_t* channel, int32_t element_type,
+                                                           const void* send_device_ptr, void* recv_device_ptr,
+                                                           size_t element_count) {
+  if (!command_buffer || !channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (command_buffer->recording)
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "collectives cannot be recorded into a graph");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(command_buffer->device->context), "cuCtxSetCurrent");
+  return all_gather_on(command_buffer, channel, element_type, send_device_ptr, recv_device_ptr, element_count,
+                       command_buffer->device->stream);
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather_overlapped(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                      iree_hal_b200_channel_t* channel,
+                                                                      int32_t element_type, const void* send_device_ptr,
+                                                                      void* recv_device_ptr, size_t element_count) {
+  if (!command_buffer || !channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (command_buffer->recording)
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "collectives cannot be recorded into a graph");
+  iree_hal_b200_device_t* d = command_buffer->device;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  if (!d->collective_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->collective_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->dispatch_done, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->collective_done, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  // The collective starts once everything recorded so far has run; later dispatches do not wait for it.
+  CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->dispatch_done, d->stream), "cuEventRecord");
+  CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->collective_stream, d->dispatch_done, 0), "cuStreamWaitEvent");
+  return all_gather_on(command_buffer, channel, element_type, send_device_ptr, recv_device_ptr, element_count,
+                       d->collective_stream);
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_join_collectives(iree_hal_b200_command_buffer_t* command_buffer) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command buffer is NULL");
+  iree_hal_b200_device_t* d = command_buffer->device;
+  if (!d->collective_stream) return IREE_B200_STATUS_OK;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->collective_done, d->collective_stream), "cuEventRecord");
+  CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->stream, d->collective_done, 0), "cuStreamWaitEvent");
+  return IREE_B200_STATUS_OK;
 }
 
 }  // extern "C"

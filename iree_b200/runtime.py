@@ -160,6 +160,21 @@ class Event:
         return float(ms.value)
 
 
+class Graph:
+    """A recorded sequence of dispatches replayed with one cuGraphLaunch."""
+
+    def __init__(self, ctx: "Context", handle):
+        self.ctx, self.handle = ctx, handle
+
+    def execute(self) -> None:
+        check(library().iree_hal_b200_graph_execute(self.ctx.command_buffer, self.handle))
+
+    def release(self) -> None:
+        if self.handle:
+            library().iree_hal_b200_graph_release(self.handle)
+            self.handle = None
+
+
 class Context:
     """Device + loaded contraction executable + command buffer (``iree_b200_context_t``)."""
 
@@ -195,6 +210,14 @@ class Context:
     @property
     def launch_count(self) -> int:
         return int(library().iree_hal_b200_command_buffer_launch_count(self.command_buffer))
+
+    def begin_graph(self) -> None:
+        check(library().iree_hal_b200_command_buffer_begin_graph(self.command_buffer))
+
+    def end_graph(self) -> Graph:
+        h = C.c_void_p()
+        check(library().iree_hal_b200_command_buffer_end_graph(self.command_buffer, C.byref(h)))
+        return Graph(self, h)
 
     def event(self) -> "Event":
         return Event(self)

@@ -62,15 +62,18 @@ def bench_state(ctx: rt.Context, wl, rank: int, world: int, channel):
         p = rt.W4A16Params(M, n_local, K, 128, n_local, 0, rt.W4A16_AUTO, 0)
         variant, tile_n = ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
         sets.append((p, da, dw, ds, dc, ws, variant, tile_n))
-    gather = ctx.alloc(world * M * n_local * 2) if channel is not None else None
+    gathers = [ctx.alloc(world * M * n_local * 2) for _ in sets] if channel is not None else None
 
     def step(i):
         p, da, dw, ds, dc, ws, variant, tile_n = sets[i % n_sets]
+        if channel is not None and i % n_sets == 0:
+            rt.check(lib.iree_hal_b200_command_buffer_join_collectives(ctx.command_buffer))
         ctx.w4a16_run(p, da, dw, ds, dc, ws, variant, tile_n)
         if channel is not None:
-            rt.check(lib.iree_hal_b200_command_buffer_all_gather(ctx.command_buffer, channel, C.c_int32(1),
-                                                                 C.c_void_p(dc.ptr), C.c_void_p(gather.ptr),
-                                                                 C.c_size_t(M * n_local)))
+            # overlaps the following dispatches on the device's second stream
+            rt.check(lib.iree_hal_b200_command_buffer_all_gather_overlapped(
+                ctx.command_buffer, channel, C.c_int32(1), C.c_void_p(dc.ptr), C.c_void_p(gathers[i % n_sets].ptr),
+                C.c_size_t(M * n_local)))
 
     def check():
         for x in sets:

@@ -235,3 +235,33 @@ def test_api_argument_errors(ctx):
     with pytest.raises(ib.IreeB200Error) as e:
         ctx.dispatch("no_such_export", [], [], (1, 1, 1))
     assert e.value.code_name == "NOT_FOUND"
+
+
+def test_graph_mode_replays_recorded_dispatches(ctx):
+    """Graph command-buffer mode: dispatches recorded between begin_graph / end_graph run only
+    when the graph executes, in order, and give the stream-mode result."""
+    rng = np.random.default_rng(8)
+    M, N, K = 256, 384, 512
+    a = small_ints(rng, ib.KIND_F16, (M, K)); b = small_ints(rng, ib.KIND_F16, (K, N))
+    da, db = ctx.to_device(a), ctx.to_device(b)
+    c1, c2 = ctx.alloc(M * N * 2).fill(0), ctx.alloc(M * N * 2).fill(0)
+    ws = ctx.workspace()
+    p = MatmulParams(ib.KIND_F16, ib.EPILOGUE_CAST, M, N, K, 1, ib.RHS_KN, 0, 0)
+    bn = ctx.matmul_prepare(p, da, db, ws)
+    before = ctx.launch_count
+    ctx.begin_graph()
+    ctx.matmul_run(p, da, db, c1, ws, bn)
+    ctx.matmul_run(p, da, db, c2, ws, bn)
+    graph = ctx.end_graph()
+    ctx.synchronize()
+    assert not c1.download(np.uint16, (M, N)).any()          # recorded, not executed
+    assert ctx.launch_count == before
+    graph.execute()
+    ctx.workspace_status(ws)
+    want = (a.astype(np.float64) @ b.astype(np.float64))
+    for c in (c1, c2):
+        assert (c.download(np.float16, (M, N)).astype(np.float64) == want).all()
+    assert ctx.launch_count == before + 2
+    graph.release()
+    for x in (da, db, c1, c2, ws):
+        x.free()

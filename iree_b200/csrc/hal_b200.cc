@@ -1088,8 +1088,10 @@ int choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_matmul_params_
     if (p->tile_n && bn != p->tile_n) continue;
     const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn) * p->batch;
     const int64_t waves = (tiles + sms - 1) / sms;
-    // Time model: every wave costs (fixed + bn) units; padding columns are wasted work.
-    const double cost = static_cast<double>(waves) * (48.0 + bn);
+    // Time model fitted on 4096^3 f16 (wave time 25.0 / 22.3 / 20.3 us at tile widths 256 / 192 / 128):
+    // a wave costs (400 + bn) units, i.e. narrow tiles are far from proportionally cheaper because the
+    // A tile is re-fetched per tile and the operand traffic per flop grows.
+    const double cost = static_cast<double>(waves) * (400.0 + bn);
     const double score = 1.0 / cost;
     if (score > best_score * 1.0001) {
       best_score = score;
@@ -1396,7 +1398,7 @@ static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a1
     if (p->tile_n && bn != p->tile_n) continue;
     const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn);
     const int64_t waves = (tiles + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * (48.0 + bn);
+    const double cost = static_cast<double>(waves) * (400.0 + bn);
     if (!best || cost < best_cost * 0.9999) {
       best = bn;
       best_cost = cost;

@@ -1,0 +1,136 @@
+"""``iree-run-module``-shaped command line over a host plan (``iree_b200.dispatch_gen.Plan``).
+
+    python -m iree_b200.run_module --device=cuda --module=plan.json --function=c2 \
+        --input=4096x4096xf16=@lhs.npy --input=4096x4096xf16=@rhs.npy \
+        [--output=@out.npy] [--expected_output=4096x4096xf16=@want.npy] [--print_statistics]
+
+Flag names, the ``EXEC @function`` line, the ``SHAPExTYPE=@file.npy`` input grammar and the
+non-zero exit code on a mismatch follow runtime/src/iree/tooling/run_module.c:23-91,199-322. A real
+.vmfb needs IREE's bytecode VM, which is outside this repository; the module here is the plan
+(exports, bindings, push constants, grids) plus the cubin, executed through the same HAL calls a
+compiled program makes: executable create from an ExecutableDef, push constants, push descriptor
+set, dispatch. Only ``--device=cuda`` exists: there is no CPU path.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import numpy as np
+
+from . import runtime as rt
+from .dispatch_gen import Plan
+
+_DTYPES = {"f16": np.float16, "bf16": np.uint16, "i8": np.int8, "si8": np.int8, "ui8": np.uint8, "i32": np.int32,
+           "f32": np.float32}
+
+
+def parse_tensor_flag(text: str):
+    """``4096x4096xf16=@file.npy`` or ``2x2xi8=1 2 3 4`` -> ndarray (hal/string_util.c grammar)."""
+    spec, _, value = text.partition("=")
+    parts = spec.split("x")
+    dtype = _DTYPES[parts[-1]]
+    shape = tuple(int(p) for p in parts[:-1])
+    if value.startswith("@"):
+        arr = np.load(value[1:]) if value.endswith(".npy") else np.fromfile(value[1:], dtype=dtype)
+        arr = np.ascontiguousarray(arr).view(dtype).reshape(shape)
+    else:
+        vals = value.replace(",", " ").split()
+        arr = (np.full(shape, dtype(float(vals[0]))) if len(vals) == 1 else np.array([float(v) for v in vals])).astype(
+            dtype).reshape(shape)
+    return arr
+
+
+def execute_plan(ctx: rt.Context, plan: Plan, inputs):
+    """Runs every dispatch of the plan through the raw HAL-level calls; returns the outputs."""
+    if len(inputs) != len(plan.inputs):
+        raise rt.IreeB200Error(3, "function expects %d inputs, %d given" % (len(plan.inputs), len(inputs)))
+    buffers, owned = {}, []
+    for decl, arr in zip(plan.inputs, inputs):
+        if list(arr.shape) != list(decl["shape"]):
+            raise rt.IreeB200Error(3, "input %s: expected shape %s, got %s" % (decl["name"], decl["shape"], list(arr.shape)))
+        buffers[decl["name"]] = ctx.to_device(arr)
+    for decl in plan.outputs:
+        n = int(np.prod(decl["shape"])) * np.dtype(_DTYPES[decl["dtype"]]).itemsize
+        buffers[decl["name"]] = ctx.alloc(max(n, 1))
+    for t in plan.transients:
+        buf = ctx.alloc(t["bytes"])
+        if t.get("zero"):
+            buf.fill(0)
+        if t.get("templates"):
+            kind = t["templates"]
+            es = 1 if kind == "i8" else 2
+            host = b"".join(ctx.encode_tensor_map(es, kind == "bf16", buf, 128 // es * 4, 256, 1, 128 // es, 64)
+                            for _ in range(2))
+            buf.upload(np.frombuffer(host, np.uint8))
+        buffers[t["name"]] = buf
+        if "host_tensor_maps" in t:
+            _host_tensor_maps(ctx, t["host_tensor_maps"], buffers, buf)
+    for d in plan.dispatches:
+        ctx.dispatch(d.export, [buffers[b] for b in d.bindings], d.constants, d.grid)
+    if "workspace" in buffers:
+        ctx.workspace_status(buffers["workspace"])
+    ctx.synchronize()
+    outs = [buffers[o["name"]].download(_DTYPES[o["dtype"]], tuple(o["shape"])) for o in plan.outputs]
+    for b in buffers.values():
+        b.free()
+    return outs
+
+
+def _host_tensor_maps(ctx, spec, buffers, ws):
+    if spec["kind"] == "w4a16":
+        p = rt.W4A16Params(spec["M"], spec["N"], spec["K"], 128, spec["N"], 0, rt.W4A16_GEMM, spec["tile_n"])
+        ctx.w4a16_prepare(p, buffers["a"], buffers["wq"], buffers["scales"], buffers["out"], ws)
+    else:
+        kind = {"f16": rt.KIND_F16, "bf16": rt.KIND_BF16, "i8": rt.KIND_I8}[spec["kind"]]
+        p = rt.MatmulParams(kind, rt.EPILOGUE_ACCUMULATOR if kind == rt.KIND_I8 else rt.EPILOGUE_CAST, spec["M"],
+                            spec["N"], spec["K"], spec["batch"], spec["layout"], spec["tile_n"], 0)
+        ctx.matmul_prepare(p, buffers["lhs"], buffers["rhs"], ws)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="iree_b200.run_module", allow_abbrev=False)
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--module", required=True)
+    ap.add_argument("--function", default="")
+    ap.add_argument("--input", action="append", default=[])
+    ap.add_argument("--output", action="append", default=[])
+    ap.add_argument("--expected_output", action="append", default=[])
+    ap.add_argument("--print_statistics", action="store_true")
+    args = ap.parse_args(argv)
+    if not args.device.startswith("cuda"):
+        print("only --device=cuda is available (no CPU path)", file=sys.stderr)
+        return 2
+    plan = Plan.from_json(open(args.module).read())
+    if args.function and args.function != plan.function:
+        print("NOT_FOUND: no function @%s in the module (it holds @%s)" % (args.function, plan.function), file=sys.stderr)
+        return 1
+    inputs = [parse_tensor_flag(t) for t in args.input]
+    ordinal = int(args.device.split(":")[1]) if ":" in args.device else 0
+    ctx = rt.Context(ordinal)
+    try:
+        print("EXEC @%s" % plan.function)
+        outs = execute_plan(ctx, plan, inputs)
+        for i, o in enumerate(outs):
+            if i < len(args.output) and args.output[i].startswith("@"):
+                np.save(args.output[i][1:], o)
+            else:
+                print("result[%d]: hal.buffer_view\n%sx%s=%s ..." % (i, "x".join(map(str, o.shape)), plan.outputs[i]["dtype"],
+                                                                   " ".join(str(v) for v in o.reshape(-1)[:8])))
+        rc = 0
+        for i, text in enumerate(args.expected_output):
+            want = parse_tensor_flag(text)
+            ok = (outs[i] == want).all() if outs[i].dtype.kind in "iu" else np.allclose(
+                outs[i].astype(np.float32), want.astype(np.float32), rtol=1e-2, atol=1e-2)
+            print("[SUCCESS] all function outputs matched their expected values." if ok
+                  else "[FAILED] result[%d]: element mismatch" % i)
+            rc |= 0 if ok else 1
+        if args.print_statistics:
+            print("[[ statistics ]] kernel launches: %d" % ctx.launch_count)
+        return rc
+    finally:
+        ctx.close()
+
+
+if __name__ == "__main__":
+    sys.exit(main())

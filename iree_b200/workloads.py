@@ -73,10 +73,10 @@ def c4_w4a16(M, N=11008, K=4096, group=128, seed=3):
 
 def c5_w4a16_sharded(M, world=1, rank=0, N=28672, K=8192, group=128, seed=4):
     """Llama-70B-shaped W4A16; rank r owns weight rows [r*N/world, (r+1)*N/world)."""
+    from .sharding import shard_weights
     a, wq, s = c4_w4a16(M, N=N, K=K, group=group, seed=seed)
-    assert N % world == 0
-    n0, n1 = rank * N // world, (rank + 1) * N // world
-    return a, wq[n0:n1], s[n0:n1]
+    wq_r, s_r = shard_weights(wq, s, world, rank)
+    return a, wq_r, s_r
 
 
 def small_int_matrix(rng, shape, dtype, lo, hi):

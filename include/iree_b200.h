@@ -245,6 +245,8 @@ enum {
 enum {
   IREE_B200_FLAG_FORCE_GENERIC = 1,      /* use the shape-agnostic SIMT kernel */
   IREE_B200_FLAG_DEVICE_TENSORMAPS = 2,  /* build the tensor maps with the b200_encode_tensormaps dispatch */
+  IREE_B200_FLAG_PAIR_CTAS = 4,          /* force the CTA-pair kernels (256-row tiles, cta_group::2) */
+  IREE_B200_FLAG_SINGLE_CTA = 8,         /* force the single-CTA kernels (128-row tiles) */
 };
 #define IREE_B200_WORKSPACE_BYTES 512
 

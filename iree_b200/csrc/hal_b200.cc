@@ -1004,6 +1004,12 @@ const EntryDecl kEntries[] = {
     {"b200_matmul_bf16_f32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_matmul_i8_i32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_matmul_i8_requant_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_pair_f16_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_pair_f16_f32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_pair_bf16_bf16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_pair_bf16_f32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_pair_i8_i32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
+    {"b200_matmul_pair_i8_requant_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_encode_tensormaps", {32, 1, 1}, 0},
     {"b200_selftest_wait_timeout", {32, 1, 1}, 0},
     {"b200_matmul_generic_f16_f16", {16, 16, 1}, 0},
@@ -1036,6 +1042,19 @@ struct iree_b200_context_t {
 namespace {
 
 int elem_bytes_of(int kind) { return kind == IREE_B200_KIND_I8 ? 1 : 2; }
+
+const char* pair_export_name(int kind, int epilogue) {
+  if (kind == IREE_B200_KIND_F16 && epilogue == IREE_B200_EPILOGUE_CAST) return "b200_matmul_pair_f16_f16";
+  if (kind == IREE_B200_KIND_F16 && epilogue == IREE_B200_EPILOGUE_ACCUMULATOR) return "b200_matmul_pair_f16_f32";
+  if (kind == IREE_B200_KIND_BF16 && epilogue == IREE_B200_EPILOGUE_CAST) return "b200_matmul_pair_bf16_bf16";
+  if (kind == IREE_B200_KIND_BF16 && epilogue == IREE_B200_EPILOGUE_ACCUMULATOR) return "b200_matmul_pair_bf16_f32";
+  if (kind == IREE_B200_KIND_I8 && epilogue == IREE_B200_EPILOGUE_ACCUMULATOR) return "b200_matmul_pair_i8_i32";
+  if (kind == IREE_B200_KIND_I8 && epilogue == IREE_B200_EPILOGUE_REQUANT_F16) return "b200_matmul_pair_i8_requant_f16";
+  return nullptr;
+}
+
+// CTA pairs (256 x tile_n tiles) pay off when there are enough 256-row tiles to fill the SM pairs.
+bool use_pairs(const iree_b200_context_t* ctx, const iree_b200_matmul_params_t* p);
 
 const char* export_name(int kind, int epilogue, bool generic) {
   if (kind == IREE_B200_KIND_F16 && epilogue == IREE_B200_EPILOGUE_CAST)
@@ -1076,11 +1095,21 @@ bool tma_eligible(const iree_b200_matmul_params_t* p, const void* lhs, const voi
 
 // Tile width: the widest tile that still gives every SM work, weighing wave quantisation
 // against the lower efficiency of narrow tiles.
+bool use_pairs(const iree_b200_context_t* ctx, const iree_b200_matmul_params_t* p) {
+  if (p->flags & IREE_B200_FLAG_SINGLE_CTA) return false;
+  if (p->flags & IREE_B200_FLAG_PAIR_CTAS) return true;
+  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const int64_t tiles = static_cast<int64_t>((p->M + 255) / 256) * ((p->N + 255) / 256) * p->batch;
+  return p->M >= 256 && tiles >= sms / 2 && p->K >= 512;
+}
+
 int choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_matmul_params_t* p) {
   const int es = elem_bytes_of(p->kind);
-  const int chunk = (p->rhs_layout == IREE_B200_RHS_KN) ? 128 / es : 32;
-  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
-  const int64_t tiles_m = (p->M + 127) / 128;
+  const bool pairs = use_pairs(ctx, p);
+  // In pair mode each CTA holds half a tile: the half must be whole 128-byte column chunks.
+  const int chunk = (p->rhs_layout == IREE_B200_RHS_KN) ? (pairs ? 2 : 1) * 128 / es : (pairs ? 64 : 32);
+  const int sms = (ctx->device->sm_count > 0 ? ctx->device->sm_count : 148) / (pairs ? 2 : 1);
+  const int64_t tiles_m = (p->M + (pairs ? 255 : 127)) / (pairs ? 256 : 128);
   int best = 0;
   double best_score = -1;
   for (int bn = 256; bn >= 32; bn -= 32) {
@@ -1226,7 +1255,8 @@ iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const 
         {1, const_cast<void*>(rhs)},
         {2, static_cast<uint8_t*>(context->templates) + 2 * t * 128},
         {3, workspace}};
-    const int32_t constants[7] = {params->M, params->N, params->K, params->batch, params->rhs_layout, bn, es};
+    const int32_t constants[7] = {params->M, params->N, params->K, params->batch, params->rhs_layout,
+                                  use_pairs(context, params) ? bn / 2 : bn, es};
     auto* cb = context->command_buffer;
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
@@ -1238,7 +1268,8 @@ iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const 
   const int bf = params->kind == IREE_B200_KIND_BF16;
   B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, lhs, K, M, B, bk, 128, host));
   if (params->rhs_layout == IREE_B200_RHS_NK) {
-    B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, K, N, B, bk, bn, host + 128));
+    B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, K, N, B, bk,
+                                                     use_pairs(context, params) ? bn / 2 : bn, host + 128));
   } else {
     B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, N, K, B, bk, bk, host + 128));
   }
@@ -1258,8 +1289,10 @@ iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the requant epilogue needs row and column scales");
   auto* cb = context->command_buffer;
   const bool generic = !tma_eligible(params, lhs, rhs) || !params->K;
-  const int32_t ord = iree_hal_b200_executable_lookup(context->executable,
-                                                      export_name(params->kind, params->epilogue, generic));
+  const bool pairs = !generic && use_pairs(context, params);
+  const int32_t ord = iree_hal_b200_executable_lookup(
+      context->executable, pairs ? pair_export_name(params->kind, params->epilogue)
+                                 : export_name(params->kind, params->epilogue, generic));
   if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export missing from the executable");
   if (generic) {
     iree_hal_b200_descriptor_set_binding_t bindings[5] = {{0, const_cast<void*>(lhs)},
@@ -1275,9 +1308,17 @@ iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree
   }
   if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
   if (tile_n <= 0) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "run() needs the tile_n that prepare() returned");
-  const int64_t tiles = static_cast<int64_t>((params->M + 127) / 128) * ((params->N + tile_n - 1) / tile_n) * params->batch;
   const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
-  const uint32_t grid = static_cast<uint32_t>(tiles < sms ? tiles : sms);
+  uint32_t grid;
+  if (pairs) {
+    const int64_t tiles =
+        static_cast<int64_t>((params->M + 255) / 256) * ((params->N + tile_n - 1) / tile_n) * params->batch;
+    grid = 2u * static_cast<uint32_t>(tiles < sms / 2 ? tiles : sms / 2);  // whole pairs only
+  } else {
+    const int64_t tiles =
+        static_cast<int64_t>((params->M + 127) / 128) * ((params->N + tile_n - 1) / tile_n) * params->batch;
+    grid = static_cast<uint32_t>(tiles < sms ? tiles : sms);
+  }
   const int32_t constants[6] = {params->M, params->N, params->K, params->batch, params->rhs_layout, tile_n};
   if (requant) {
     iree_hal_b200_descriptor_set_binding_t bindings[4] = {

@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 KIND_F16, KIND_BF16, KIND_I8 = 0, 1, 2
 EPILOGUE_CAST, EPILOGUE_ACCUMULATOR, EPILOGUE_REQUANT_F16 = 0, 1, 2
 RHS_KN, RHS_NK = 0, 1
-FLAG_FORCE_GENERIC, FLAG_DEVICE_TENSORMAPS = 1, 2
+FLAG_FORCE_GENERIC, FLAG_DEVICE_TENSORMAPS, FLAG_PAIR_CTAS, FLAG_SINGLE_CTA = 1, 2, 4, 8
 WORKSPACE_BYTES = 512
 
 _STATUS_NAMES = {0: "OK", 1: "CANCELLED", 2: "UNKNOWN", 3: "INVALID_ARGUMENT", 4: "DEADLINE_EXCEEDED",

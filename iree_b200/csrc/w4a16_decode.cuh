@@ -145,17 +145,30 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int ksplit = gridDim.y;
-  const int k_slice0 = blockIdx.y * kDecodeSliceK;
-  const int kc = k_slice0 + warp * kDecodeChunkK;  // this warp's K chunk (K is a multiple of 256)
   const int groups_per_row = K >> 7;
   const int row_bytes = K >> 1;
   const int num_tiles = N / kDecodeTileRows;
-  int active_warps = (K - k_slice0) / kDecodeChunkK;  // K chunks in this CTA's slice
+  // K beyond one slice (4096) is covered either by several passes of this CTA over its tiles
+  // (gridDim.y == 1: partial sums wait in the f32 scratch between passes; nobody else touches
+  // them, so no atomics and no fences) or by splitting the slices over gridDim.y CTAs (global
+  // atomics plus an arrival counter per tile).
+  const int ksplit = gridDim.y;
+  const int num_slices = (K + kDecodeSliceK - 1) / kDecodeSliceK;
+  const int num_passes = ksplit == 1 ? num_slices : 1;
+  bool dead = false;  // a wait ran out: skip the work, keep meeting the CTA-wide barriers
+
+  for (int pass = 0; pass < num_passes; ++pass) {
+  const int k_slice0 = (ksplit == 1 ? pass : static_cast<int>(blockIdx.y)) * kDecodeSliceK;
+  const int kc = k_slice0 + warp * kDecodeChunkK;  // this warp's K chunk (K is a multiple of 256)
+  int active_warps = (K - k_slice0) / kDecodeChunkK;  // K chunks in this slice
   if (active_warps > kDecodeWarps) active_warps = kDecodeWarps;
   const uint32_t slice_row_bytes = active_warps * (kDecodeChunkK / 2);
+  const bool first_pass = pass == 0, last_pass = pass == num_passes - 1;
 
+  __syncthreads();  // every warp is done with the previous pass (and its global partial sums)
   if (threadIdx.x == 0) {
+    if (pass > 0)  // the barriers of the previous pass are quiescent: retire them before re-use
+      for (int i = 0; i < 2 * kDecodeStages + 2 * kDecodeSlots; ++i) mbar_inval(bars + 8u * i);
     for (int i = 0; i < kDecodeStages; ++i) {
       mbar_init(wfull_bar(i), 1);
       mbar_init(wempty_bar(i), active_warps);
@@ -164,11 +177,11 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
       mbar_init(pfull_bar(i), active_warps);
       mbar_init(pempty_bar(i), 1);
     }
-    *abort_flag = 0;
+    if (pass == 0) *abort_flag = 0;
     mbar_fence_init();
   }
   __syncthreads();
-  if (warp >= active_warps) return;  // nothing below synchronises the whole CTA
+  if (warp >= active_warps || dead || *abort_flag) continue;
 
   const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
@@ -294,7 +307,15 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
 #pragma unroll
       for (int it = 0; it < 4 * MH; ++it) {
         const int r = g + 8 * ((it >> 1) & 1), m = 2 * q + (it & 1) + 8 * (it >> 2);
-        if (m < M) out[static_cast<size_t>(m) * ldo + n_off + tile * kDecodeTileRows + r] = __float2half_rn(vals[it]);
+        float* cell = &partial[static_cast<size_t>(m) * N + tile * kDecodeTileRows + r];
+        float total = vals[it];
+        if (!first_pass) total += __ldcg(cell);      // what the earlier K slices left here
+        if (!last_pass) {
+          __stcg(cell, total);
+        } else {
+          if (num_passes > 1) __stcg(cell, 0.f);     // leave the scratch clean for the next launch
+          if (m < M) out[static_cast<size_t>(m) * ldo + n_off + tile * kDecodeTileRows + r] = __float2half_rn(total);
+        }
       }
     } else {
 #pragma unroll
@@ -409,6 +430,8 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   }
   for (int jf = my_tiles > 2 ? my_tiles - 2 : 0; jf < my_tiles; ++jf)
     if (warp == jf % active_warps && !finalize(jf)) break;
+  if (*abort_flag) dead = true;
+  }  // pass
 }
 
 }  // namespace b200

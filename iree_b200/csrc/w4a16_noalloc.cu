@@ -100,8 +100,8 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
   }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int ksplit = (K + 4095) / 4096;
-  if (ksplit > 1) {
+  const int ksplit = 1;  // K beyond 4096 is covered by passes inside the kernel
+  if (K > 4096) {
     // Every call shares the array and it keeps what the last call left there. The kernel zeroes
     // what it used, but a call that was cut short would not have, so the part this call will
     // use is cleared first: the partial sums [16][N] and the counters that follow them.

@@ -248,6 +248,8 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
       const bool row_live = r < bn;
       const __half* srow = scales + static_cast<size_t>(n < N ? n : 0) * (K >> 7);
       __half2 s2 = __half2half2(__float2half_rn(0.f));
+      // The scale of the next group is fetched one group ahead so that its latency is hidden.
+      __half next_scale = (row_live && n < N) ? srow[0] : __float2half_rn(0.f);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int rs = raw_it % kW4RawStages;
         if ((kb & 1) == 0) {
@@ -260,7 +262,8 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
             ok = false;
             break;
           }
-          if (row_live && n < N) s2 = __half2half2(srow[kb >> 1]);
+          s2 = __half2half2(next_scale);
+          if (row_live && n < N && kb + 2 < num_kb) next_scale = srow[(kb >> 1) + 1];
         }
         const int st = it % kW4Stages;
         const uint32_t ph = (it / kW4Stages) & 1;

@@ -80,6 +80,18 @@ def workloads():
                                          "C5: Llama-70B-shaped W4A16 M=%d N=28672 K=8192 sharded along N, seed 4" % m,
                                          "GB/s" if m <= 16 else "TFLOP/s", "hbm" if m <= 16 else "tensor", "f16",
                                          M=m, N=28672, K=8192, sharded=True)
+    # Data-tiled entry points (the micro kernels llvm-cpu's matmul is made of), on operands of the configurations above.
+    w["f2_pack_rhs_c3"] = Workload("f2_pack_rhs_c3", "tiling", "pack of the C3 int8 weight matrix [4096, 11008] into RHS "
+                                   "tiles [688, 2048, 16, 2] (transpose inner + outer)", "GB/s", "hbm", "u8", op="pack",
+                                   M=0, N=11008, K=4096)
+    w["f2_unpack_acc_c2"] = Workload("f2_unpack_acc_c2", "tiling", "unpack of a C2-sized f32 accumulator [256, 256, 16, 16] "
+                                     "to row-major [4096, 4096]", "GB/s", "hbm", "u32", op="unpack", M=4096, N=4096, K=0)
+    w["f2_mmt4d_c1"] = Workload("f2_mmt4d_c1", "tiling", "mmt4d s8s8s32 on C1-sized tiled operands [64, 512, 16, 2] x "
+                                "[64, 512, 16, 2] -> [64, 64, 16, 16]", "TOP/s", "tensor", "i8", op="mmt4d",
+                                M=1024, N=1024, K=1024)
+    w["f2_mmt4d_c3_m512"] = Workload("f2_mmt4d_c3_m512", "tiling", "mmt4d s8s8s32 on C3-sized tiled operands, M=512 "
+                                     "N=11008 K=4096 in 16x16x2 tiles", "TOP/s", "tensor", "i8", op="mmt4d",
+                                     M=512, N=11008, K=4096)
     return w
 
 
@@ -168,7 +180,34 @@ def cpu_arm(wl, steps=1, warmup=0):
     from iree_b200 import workloads as gen
     cores = os.cpu_count() or 1
     kind = "reference" if oracle.have_ref() else "port"
-    if wl.family == "matmul":
+    if wl.family == "tiling":
+        from iree_b200 import data_tiling
+        arrays = data_tiling.operands(wl)
+        use_ref = oracle.have_ref()
+        kind, cores = ("reference" if use_ref else "port"), 1
+        sample = "the whole operation through %s, 1 thread" % (
+            "the reference's iree_uk_%s" % wl.op if use_ref else "the plain-C restatement")
+        if wl.op == "pack":
+            K, N = arrays[0].shape
+            fn = oracle.pack_ref if use_ref else oracle.pack_port
+
+            def once():
+                fn(arrays[0], (N // 16, K // 2, 16, 2), True, True)
+            ops_per, byts_per = 0.0, 2.0 * arrays[0].nbytes
+        elif wl.op == "unpack":
+            fn = oracle.unpack_ref if use_ref else oracle.unpack_port
+
+            def once():
+                fn(arrays[0], (wl.M, wl.N))
+            ops_per, byts_per = 0.0, 2.0 * arrays[0].nbytes
+        else:
+            fn = oracle.mmt4d_ref if use_ref else oracle.mmt4d_port
+
+            def once():
+                fn(oracle.TYPE_S8S8S32, arrays[0], arrays[1])
+            ops_per = 2.0 * wl.M * wl.N * wl.K
+            byts_per = float(arrays[0].nbytes + arrays[1].nbytes + wl.M * wl.N * 4)
+    elif wl.family == "matmul":
         t = oracle.TYPE_S8S8S32 if wl.kind == 2 else oracle.TYPE_F16F16F32
         rng = np.random.default_rng(1)
         M, N, K = wl.M, wl.N, wl.K
@@ -341,6 +380,14 @@ def run_b200(args, wl):
         workload_desc = wl.desc + ("; weak scaling: every rank runs its own N-slice of an N=%d*%d problem and the f16 "
                                    "outputs are all-gathered through the channel" % (wl.N, world) if world > 1 else "")
         l2_note = "operands rotate over %d sets (%.0f MB > 126 MB L2)" % (n_sets, n_sets * set_bytes / 1e6)
+    elif wl.family == "tiling":
+        from iree_b200 import data_tiling
+        if world > 1:
+            raise SystemExit("the data-tiling workloads are single-GPU (replicas only)")
+        state = data_tiling.bench_state(ctx, wl)
+        step, check, e2e_step = state.step, state.check, state.e2e_step
+        ops, byts, h2d, d2h = state.ops, state.bytes, state.h2d, state.d2h
+        workload_desc, l2_note = state.desc, state.l2_note
     else:
         from iree_b200 import w4a16 as w4
         state = w4.bench_state(ctx, wl, rank, world, channel)

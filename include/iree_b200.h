@@ -347,6 +347,57 @@ iree_b200_status_t iree_b200_w4a16_run_sequence(iree_b200_context_t* context, co
                                                 const void* const* scales, void* const* out, void* const* workspace,
                                                 int32_t variant, int32_t tile_n, int32_t first, int32_t count);
 
+/* ---- data-tiled entry points: pack / unpack / mmt4d -------------------------------------------
+ *
+ * The GPU counterparts of the three micro kernels llvm-cpu's data-tiled matmul is made of. The
+ * argument lists are the reference's (runtime/src/iree/builtins/ukernel/pack.h:26-34,
+ * unpack.h:17-25, mmt4d.h:14-21) with a context in front instead of `cpu_data` behind; buffers
+ * are device pointers, sizes / strides / offsets are in elements, flags carry the reference's
+ * bit values (exported_bits.h:29-83). Work is enqueued on the context's stream. */
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_MASK 0xFF
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_S8S8S32 0x02
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_F16F16F32 0x03
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_F16F16F16 0x04
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16F32 0x05
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16BF16 0x06
+#define IREE_B200_UK_FLAG_MMT4D_ACCUMULATE 0x100
+#define IREE_B200_UK_FLAG_PACK_TYPE_MASK 0xFF
+#define IREE_B200_UK_FLAG_PACK_TYPE_F32F32 0x01
+#define IREE_B200_UK_FLAG_PACK_TYPE_I8I8 0x02
+#define IREE_B200_UK_FLAG_PACK_TYPE_I32I32 0x03
+#define IREE_B200_UK_FLAG_PACK_TYPE_F16F16 0x04
+#define IREE_B200_UK_FLAG_PACK_TYPE_BF16BF16 0x05
+#define IREE_B200_UK_FLAG_PACK_TRANSPOSE_INNER 0x100
+#define IREE_B200_UK_FLAG_PACK_TRANSPOSE_OUTER 0x200
+/* iree_uk_pack: row-major [in_size0, in_size1] -> tiled [out_size0..3], ragged edge filled with
+ * the low bytes of padding_value. out_stride1 must equal out_size2 * out_size3 (pack.c:72). */
+iree_b200_status_t iree_b200_uk_pack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
+                                     int64_t in_stride0, int64_t in_stride1, void* out_buffer, int64_t out_offset,
+                                     int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,
+                                     int64_t out_size0, int64_t out_size1, int64_t out_size2, int64_t out_size3,
+                                     uint64_t padding_value, uint32_t flags);
+/* iree_uk_unpack: the inverse; in_stride1 must equal in_size2 * in_size3 (unpack.c:49). The type
+ * flags are the pack ones (I8I8 is accepted here although the reference's unpack has no user
+ * for it). */
+iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
+                                       int64_t in_stride0, int64_t in_stride1, void* out_buffer, int64_t out_offset,
+                                       int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,
+                                       int64_t in_size2, int64_t in_size3, int64_t out_size0, int64_t out_size1,
+                                       uint32_t flags);
+/* iree_uk_mmt4d: out[M,N,M0,N0] (+)= lhs[M,K,M0,K0] x rhs[N,K,N0,K0]. The tiled operands are
+ * brought to row-major by the unpack kernel, multiplied by the tensor-core contraction kernel
+ * and the accumulator is tiled (and added, with ACCUMULATE) by the pack kernel; `workspace` is a
+ * zero-filled device buffer of iree_b200_uk_mmt4d_workspace_bytes() bytes, 256-byte aligned.
+ * Types: S8S8S32 (bit-exact), F16F16F32, BF16BF16F32, F16F16F16, BF16BF16BF16 (f32 accumulation
+ * in tensor-core order; ACCUMULATE only with 32-bit outputs); other types: UNIMPLEMENTED. */
+size_t iree_b200_uk_mmt4d_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
+                                          uint32_t flags);
+iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* lhs_buffer, int64_t lhs_offset,
+                                      int64_t lhs_stride0, const void* rhs_buffer, int64_t rhs_offset,
+                                      int64_t rhs_stride0, void* out_buffer, int64_t out_offset, int64_t out_stride0,
+                                      int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
+                                      uint32_t flags, void* workspace);
+
 /* ---- W4A16 decode without any allocation ---------------------------------------------------------
  * No counterpart in the reference: added for hosts that cannot allocate device memory where
  * they dispatch (inside a stream capture, after handing all memory to their own pool, or on a

@@ -989,6 +989,8 @@ constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
 constexpr uint32_t kDecodeSmemM8 = 3 * 16 * 2048 + 3 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 3 + 8) * 8 + 16;
 constexpr uint32_t kDecodeSmemM16 = 3 * 16 * 2048 + 3 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 3 + 8) * 8 + 16;
 constexpr uint32_t kW4SmemBytes = 1024 + 3 * (128 * 128 + 256 * 128) + 2 * (256 * 64) + 256;
+// staging region of the pack / unpack kernels: 64 rows of at most 512 bytes, 16 bytes of padding per row
+constexpr uint32_t kTilingStageBytes = 64 * (2 * 256 + 16);
 
 struct EntryDecl {
   const char* name;
@@ -1022,6 +1024,12 @@ const EntryDecl kEntries[] = {
     {"b200_w4a16_decode_m16", {512, 1, 1}, kDecodeSmemM16},
     {"b200_w4a16_gemm", {512, 1, 1}, kW4SmemBytes},
     {"b200_w4a16_generic", {256, 1, 1}, 0},
+    {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},
+    {"b200_pack_b16", {256, 1, 1}, kTilingStageBytes},
+    {"b200_pack_b32", {256, 1, 1}, kTilingStageBytes},
+    {"b200_unpack_b8", {256, 1, 1}, kTilingStageBytes},
+    {"b200_unpack_b16", {256, 1, 1}, kTilingStageBytes},
+    {"b200_unpack_b32", {256, 1, 1}, kTilingStageBytes},
 };
 constexpr int kEntryCount = sizeof kEntries / sizeof kEntries[0];
 
@@ -1606,6 +1614,187 @@ iree_b200_status_t iree_b200_w4a16_run_sequence(iree_b200_context_t* context, co
     B200_RETURN_IF_ERROR(iree_b200_w4a16_run(context, params, a[s], wq[s], scales[s], out[s], workspace[s], variant, tile_n));
   }
   return IREE_B200_STATUS_OK;
+}
+
+}  // extern "C"
+
+// ---- pack / unpack / mmt4d ----------------------------------------------------------------------------
+
+namespace {
+
+constexpr uint32_t kUkTransposeInner = 0x100, kUkTransposeOuter = 0x200;
+constexpr uint32_t kTilingAccumulateI32 = 0x10000, kTilingAccumulateF32 = 0x20000;
+
+int pack_elem_bytes(uint32_t flags) {
+  switch (flags & IREE_B200_UK_FLAG_PACK_TYPE_MASK) {
+    case IREE_B200_UK_FLAG_PACK_TYPE_F32F32:
+    case IREE_B200_UK_FLAG_PACK_TYPE_I32I32: return 4;
+    case IREE_B200_UK_FLAG_PACK_TYPE_I8I8: return 1;
+    case IREE_B200_UK_FLAG_PACK_TYPE_F16F16:
+    case IREE_B200_UK_FLAG_PACK_TYPE_BF16BF16: return 2;
+    default: return 0;
+  }
+}
+
+bool fits_i32(int64_t v) { return v >= 0 && v <= INT32_MAX; }
+
+// Grid of the tiling kernels: one CTA per staged region (at most 64 rows by 256 bytes of whole
+// tiles), or a bounded grid-stride launch when a tile is too large to stage.
+uint32_t tiling_grid(int64_t o0, int64_t o1, int64_t o2, int64_t o3, uint32_t flags, int es, int sms) {
+  const bool ti = flags & kUkTransposeInner, to = flags & kUkTransposeOuter;
+  const int64_t tile0 = ti ? o3 : o2, tile1 = ti ? o2 : o3, outer0 = to ? o1 : o0, outer1 = to ? o0 : o1;
+  if (tile0 > 0 && tile1 > 0 && tile0 <= 64 && tile1 * es <= 512) {
+    const int64_t nr = 64 / tile0;
+    int64_t nc = (256 / es) / tile1;
+    if (nc == 0) nc = 1;
+    return static_cast<uint32_t>(((outer0 + nr - 1) / nr) * ((outer1 + nc - 1) / nc));
+  }
+  const int64_t blocks = (o0 * o1 * o2 * o3 + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sms) * 8;
+  return static_cast<uint32_t>(blocks < cap ? blocks : cap);
+}
+
+// Shared by pack (row-major -> tiled) and unpack; `rm_*` describe the row-major side.
+iree_b200_status_t tiling_dispatch(iree_b200_context_t* ctx, bool pack, int es, const void* in, void* out,
+                                   int64_t rm_size0, int64_t rm_size1, int64_t rm_stride0, int64_t rm_stride1,
+                                   int64_t t0, int64_t t1, int64_t t2, int64_t t3, int64_t t_stride0,
+                                   uint32_t kernel_flags, uint64_t padding) {
+  if (!fits_i32(rm_size0) || !fits_i32(rm_size1) || !fits_i32(rm_stride0) || !fits_i32(rm_stride1) || !fits_i32(t0) ||
+      !fits_i32(t1) || !fits_i32(t2) || !fits_i32(t3) || !fits_i32(t_stride0))
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "sizes and strides must be non-negative 32-bit values");
+  if (t0 == 0 || t1 == 0 || t2 == 0 || t3 == 0) return IREE_B200_STATUS_OK;  // early return, pack.c:106-109
+  const bool ti = kernel_flags & kUkTransposeInner, to = kernel_flags & kUkTransposeOuter;
+  const int64_t tile0 = ti ? t3 : t2, tile1 = ti ? t2 : t3, outer0 = to ? t1 : t0, outer1 = to ? t0 : t1;
+  if (outer0 * tile0 < rm_size0 || outer1 * tile1 < rm_size1)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the tiled shape does not cover the %lldx%lld matrix",
+                static_cast<long long>(rm_size0), static_cast<long long>(rm_size1));
+  if (!in || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
+  const char* name = pack ? (es == 1 ? "b200_pack_b8" : es == 2 ? "b200_pack_b16" : "b200_pack_b32")
+                          : (es == 1 ? "b200_unpack_b8" : es == 2 ? "b200_unpack_b16" : "b200_unpack_b32");
+  const int32_t ord = iree_hal_b200_executable_lookup(ctx->executable, name);
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export %s missing from the executable", name);
+  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const uint32_t grid = tiling_grid(t0, t1, t2, t3, kernel_flags, es, sms);
+  auto* cb = ctx->command_buffer;
+  iree_hal_b200_descriptor_set_binding_t bindings[2] = {{0, const_cast<void*>(in)}, {1, out}};
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 2, bindings));
+  if (pack) {
+    const int32_t c[13] = {(int32_t)rm_size0, (int32_t)rm_size1, (int32_t)rm_stride0, (int32_t)rm_stride1,
+                           (int32_t)t0,       (int32_t)t1,       (int32_t)t2,         (int32_t)t3,
+                           (int32_t)t_stride0, (int32_t)kernel_flags, (int32_t)(uint32_t)padding, 0, 0};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
+    return iree_hal_b200_command_buffer_dispatch(cb, ctx->executable, ord, 2, 13, grid, 1, 1);
+  }
+  const int32_t c[12] = {(int32_t)t0,       (int32_t)t1,         (int32_t)t2,         (int32_t)t3, (int32_t)t_stride0,
+                         (int32_t)rm_size0, (int32_t)rm_size1,   (int32_t)rm_stride0, (int32_t)rm_stride1,
+                         (int32_t)kernel_flags, 0, 0};
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
+  return iree_hal_b200_command_buffer_dispatch(cb, ctx->executable, ord, 2, 12, grid, 1, 1);
+}
+
+struct Mmt4dTypes {
+  int kind, epilogue, elem_bytes, out_bytes;
+};
+bool mmt4d_types(uint32_t flags, Mmt4dTypes* t) {
+  switch (flags & IREE_B200_UK_FLAG_MMT4D_TYPE_MASK) {
+    case IREE_B200_UK_FLAG_MMT4D_TYPE_S8S8S32: *t = {IREE_B200_KIND_I8, IREE_B200_EPILOGUE_ACCUMULATOR, 1, 4}; return true;
+    case IREE_B200_UK_FLAG_MMT4D_TYPE_F16F16F32: *t = {IREE_B200_KIND_F16, IREE_B200_EPILOGUE_ACCUMULATOR, 2, 4}; return true;
+    case IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16F32: *t = {IREE_B200_KIND_BF16, IREE_B200_EPILOGUE_ACCUMULATOR, 2, 4}; return true;
+    case IREE_B200_UK_FLAG_MMT4D_TYPE_F16F16F16: *t = {IREE_B200_KIND_F16, IREE_B200_EPILOGUE_CAST, 2, 2}; return true;
+    case IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16BF16: *t = {IREE_B200_KIND_BF16, IREE_B200_EPILOGUE_CAST, 2, 2}; return true;
+    default: return false;
+  }
+}
+size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace
+
+extern "C" {
+
+iree_b200_status_t iree_b200_uk_pack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
+                                     int64_t in_stride0, int64_t in_stride1, void* out_buffer, int64_t out_offset,
+                                     int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,
+                                     int64_t out_size0, int64_t out_size1, int64_t out_size2, int64_t out_size3,
+                                     uint64_t padding_value, uint32_t flags) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  const int es = pack_elem_bytes(flags);
+  if (!es) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown pack type 0x%x", flags & 0xFF);
+  if (flags & ~(IREE_B200_UK_FLAG_PACK_TYPE_MASK | kUkTransposeInner | kUkTransposeOuter))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown pack flags 0x%x", flags);
+  if (out_stride1 != out_size2 * out_size3)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_stride1 must equal out_size2 * out_size3");
+  return tiling_dispatch(context, true, es, static_cast<const uint8_t*>(in_buffer) + in_offset * es,
+                         static_cast<uint8_t*>(out_buffer) + out_offset * es, in_size0, in_size1, in_stride0, in_stride1,
+                         out_size0, out_size1, out_size2, out_size3, out_stride0, flags & (kUkTransposeInner | kUkTransposeOuter),
+                         padding_value);
+}
+
+iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
+                                       int64_t in_stride0, int64_t in_stride1, void* out_buffer, int64_t out_offset,
+                                       int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,
+                                       int64_t in_size2, int64_t in_size3, int64_t out_size0, int64_t out_size1,
+                                       uint32_t flags) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  const int es = pack_elem_bytes(flags);
+  if (!es) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown unpack type 0x%x", flags & 0xFF);
+  if (flags & ~(IREE_B200_UK_FLAG_PACK_TYPE_MASK | kUkTransposeInner | kUkTransposeOuter))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown unpack flags 0x%x", flags);
+  if (in_stride1 != in_size2 * in_size3)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "in_stride1 must equal in_size2 * in_size3");
+  return tiling_dispatch(context, false, es, static_cast<const uint8_t*>(in_buffer) + in_offset * es,
+                         static_cast<uint8_t*>(out_buffer) + out_offset * es, out_size0, out_size1, out_stride0,
+                         out_stride1, in_size0, in_size1, in_size2, in_size3, in_stride0,
+                         flags & (kUkTransposeInner | kUkTransposeOuter), 0);
+}
+
+size_t iree_b200_uk_mmt4d_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
+                                          uint32_t flags) {
+  Mmt4dTypes t;
+  if (!mmt4d_types(flags, &t) || M < 0 || N < 0 || K < 0 || M0 < 0 || N0 < 0 || K0 < 0) return 0;
+  const size_t m = static_cast<size_t>(M) * M0, n = static_cast<size_t>(N) * N0, k = static_cast<size_t>(K) * K0;
+  return up256(IREE_B200_WORKSPACE_BYTES) + up256(m * k * t.elem_bytes) + up256(n * k * t.elem_bytes) +
+         up256(m * n * t.out_bytes);
+}
+
+iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* lhs_buffer, int64_t lhs_offset,
+                                      int64_t lhs_stride0, const void* rhs_buffer, int64_t rhs_offset,
+                                      int64_t rhs_stride0, void* out_buffer, int64_t out_offset, int64_t out_stride0,
+                                      int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
+                                      uint32_t flags, void* workspace) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  Mmt4dTypes t;
+  if (!mmt4d_types(flags, &t))
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "mmt4d type 0x%x has no tensor-core kernel", flags & 0xFF);
+  if (flags & ~(IREE_B200_UK_FLAG_MMT4D_TYPE_MASK | IREE_B200_UK_FLAG_MMT4D_ACCUMULATE | 0x200u | 0x400u))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown mmt4d flags 0x%x", flags);
+  const bool accumulate = flags & IREE_B200_UK_FLAG_MMT4D_ACCUMULATE;
+  if (accumulate && t.out_bytes != 4)
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "ACCUMULATE needs a 32-bit output type");
+  if (M < 0 || N < 0 || K < 0 || M0 < 0 || N0 < 0 || K0 < 0)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "negative dimension");
+  const int64_t m = M * M0, n = N * N0, k = K * K0;
+  if (!fits_i32(m) || !fits_i32(n) || !fits_i32(k)) return fail(IREE_B200_STATUS_OUT_OF_RANGE, "dimension above 2^31");
+  if (m == 0 || n == 0) return IREE_B200_STATUS_OK;  // mmt4d.c early return: nothing to write
+  if (k == 0 && accumulate) return IREE_B200_STATUS_OK;
+  if (!lhs_buffer || !rhs_buffer || !out_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 256-byte aligned device buffer");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* lhs_rm = ws + up256(IREE_B200_WORKSPACE_BYTES);
+  uint8_t* rhs_rm = lhs_rm + up256(static_cast<size_t>(m) * k * t.elem_bytes);
+  uint8_t* acc_rm = rhs_rm + up256(static_cast<size_t>(n) * k * t.elem_bytes);
+  const uint8_t* lhs = static_cast<const uint8_t*>(lhs_buffer) + lhs_offset * t.elem_bytes;
+  const uint8_t* rhs = static_cast<const uint8_t*>(rhs_buffer) + rhs_offset * t.elem_bytes;
+  uint8_t* out = static_cast<uint8_t*>(out_buffer) + out_offset * t.out_bytes;
+  if (k > 0) {
+    B200_RETURN_IF_ERROR(tiling_dispatch(context, false, t.elem_bytes, lhs, lhs_rm, m, k, k, 1, M, K, M0, K0, lhs_stride0, 0, 0));
+    B200_RETURN_IF_ERROR(tiling_dispatch(context, false, t.elem_bytes, rhs, rhs_rm, n, k, k, 1, N, K, N0, K0, rhs_stride0, 0, 0));
+  }
+  iree_b200_matmul_params_t p = {t.kind, t.epilogue, (int32_t)m, (int32_t)n, (int32_t)k, 1, IREE_B200_RHS_NK, 0, 0};
+  B200_RETURN_IF_ERROR(iree_b200_matmul(context, &p, lhs_rm, rhs_rm, acc_rm, nullptr, nullptr, ws));
+  uint32_t kf = 0;
+  if (accumulate) kf = t.kind == IREE_B200_KIND_I8 ? kTilingAccumulateI32 : kTilingAccumulateF32;
+  return tiling_dispatch(context, true, t.out_bytes, acc_rm, out, m, n, n, 1, M, N, M0, N0, out_stride0, kf, 0);
 }
 
 }  // extern "C"

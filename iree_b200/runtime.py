@@ -78,6 +78,7 @@ def library():
         lib.iree_b200_context_command_buffer.restype = C.c_void_p
         lib.iree_hal_b200_command_buffer_launch_count.restype = C.c_uint64
         lib.iree_b200_w4a16_workspace_bytes.restype = C.c_size_t
+        lib.iree_b200_uk_mmt4d_workspace_bytes.restype = C.c_size_t
         _lib = lib
     return _lib
 
@@ -338,6 +339,36 @@ class Context:
             self._ptr_array(cols[2]), self._ptr_array(cols[3]), self._ptr_array(cols[4]), C.c_int32(variant),
             C.c_int32(tile_n), C.c_int32(first), C.c_int32(count)))
 
+    # data-tiled entry points (argument order of iree_uk_pack / iree_uk_unpack / iree_uk_mmt4d)
+    def uk_pack(self, in_buffer, in_offset, in_stride0, in_stride1, out_buffer, out_offset, out_stride0, out_stride1,
+                in_size0, in_size1, out_size0, out_size1, out_size2, out_size3, padding_value, flags) -> None:
+        i64 = C.c_int64
+        check(library().iree_b200_uk_pack(
+            self.handle, _vp(in_buffer), i64(in_offset), i64(in_stride0), i64(in_stride1), _vp(out_buffer),
+            i64(out_offset), i64(out_stride0), i64(out_stride1), i64(in_size0), i64(in_size1), i64(out_size0),
+            i64(out_size1), i64(out_size2), i64(out_size3), C.c_uint64(padding_value), C.c_uint32(flags)))
+
+    def uk_unpack(self, in_buffer, in_offset, in_stride0, in_stride1, out_buffer, out_offset, out_stride0, out_stride1,
+                  in_size0, in_size1, in_size2, in_size3, out_size0, out_size1, flags) -> None:
+        i64 = C.c_int64
+        check(library().iree_b200_uk_unpack(
+            self.handle, _vp(in_buffer), i64(in_offset), i64(in_stride0), i64(in_stride1), _vp(out_buffer),
+            i64(out_offset), i64(out_stride0), i64(out_stride1), i64(in_size0), i64(in_size1), i64(in_size2),
+            i64(in_size3), i64(out_size0), i64(out_size1), C.c_uint32(flags)))
+
+    def uk_mmt4d_workspace(self, M, N, K, M0, N0, K0, flags) -> DeviceBuffer:
+        nbytes = int(library().iree_b200_uk_mmt4d_workspace_bytes(C.c_int64(M), C.c_int64(N), C.c_int64(K), C.c_int32(M0),
+                                                                  C.c_int32(N0), C.c_int32(K0), C.c_uint32(flags)))
+        return DeviceBuffer(self, max(nbytes, 512)).fill(0)
+
+    def uk_mmt4d(self, lhs, lhs_offset, lhs_stride0, rhs, rhs_offset, rhs_stride0, out, out_offset, out_stride0,
+                 M, N, K, M0, N0, K0, flags, workspace) -> None:
+        i64 = C.c_int64
+        check(library().iree_b200_uk_mmt4d(
+            self.handle, _vp(lhs), i64(lhs_offset), i64(lhs_stride0), _vp(rhs), i64(rhs_offset), i64(rhs_stride0),
+            _vp(out), i64(out_offset), i64(out_stride0), i64(M), i64(N), i64(K), C.c_int32(M0), C.c_int32(N0),
+            C.c_int32(K0), C.c_uint32(flags), _vp(workspace)))
+
     def encode_tensor_map(self, elem_bytes, is_bf16, ptr, dim0, dim1, dim2, box0, box1) -> bytes:
         out = C.create_string_buffer(128)
         check(library().iree_b200_encode_tensor_map(self.handle, C.c_int32(elem_bytes), C.c_int32(int(is_bf16)),
@@ -374,4 +405,87 @@ def matmul_numpy(ctx: Context, kind: int, epilogue: int, lhs: np.ndarray, rhs: n
     rs = None if row_scale is None else np.ascontiguousarray(row_scale, np.float32)
     cs = None if col_scale is None else np.ascontiguousarray(col_scale, np.float32)
     ctx.matmul_host(p, lhs, rhs, out, rs, cs)
+    return out
+
+
+# ---- data tiling conveniences (tests and the bench) -------------------------------------------------
+
+UK_PACK_TYPE = {1: 0x02, 2: 0x04, 4: 0x03}  # element bytes -> I8I8 / F16F16 / I32I32 (pure data movement)
+UK_TRANSPOSE_INNER, UK_TRANSPOSE_OUTER = 0x100, 0x200
+UK_MMT4D_S8S8S32, UK_MMT4D_F16F16F32, UK_MMT4D_F16F16F16 = 0x02, 0x03, 0x04
+UK_MMT4D_BF16BF16F32, UK_MMT4D_BF16BF16BF16, UK_MMT4D_ACCUMULATE = 0x05, 0x06, 0x100
+
+
+def pack_numpy(ctx: Context, x: np.ndarray, tile, transpose_inner=False, transpose_outer=False, padding: int = 0,
+               out_shape=None) -> np.ndarray:
+    """Host [S0,S1] array in, tiled [o0,o1,o2,o3] array out, through iree_b200_uk_pack. `tile` is the
+    (rows, cols) tile extent in matrix terms; x may be a strided 2-D view."""
+    assert x.ndim == 2
+    es = x.dtype.itemsize
+    t0, t1 = tile
+    n0, n1 = -(-x.shape[0] // t0), -(-x.shape[1] // t1)
+    if out_shape is None:
+        outer = (n1, n0) if transpose_outer else (n0, n1)
+        inner = (t1, t0) if transpose_inner else (t0, t1)
+        out_shape = outer + inner
+    # A strided view travels as its whole (contiguous) base plus offset and strides, in elements.
+    base = x
+    while base.base is not None and isinstance(base.base, np.ndarray):
+        base = base.base
+    if not base.flags.c_contiguous:
+        base = x = np.ascontiguousarray(x)
+    offset = (x.__array_interface__["data"][0] - base.__array_interface__["data"][0]) // es
+    stride0, stride1 = x.strides[0] // es, x.strides[1] // es
+    dev_in = ctx.to_device(base.reshape(-1).view(np.uint8)) if base.size else ctx.alloc(16)
+    count = int(np.prod(out_shape))
+    dev_out = ctx.alloc(max(count * es, 16)).fill(0xCD)
+    flags = UK_PACK_TYPE[es] | (UK_TRANSPOSE_INNER if transpose_inner else 0) | (UK_TRANSPOSE_OUTER if transpose_outer else 0)
+    ctx.uk_pack(dev_in, offset, stride0, stride1, dev_out, 0, out_shape[1] * out_shape[2] * out_shape[3],
+                out_shape[2] * out_shape[3], x.shape[0], x.shape[1], *out_shape, padding, flags)
+    out = dev_out.download(x.dtype, out_shape)
+    dev_in.free()
+    dev_out.free()
+    return out
+
+
+def unpack_numpy(ctx: Context, x4: np.ndarray, out_shape, transpose_inner=False, transpose_outer=False,
+                 fill: int = 0xCD) -> np.ndarray:
+    """Tiled host array in, row-major [S0,S1] out, through iree_b200_uk_unpack; untouched output bytes keep `fill`."""
+    x4 = np.ascontiguousarray(x4)
+    es = x4.dtype.itemsize
+    dev_in = ctx.to_device(x4) if x4.size else ctx.alloc(16)
+    count = int(out_shape[0] * out_shape[1])
+    dev_out = ctx.alloc(max(count * es, 16)).fill(fill)
+    flags = UK_PACK_TYPE[es] | (UK_TRANSPOSE_INNER if transpose_inner else 0) | (UK_TRANSPOSE_OUTER if transpose_outer else 0)
+    ctx.uk_unpack(dev_in, 0, x4.shape[1] * x4.shape[2] * x4.shape[3], x4.shape[2] * x4.shape[3], dev_out, 0, out_shape[1], 1,
+                  *x4.shape, out_shape[0], out_shape[1], flags)
+    out = dev_out.download(x4.dtype, tuple(out_shape))
+    dev_in.free()
+    dev_out.free()
+    return out
+
+
+def mmt4d_numpy(ctx: Context, type_flag: int, lhs4: np.ndarray, rhs4: np.ndarray, acc4=None) -> np.ndarray:
+    """lhs4 [M,K,M0,K0], rhs4 [N,K,N0,K0] -> [M,N,M0,N0] through iree_b200_uk_mmt4d (acc4 given: ACCUMULATE)."""
+    lhs4, rhs4 = np.ascontiguousarray(lhs4), np.ascontiguousarray(rhs4)
+    M, K, M0, K0 = lhs4.shape
+    N, K2, N0, K02 = rhs4.shape
+    assert (K, K0) == (K2, K02)
+    odt = {UK_MMT4D_S8S8S32: np.int32, UK_MMT4D_F16F16F32: np.float32, UK_MMT4D_BF16BF16F32: np.float32,
+           UK_MMT4D_F16F16F16: np.float16, UK_MMT4D_BF16BF16BF16: np.uint16}[type_flag]
+    flags = type_flag | (UK_MMT4D_ACCUMULATE if acc4 is not None else 0)
+    out_shape = (M, N, M0, N0)
+    count = int(np.prod(out_shape))
+    dl = ctx.to_device(lhs4) if lhs4.size else ctx.alloc(16)
+    dr = ctx.to_device(rhs4) if rhs4.size else ctx.alloc(16)
+    if acc4 is not None:
+        do = ctx.to_device(np.ascontiguousarray(acc4, odt)) if count else ctx.alloc(16)
+    else:
+        do = ctx.alloc(max(count * np.dtype(odt).itemsize, 16)).fill(0xCD)
+    ws = ctx.uk_mmt4d_workspace(M, N, K, M0, N0, K0, flags)
+    ctx.uk_mmt4d(dl, 0, K * M0 * K0, dr, 0, K * N0 * K0, do, 0, N * M0 * N0, M, N, K, M0, N0, K0, flags, ws)
+    ctx.workspace_status(ws)
+    out = do.download(odt, out_shape)
+    for b in (dl, dr, do, ws):
+        b.free()
     return out

@@ -1,0 +1,208 @@
+"""Parity of the GPU pack / unpack / mmt4d entry points with the CPU oracle, through the C ABI.
+
+pack and unpack move bytes, so every comparison is bit-exact; mmt4d is bit-exact for s8s8s32
+and within rtol = atol = 1e-2 for the float types (exact on small-integer data).
+"""
+import numpy as np
+import pytest
+
+import iree_b200 as ib
+import oracle
+from iree_b200 import runtime as rt
+from iree_b200.runtime import mmt4d_numpy, pack_numpy, unpack_numpy
+
+pytestmark = pytest.mark.gpu
+
+RTOL = ATOL = 1e-2
+
+# builtins/ukernel/tools/pack_test.c:137-147 (outer shapes) and :214-245 (type / tile pairs), plus
+# the tiles the x86-64 and generic tables choose for the benchmark types.
+OUTER_SHAPES = [(0, 1), (1, 0), (1, 1), (3, 2), (9, 33)]
+TYPE_TILES = [(np.float32, 3, 5), (np.int8, 4, 2), (np.int32, 3, 4), (np.float16, 6, 7), (np.uint16, 9, 2),
+              (np.float32, 8, 1), (np.int8, 8, 2), (np.float32, 8, 8), (np.int32, 8, 8), (np.float32, 16, 1),
+              (np.uint16, 16, 2), (np.int8, 16, 2), (np.float32, 16, 16), (np.int32, 16, 16), (np.int8, 1, 2),
+              (np.float16, 16, 1)]
+
+
+def random_array(rng, dtype, shape):
+    dtype = np.dtype(dtype)
+    return rng.integers(0, 256, (int(np.prod(shape)) * dtype.itemsize,), dtype=np.uint8).view(dtype).reshape(shape)
+
+
+def cases():
+    """(out_shape, in_shape, transpose_inner, transpose_outer) the way pack_test.c:152-190 builds them."""
+    rng = np.random.default_rng(7)
+    for (s0, s1) in OUTER_SHAPES:
+        for ti in (False, True):
+            for to in (False, True):
+                for pad in ("none", "one_incomplete_tile", "a_lot"):
+                    yield (s0, s1), ti, to, pad, rng
+
+
+@pytest.mark.parametrize("dtype,tile0,tile1", TYPE_TILES)
+def test_pack_matches_the_oracle_bit_for_bit(ctx, dtype, tile0, tile1):
+    for (s0, s1), ti, to, pad, rng in cases():
+        o0, o1 = (s0 + 16, s1 + 16) if pad == "a_lot" else (s0, s1)
+        out_shape = ((o1, o0) if to else (o0, o1)) + (tile0, tile1)
+        t0, t1 = (tile1, tile0) if ti else (tile0, tile1)
+        in0, in1 = s0 * t0, s1 * t1
+        if pad != "none":
+            in0 = max(in0 - int(rng.integers(0, t0)), 0)
+            in1 = max(in1 - int(rng.integers(0, t1)), 0)
+        x = random_array(rng, dtype, (in0, in1))
+        padding = int(rng.integers(0, 256)) * 0x01010101 & ((1 << (8 * np.dtype(dtype).itemsize)) - 1)
+        want = oracle.pack_port(x, out_shape, ti, to, padding)
+        got = pack_numpy(ctx, x, (t0, t1), ti, to, padding, out_shape=out_shape)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (dtype, out_shape, x.shape, ti, to, pad)
+
+
+@pytest.mark.parametrize("dtype,tile0,tile1", TYPE_TILES)
+def test_unpack_matches_the_oracle_and_leaves_the_rest_alone(ctx, dtype, tile0, tile1):
+    for (s0, s1), ti, to, pad, rng in cases():
+        o0, o1 = (s0 + 16, s1 + 16) if pad == "a_lot" else (s0, s1)
+        in_shape = ((o1, o0) if to else (o0, o1)) + (tile0, tile1)
+        t0, t1 = (tile1, tile0) if ti else (tile0, tile1)
+        out0, out1 = s0 * t0, s1 * t1
+        if pad != "none":
+            out0 = max(out0 - int(rng.integers(0, t0)), 0)
+            out1 = max(out1 - int(rng.integers(0, t1)), 0)
+        x4 = random_array(rng, dtype, in_shape)
+        want = oracle.unpack_port(x4, (out0, out1), ti, to)
+        got = unpack_numpy(ctx, x4, (out0, out1), ti, to)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (dtype, in_shape, (out0, out1), ti, to, pad)
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference ukernels were not compiled")
+def test_pack_and_unpack_match_the_reference_ukernels_on_operand_sized_matrices(ctx):
+    """The three packs of one data-tiled matmul (pack.c / unpack.c as built from the reference's
+    own sources): LHS, RHS with both transposes, and the accumulator round trip."""
+    rng = np.random.default_rng(11)
+    M, K, N = 300, 517, 260
+    a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    b = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    m0, n0, k0 = 16, 16, 2
+    m1, n1, k1 = -(-M // m0), -(-N // n0), -(-K // k0)
+    assert np.array_equal(pack_numpy(ctx, a, (m0, k0)), oracle.pack_ref(a, (m1, k1, m0, k0)))
+    assert np.array_equal(pack_numpy(ctx, b, (k0, n0), True, True), oracle.pack_ref(b, (n1, k1, n0, k0), True, True))
+    acc = rng.integers(-2 ** 31, 2 ** 31, (m1, n1, m0, n0)).astype(np.int32)
+    assert np.array_equal(unpack_numpy(ctx, acc, (M, N)), oracle.unpack_ref(acc, (M, N)))
+    f = rng.standard_normal((M, N)).astype(np.float32)
+    assert np.array_equal(pack_numpy(ctx, f, (m0, n0)), oracle.pack_ref(f, (m1, n1, m0, n0)))
+
+
+def test_pack_of_a_strided_view_and_tiles_too_large_to_stage(ctx):
+    rng = np.random.default_rng(3)
+    base = rng.integers(-128, 128, (70, 200), dtype=np.int8)
+    view = base[3:60:2, 5:190:3]                       # in_offset, in_stride0 and in_stride1 all in play
+    want = oracle.pack_port(np.ascontiguousarray(view), (-(-view.shape[0] // 8), -(-view.shape[1] // 4), 8, 4), padding=0x7F)
+    assert np.array_equal(pack_numpy(ctx, view, (8, 4), padding=0x7F), want)
+    big = rng.standard_normal((150, 700)).astype(np.float32)  # 100 x 300 tiles: the direct path
+    want = oracle.pack_port(big, (2, 3, 100, 300), padding=0)
+    assert np.array_equal(pack_numpy(ctx, big, (100, 300)), want)
+    assert np.array_equal(unpack_numpy(ctx, want, (150, 700)), big)
+
+
+def test_round_trip_at_benchmark_size(ctx):
+    """unpack(pack(x)) == x on the weight matrix of the W8A8 configuration (4096 x 11008 int8),
+    both operand roles; the padded tail of a ragged matrix holds the fill value."""
+    rng = np.random.default_rng(5)
+    w = rng.integers(-127, 128, (4096, 11008), dtype=np.int8)
+    p = pack_numpy(ctx, w, (2, 16), True, True)                # RHS role: [N1, K1, N0, K0]
+    assert p.shape == (688, 2048, 16, 2)
+    assert np.array_equal(p[5, 7], w[14:16, 80:96].T)
+    assert np.array_equal(unpack_numpy(ctx, p, w.shape, True, True), w)
+    ragged = w[:4001, :1003]
+    p = pack_numpy(ctx, ragged, (16, 2), padding=0x55)
+    assert np.array_equal(unpack_numpy(ctx, p, ragged.shape), ragged)
+    assert (p[-1, :, 1:, :] == 0x55).all() and (p[:, -1, :, 1] == 0x55).all()
+
+
+def test_argument_errors(ctx):
+    buf = ctx.alloc(1024)
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.uk_pack(buf, 0, 8, 1, buf, 0, 16, 7, 8, 8, 2, 2, 4, 2, 0, 0x02)   # out_stride1 != o2 * o3
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.uk_pack(buf, 0, 8, 1, buf, 0, 16, 8, 8, 8, 2, 2, 4, 2, 0, 0x07)   # no such type
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.uk_pack(buf, 0, 8, 1, buf, 0, 8, 8, 8, 8, 1, 1, 4, 2, 0, 0x02)    # tiles do not cover the matrix
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.uk_mmt4d(buf, 0, 8, buf, 0, 8, buf, 0, 8, 1, 1, 1, 2, 2, 2, 0x01, buf)  # f32f32f32
+    assert e.value.code_name == "UNIMPLEMENTED"
+    buf.free()
+
+
+# ---- mmt4d ---------------------------------------------------------------------------------------------
+
+# builtins/ukernel/tools/mmt4d_test.c:449-504: generic tiles, then the x86-64 tiles incl. narrow M0.
+MMT4D_I8_TILES = [(4, 4, 2), (3, 5, 7), (9, 6, 3), (1, 16, 2), (2, 16, 2), (4, 16, 2), (8, 16, 2), (16, 16, 2), (8, 8, 2)]
+MMT4D_SHAPES = [(1, 1, 1), (2, 3, 5), (3, 2, 17), (7, 9, 64)]  # outer M, N, K
+
+
+@pytest.mark.parametrize("m0,n0,k0", MMT4D_I8_TILES)
+def test_mmt4d_s8s8s32_bit_exact(ctx, m0, n0, k0):
+    rng = np.random.default_rng(m0 * 100 + n0 * 10 + k0)
+    for (M, N, K) in MMT4D_SHAPES:
+        lhs = rng.integers(-128, 128, (M, K, m0, k0), dtype=np.int8)
+        rhs = rng.integers(-128, 128, (N, K, n0, k0), dtype=np.int8)
+        want = oracle.mmt4d_port(oracle.TYPE_S8S8S32, lhs, rhs)
+        assert np.array_equal(mmt4d_numpy(ctx, rt.UK_MMT4D_S8S8S32, lhs, rhs), want), (M, N, K)
+        acc = rng.integers(-10 ** 6, 10 ** 6, (M, N, m0, n0)).astype(np.int32)
+        want = oracle.mmt4d_port(oracle.TYPE_S8S8S32, lhs, rhs, acc)
+        assert np.array_equal(mmt4d_numpy(ctx, rt.UK_MMT4D_S8S8S32, lhs, rhs, acc), want), (M, N, K, "accumulate")
+
+
+@pytest.mark.parametrize("type_flag,otype", [(rt.UK_MMT4D_F16F16F32, "F16F16F32"), (rt.UK_MMT4D_BF16BF16F32, "BF16BF16F32"),
+                                             (rt.UK_MMT4D_F16F16F16, "F16F16F16")])
+@pytest.mark.parametrize("m0,n0,k0", [(16, 16, 1), (8, 8, 1), (1, 16, 1), (3, 5, 7)])
+def test_mmt4d_float_types(ctx, type_flag, otype, m0, n0, k0):
+    # The 16-bit output type is the f32 result rounded once at the end (mmt4d_tile_generic.c:199-260
+    # with SKIP_INTERMEDIATE_ROUNDINGS).
+    ot = oracle.TYPE_BF16BF16F32 if otype.startswith("BF16") else oracle.TYPE_F16F16F32
+    narrow = (lambda x: oracle.truncf(x)) if otype == "F16F16F16" else (lambda x: x)
+    rng = np.random.default_rng(9)
+    bf = type_flag == rt.UK_MMT4D_BF16BF16F32
+    for (M, N, K) in [(2, 3, 40), (5, 4, 256)]:
+        def draw(shape, small):
+            x = (rng.integers(-4, 5, shape) if small else rng.standard_normal(shape) / np.sqrt(K * k0)).astype(np.float32)
+            return (x.view(np.uint32) >> 16).astype(np.uint16) if bf else x.astype(np.float16)
+        for small in (True, False):
+            lhs, rhs = draw((M, K, m0, k0), small), draw((N, K, n0, k0), small)
+            want = narrow(oracle.mmt4d_port(ot, lhs, rhs)).astype(np.float64)
+            got = mmt4d_numpy(ctx, type_flag, lhs, rhs).astype(np.float64)
+            if small:
+                assert np.array_equal(got, want)
+            else:
+                assert np.allclose(got, want, rtol=RTOL, atol=ATOL)
+            if type_flag != rt.UK_MMT4D_F16F16F16:
+                acc = rng.standard_normal((M, N, m0, n0)).astype(np.float32)
+                want = oracle.mmt4d_port(ot, lhs, rhs, acc)
+                got = mmt4d_numpy(ctx, type_flag, lhs, rhs, acc)
+                assert np.allclose(got, want, rtol=RTOL, atol=ATOL)
+
+
+def test_mmt4d_empty_and_k_zero(ctx):
+    lhs = np.zeros((2, 0, 4, 2), np.int8)
+    rhs = np.zeros((3, 0, 4, 2), np.int8)
+    assert (mmt4d_numpy(ctx, rt.UK_MMT4D_S8S8S32, lhs, rhs) == 0).all()            # K = 0: zero fill
+    acc = np.arange(2 * 3 * 16, dtype=np.int32).reshape(2, 3, 4, 4)
+    assert np.array_equal(mmt4d_numpy(ctx, rt.UK_MMT4D_S8S8S32, lhs, rhs, acc), acc)  # K = 0 + ACCUMULATE: untouched
+    assert mmt4d_numpy(ctx, rt.UK_MMT4D_S8S8S32, np.zeros((0, 3, 4, 2), np.int8), np.zeros((3, 3, 4, 2), np.int8)).size == 0
+
+
+def test_data_tiled_matmul_chain_on_the_gpu_equals_the_reference_chain(ctx):
+    """Configuration 0 the way llvm-cpu runs it (pack, pack, mmt4d, unpack with the 16x16x2 VNNI
+    tiles), every step on the GPU, bit-exact against the reference's own chain."""
+    from iree_b200 import workloads
+    a, b = workloads.c1_i8_matmul()
+    M, K = a.shape
+    N = b.shape[1]
+    m0, n0, k0 = 16, 16, 2
+    pl = pack_numpy(ctx, a, (m0, k0))
+    pr = pack_numpy(ctx, b, (k0, n0), True, True)
+    po = mmt4d_numpy(ctx, rt.UK_MMT4D_S8S8S32, pl, pr)
+    got = unpack_numpy(ctx, po, (M, N))
+    want = oracle.matmul_ref(oracle.TYPE_S8S8S32, a, b) if oracle.have_ref() else oracle.matmul_port(oracle.TYPE_S8S8S32, a, b)
+    assert np.array_equal(got, want)

@@ -165,6 +165,17 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
                                                          uint32_t workgroup_z);
 /* Number of kernel launches this command buffer has issued (for launch accounting). */
 uint64_t iree_hal_b200_command_buffer_launch_count(const iree_hal_b200_command_buffer_t* command_buffer);
+/* Dispatch overlap (programmatic dependent launch; no counterpart in the reference's CUDA driver,
+ * which serialises dispatches of a stream, stream_command_buffer.c:500-610). While enabled, a
+ * dispatch is launched (stream mode) or recorded (graph mode) so that the device may start it
+ * before the dispatch ahead of it has finished. Only exports that order themselves on the device
+ * may be dispatched this way: they call griddepcontrol.wait before reading anything an earlier
+ * kernel may write and before writing anything. Of this library's exports those are
+ * b200_w4a16_decode_m8 / _m16, which prefetch weight tiles ahead of the wait: the caller vouches
+ * that weights and scales are not written by the dispatch ahead. UNAVAILABLE when the driver
+ * lacks the feature. */
+iree_b200_status_t iree_hal_b200_command_buffer_set_dispatch_overlap(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                     int32_t enable);
 
 /* ---- graph mode ------------------------------------------------------------------------------------
  * The CUDA-graph command buffer of the reference (--cuda_use_streams=false,
@@ -346,6 +357,11 @@ iree_b200_status_t iree_b200_w4a16_run_sequence(iree_b200_context_t* context, co
                                                 int32_t set_count, const void* const* a, const void* const* wq,
                                                 const void* const* scales, void* const* out, void* const* workspace,
                                                 int32_t variant, int32_t tile_n, int32_t first, int32_t count);
+
+/* Operator-level switch for the above: while enabled, the operator entry points dispatch the
+ * exports that order themselves on the device with overlap, and every other export normally.
+ * Off by default. */
+iree_b200_status_t iree_b200_context_set_dispatch_overlap(iree_b200_context_t* context, int32_t enable);
 
 /* ---- data-tiled entry points: pack / unpack / mmt4d -------------------------------------------
  *

@@ -85,6 +85,9 @@ struct CudaSymbols {
   CU_FN(cuGraphInstantiateWithFlags, CUgraphExec*, CUgraph, unsigned long long)
   CU_FN(cuGraphLaunch, CUgraphExec, CUstream)
   CU_FN(cuGraphExecDestroy, CUgraphExec)
+  // optional (programmatic dependent launch); dispatch overlap is refused when they are missing
+  CU_FN(cuLaunchKernelEx, const CUlaunchConfig*, CUfunction, void**, void**)
+  CU_FN(cuGraphAddDependencies_v2, CUgraph, const CUgraphNode*, const CUgraphNode*, const CUgraphEdgeData*, size_t)
   CU_FN(cuGetErrorName, CUresult, const char**)
   CU_FN(cuGetErrorString, CUresult, const char**)
   CU_FN(cuTensorMapEncodeTiled, CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -154,6 +157,8 @@ iree_b200_status_t ensure_cuda() {
       LOAD(cuGetErrorString, "cuGetErrorString")
       LOAD(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
 #undef LOAD
+      load_sym(g_cu.handle, "cuLaunchKernelEx", g_cu.cuLaunchKernelEx);
+      load_sym(g_cu.handle, "cuGraphAddDependencies_v2", g_cu.cuGraphAddDependencies_v2);
       if (!ok) {
         g_cu.error = "CUDA driver library is missing required symbols";
         g_cu.handle = nullptr;
@@ -411,6 +416,9 @@ struct iree_hal_b200_command_buffer_t {
   CUgraph recording = nullptr;
   CUgraphNode last_node = nullptr;
   uint64_t recorded_nodes = 0;
+  // The next dispatches may start before the dispatch ahead of them has finished (programmatic
+  // dependent launch); the caller vouches that their exports order themselves on the device.
+  bool overlap = false;
   uint32_t constants[IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT] = {0};
   void* bindings[IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT][IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT] = {{nullptr}};
   uint64_t launches = 0;
@@ -797,18 +805,64 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
     np.sharedMemBytes = e.smem;
     np.kernelParams = params;
     CUgraphNode node = nullptr;
+    const bool programmatic = command_buffer->overlap && command_buffer->last_node;
     CU_RETURN_IF_ERROR(g_cu.cuGraphAddKernelNode(&node, command_buffer->recording,
-                                                 command_buffer->last_node ? &command_buffer->last_node : nullptr,
-                                                 command_buffer->last_node ? 1 : 0, &np),
+                                                 command_buffer->last_node && !programmatic ? &command_buffer->last_node : nullptr,
+                                                 command_buffer->last_node && !programmatic ? 1 : 0, &np),
                        "cuGraphAddKernelNode");
+    if (programmatic) {
+      // The edge leaves the upstream kernel's programmatic port: this node may be launched once
+      // every upstream block has released its dependents (or exited), and waits on the device
+      // (griddepcontrol.wait) before it touches anything the upstream kernel produces.
+      CUgraphEdgeData edge;
+      memset(&edge, 0, sizeof edge);
+      edge.from_port = CU_GRAPH_KERNEL_NODE_PORT_PROGRAMMATIC;
+      edge.to_port = 0;
+      edge.type = CU_GRAPH_DEPENDENCY_TYPE_PROGRAMMATIC;
+      CU_RETURN_IF_ERROR(g_cu.cuGraphAddDependencies_v2(command_buffer->recording, &command_buffer->last_node, &node,
+                                                        &edge, 1),
+                         "cuGraphAddDependencies");
+    }
     command_buffer->last_node = node;
     ++command_buffer->recorded_nodes;
     return IREE_B200_STATUS_OK;
   }
-  CU_RETURN_IF_ERROR(g_cu.cuLaunchKernel(e.fn, workgroup_x, workgroup_y, workgroup_z, e.block[0], e.block[1],
-                                         e.block[2], e.smem, d->stream, params, nullptr),
-                     e.name.c_str());
+  if (command_buffer->overlap) {
+    CUlaunchConfig config;
+    memset(&config, 0, sizeof config);
+    config.gridDimX = workgroup_x;
+    config.gridDimY = workgroup_y;
+    config.gridDimZ = workgroup_z;
+    config.blockDimX = e.block[0];
+    config.blockDimY = e.block[1];
+    config.blockDimZ = e.block[2];
+    config.sharedMemBytes = e.smem;
+    config.hStream = d->stream;
+    CUlaunchAttribute attr;
+    memset(&attr, 0, sizeof attr);
+    attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr.value.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
+    CU_RETURN_IF_ERROR(g_cu.cuLaunchKernelEx(&config, e.fn, params, nullptr), e.name.c_str());
+  } else {
+    CU_RETURN_IF_ERROR(g_cu.cuLaunchKernel(e.fn, workgroup_x, workgroup_y, workgroup_z, e.block[0], e.block[1],
+                                           e.block[2], e.smem, d->stream, params, nullptr),
+                       e.name.c_str());
+  }
   ++command_buffer->launches;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_set_dispatch_overlap(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                     int32_t enable) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command buffer is NULL");
+  if (enable) {
+    B200_RETURN_IF_ERROR(ensure_cuda());
+    if (!g_cu.cuLaunchKernelEx || !g_cu.cuGraphAddDependencies_v2)
+      return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no programmatic dependent launch");
+  }
+  command_buffer->overlap = enable != 0;
   return IREE_B200_STATUS_OK;
 }
 
@@ -985,9 +1039,9 @@ namespace {
 
 constexpr uint32_t kGemmThreads = 256;
 constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
-// weight ring (3 stages of 16 rows x 2048 B), scale ring (3 x 4 KiB), 4 slots of 16 per-warp partials, barriers
-constexpr uint32_t kDecodeSmemM8 = 3 * 16 * 2048 + 3 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 3 + 8) * 8 + 16;
-constexpr uint32_t kDecodeSmemM16 = 3 * 16 * 2048 + 3 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 3 + 8) * 8 + 16;
+// weight ring (4 stages of 16 rows x 2048 B), scale ring (4 x 4 KiB), 4 slots of 16 per-warp partials, barriers
+constexpr uint32_t kDecodeSmemM8 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 4 + 8) * 8 + 16;
+constexpr uint32_t kDecodeSmemM16 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 4 + 8) * 8 + 16 + 16 * 4 * 32 * 8;
 constexpr uint32_t kW4SmemBytes = 1024 + 3 * (128 * 128 + 256 * 128) + 2 * (256 * 64) + 256;
 // staging region of the pack / unpack kernels: 64 rows of at most 512 bytes, 16 bytes of padding per row
 constexpr uint32_t kTilingStageBytes = 64 * (2 * 256 + 16);
@@ -1045,6 +1099,7 @@ struct iree_b200_context_t {
   void* arena = nullptr;
   size_t arena_size = 0;
   bool arena_w4_clean = true;
+  bool dispatch_overlap = false;
 };
 
 namespace {
@@ -1188,6 +1243,14 @@ void iree_b200_context_release(iree_b200_context_t* context) {
   iree_hal_b200_executable_release(context->executable);
   iree_hal_b200_device_release(context->device);
   delete context;
+}
+iree_b200_status_t iree_b200_context_set_dispatch_overlap(iree_b200_context_t* context, int32_t enable) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  // probes the driver; the command buffer's own switch is only raised around eligible dispatches
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_set_dispatch_overlap(context->command_buffer, enable));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_set_dispatch_overlap(context->command_buffer, 0));
+  context->dispatch_overlap = enable != 0;
+  return IREE_B200_STATUS_OK;
 }
 iree_hal_b200_device_t* iree_b200_context_device(iree_b200_context_t* c) { return c ? c->device : nullptr; }
 iree_hal_b200_executable_t* iree_b200_context_executable(iree_b200_context_t* c) { return c ? c->executable : nullptr; }
@@ -1511,7 +1574,11 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     int gx = sms / ksplit;
     if (gx < 1) gx = 1;
     if (gx > tiles) gx = tiles;
-    return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 5, 5, gx, ksplit, 1);
+    // The decode exports order themselves on the device, so they may overlap the dispatch ahead.
+    cb->overlap = context->dispatch_overlap;
+    const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 5, 5, gx, ksplit, 1);
+    cb->overlap = false;
+    return st;
   }
   if (variant == IREE_B200_W4A16_GEMM) {
     if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");

@@ -73,6 +73,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// Both are no-ops in a kernel that was launched without a programmatic dependency.
+// launch_dependents: this block no longer holds back the launch of the next kernel on the stream
+// (which happens once every block of this grid has said so or has exited).
+// wait: returns once every kernel this one depends on has completed and its writes are visible;
+// nothing that a preceding kernel may produce is read, and nothing it may read is written, before it.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- proxies / fences ---------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

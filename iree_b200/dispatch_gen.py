@@ -17,7 +17,7 @@ from typing import Dict, List, Optional, Tuple
 
 GEMM_THREADS, GEMM_SMEM = 256, 197888
 W4_THREADS, W4_SMEM = 512, 181504
-DECODE_THREADS, DECODE_SMEM = 512, {8: 143488, 16: 176256}
+DECODE_THREADS, DECODE_SMEM = 512, {8: 180368, 16: 229520}
 SM_COUNT = 148
 
 ELEM_BYTES = {"f16": 2, "bf16": 2, "i8": 1, "i32": 4, "f32": 4}

@@ -212,6 +212,10 @@ class Context:
     def launch_count(self) -> int:
         return int(library().iree_hal_b200_command_buffer_launch_count(self.command_buffer))
 
+    def set_dispatch_overlap(self, enable: bool) -> None:
+        """Lets exports that order themselves on the device start before the dispatch ahead has finished."""
+        check(library().iree_b200_context_set_dispatch_overlap(self.handle, C.c_int32(1 if enable else 0)))
+
     def begin_graph(self) -> None:
         check(library().iree_hal_b200_command_buffer_begin_graph(self.command_buffer))
 

@@ -114,3 +114,54 @@ def test_argument_errors(ctx):
         ctx.w4a16_host(ib.W4A16Params(17, 16, 256, 128, 16, 0, ib.W4A16_DECODE, 0), np.zeros((17, 256), np.float16),
                        np.zeros((16, 128), np.uint8), np.zeros((16, 2), np.float16), np.zeros((17, 16), np.float16))
     assert e.value.code_name == "INVALID_ARGUMENT"      # decode kernel limit
+
+
+@pytest.mark.parametrize("M,graph", [(1, False), (8, True), (16, False), (16, True)])
+def test_overlapped_dispatch_chain_equals_the_serial_chain(ctx, M, graph):
+    """A chain of decode dispatches in which every step's activations are the previous step's
+    output (N = K), dispatched with overlap (programmatic dependent launch; stream mode and graph
+    mode): each kernel may start, and prefetch weights, before the one ahead has finished, but
+    must not read its activations early. The results are bit-identical to the serial chain."""
+    from iree_b200 import runtime as rt
+    rng = np.random.default_rng(33 + M)
+    N = K = 4096
+    steps = 12
+    a0 = (rng.standard_normal((M, K)) * 0.5).astype(np.float16)
+    layers = []
+    for _ in range(3):
+        wq = workloads.pack_int4(rng.integers(-7, 8, (N, K), dtype=np.int8))                 # zero mean
+        s = (rng.uniform(0.5, 1.5, (N, K // 128)) / (4.5 * np.sqrt(K))).astype(np.float16)   # keeps the chain's scale near 1
+        layers.append((ctx.to_device(wq), ctx.to_device(s)))
+    bufs = [ctx.to_device(a0), ctx.alloc(M * N * 2), ctx.alloc(M * N * 2)]
+    ws = ctx.w4a16_workspace(N)
+    p = rt.W4A16Params(M, N, K, 128, N, 0, ib.W4A16_DECODE, 0)
+    variant, tile_n = ctx.w4a16_prepare(p, bufs[0], layers[0][0], layers[0][1], bufs[1], ws)
+
+    def chain():
+        bufs[0].upload(a0)
+        if graph:
+            ctx.begin_graph()
+        src = 0
+        for i in range(steps):
+            dst = 1 + (i % 2)
+            wq, s = layers[i % 3]
+            ctx.w4a16_run(p, bufs[src], wq, s, bufs[dst], ws, variant, tile_n)
+            src = dst
+        if graph:
+            g = ctx.end_graph()
+            g.execute()
+            ctx.synchronize()
+            g.release()
+        ctx.workspace_status(ws)
+        return bufs[src].download(np.float16, (M, N))
+
+    serial = chain()
+    ctx.set_dispatch_overlap(True)
+    try:
+        overlapped = chain()
+    finally:
+        ctx.set_dispatch_overlap(False)
+    assert np.isfinite(serial.astype(np.float32)).all() and np.abs(serial.astype(np.float32)).max() > 1e-3
+    assert np.array_equal(serial.view(np.uint16), overlapped.view(np.uint16))
+    for b in bufs + [ws] + [x for l in layers for x in l]:
+        b.free()

@@ -118,6 +118,7 @@ static int64_t chooseTileN(int64_t M, int64_t N, int64_t batch, int64_t chunk, i
   double bestCost = 0;
   for (int64_t bn = 256; bn >= 32; bn -= 32) {
     if (bn % chunk) continue;
+    if (M <= 32 && bn > 128 && chunk <= 128) continue;  // few rows: tiles <= 128 wide select the deep-ring variant
     const int64_t tiles = ((M + 127) / 128) * ((N + bn - 1) / bn) * batch;
     const double cost = double((tiles + smCount - 1) / smCount) * (400.0 + bn);
     if (bestCost == 0 || cost < bestCost * 0.9999) {

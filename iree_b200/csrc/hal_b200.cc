@@ -1178,6 +1178,9 @@ int choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_matmul_params_
   for (int bn = 256; bn >= 32; bn -= 32) {
     if (bn % chunk) continue;
     if (p->tile_n && bn != p->tile_n) continue;
+    // Few rows: the product only streams the right-hand side; tiles of at most 128 columns select
+    // the kernels' deep-ring variant (32-row A box, nine stages in flight).
+    if (!p->tile_n && p->M <= 32 && bn > 128 && chunk <= 128) continue;
     const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn) * p->batch;
     const int64_t waves = (tiles + sms - 1) / sms;
     // Time model fitted on 4096^3 f16 (wave time 25.0 / 22.3 / 20.3 us at tile widths 256 / 192 / 128):
@@ -1337,7 +1340,9 @@ iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const 
   uint8_t host[IREE_B200_WORKSPACE_BYTES];
   memset(host, 0, sizeof host);
   const int bf = params->kind == IREE_B200_KIND_BF16;
-  B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, lhs, K, M, B, bk, 128, host));
+  // A box: 128 rows, or 32 in the few-rows variant (the same rule as in the kernels)
+  const uint32_t a_rows = (params->M <= 32 && bn <= 128) ? 32 : 128;
+  B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, lhs, K, M, B, bk, a_rows, host));
   if (params->rhs_layout == IREE_B200_RHS_NK) {
     B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, K, N, B, bk,
                                                      use_pairs(context, params) ? bn / 2 : bn, host + 128));

@@ -56,7 +56,7 @@ def choose_tile_n(M: int, N: int, batch: int, chunk: int, sm_count: int = SM_COU
     """Widest tile that still gives every SM work (same cost model as the runtime and the plugin)."""
     best, best_cost = 0, 0.0
     for bn in range(256, 31, -32):
-        if bn % chunk:
+        if bn % chunk or (M <= 32 and bn > 128 and chunk <= 128):   # few rows: the deep-ring variant
             continue
         tiles = ((M + 127) // 128) * ((N + bn - 1) // bn) * batch
         cost = ((tiles + sm_count - 1) // sm_count) * (400.0 + bn)

@@ -38,12 +38,14 @@ enum {
   IREE_B200_STATUS_INVALID_ARGUMENT = 3,
   IREE_B200_STATUS_DEADLINE_EXCEEDED = 4,
   IREE_B200_STATUS_NOT_FOUND = 5,
+  IREE_B200_STATUS_PERMISSION_DENIED = 7,
   IREE_B200_STATUS_RESOURCE_EXHAUSTED = 8,
   IREE_B200_STATUS_FAILED_PRECONDITION = 9,
   IREE_B200_STATUS_OUT_OF_RANGE = 11,
   IREE_B200_STATUS_UNIMPLEMENTED = 12,
   IREE_B200_STATUS_INTERNAL = 13,
   IREE_B200_STATUS_UNAVAILABLE = 14,
+  IREE_B200_STATUS_DATA_LOSS = 15,
 };
 
 /* Message of the last non-OK status returned on this thread ("" if none). */
@@ -413,6 +415,67 @@ iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* 
                                       int64_t rhs_stride0, void* out_buffer, int64_t out_offset, int64_t out_stride0,
                                       int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
                                       uint32_t flags, void* workspace);
+
+/* ---- parameter archives (.irpa): weights from files -------------------------------------------
+ *
+ * Index, parser, writer and loader for the reference's parameter archive format
+ * (runtime/src/iree/schemas/parameter_archive.h). The index is iree_io_parameter_index_t
+ * (runtime/src/iree/io/parameter_index.h:23-90), parsing is iree_io_parse_irpa_index
+ * (io/formats/irpa/irpa_parser.h) with its checks and status codes, writing lays the file out
+ * exactly as iree_io_parameter_archive_builder_write does (io/formats/irpa/irpa_builder.c), and
+ * iree_b200_parameter_load is what the parameter provider's load / gather does for one device
+ * buffer (io/parameter_index_provider.c). */
+typedef struct iree_b200_parameter_index_t iree_b200_parameter_index_t;
+enum {
+  IREE_B200_PARAMETER_STORAGE_SPLAT = 0, /* IREE_IO_PARAMETER_INDEX_ENTRY_STORAGE_TYPE_SPLAT */
+  IREE_B200_PARAMETER_STORAGE_FILE = 1,  /* IREE_IO_PARAMETER_INDEX_ENTRY_STORAGE_TYPE_FILE */
+};
+typedef struct iree_b200_parameter_entry_t {
+  const char* key; /* not NUL-terminated; owned by the index */
+  uint64_t key_length;
+  const char* metadata;
+  uint64_t metadata_length;
+  uint64_t length; /* bytes of the parameter */
+  int32_t storage_type;
+  uint8_t pattern_length; /* splats */
+  uint8_t pattern[16];
+  uint64_t file_offset; /* file-backed entries: absolute offset in the archive */
+} iree_b200_parameter_entry_t;
+/* One parameter handed to the writer. A data entry takes its bytes from `data`, or repeats
+ * `pattern` when data is NULL (all zeros when pattern_length is 0 too). */
+typedef struct iree_b200_parameter_source_t {
+  const char* key; /* NUL-terminated */
+  const void* metadata;
+  uint64_t metadata_length;
+  int32_t storage_type;
+  uint64_t length;
+  const void* data;
+  uint8_t pattern_length;
+  uint8_t pattern[16];
+  uint64_t alignment; /* data entries; 0 = 64 */
+} iree_b200_parameter_source_t;
+/* Maps the file and indexes every header of its chain. */
+iree_b200_status_t iree_b200_parameter_index_open(const char* path, iree_b200_parameter_index_t** out_index);
+/* The same over a buffer the caller keeps alive for the index's lifetime. */
+iree_b200_status_t iree_b200_parameter_index_parse(const void* data, size_t size,
+                                                   iree_b200_parameter_index_t** out_index);
+void iree_b200_parameter_index_release(iree_b200_parameter_index_t* index);
+int64_t iree_b200_parameter_index_count(const iree_b200_parameter_index_t* index);
+iree_b200_status_t iree_b200_parameter_index_get(const iree_b200_parameter_index_t* index, int64_t i,
+                                                 iree_b200_parameter_entry_t* out_entry);
+/* NOT_FOUND when the key is absent. */
+iree_b200_status_t iree_b200_parameter_index_lookup(const iree_b200_parameter_index_t* index, const char* key,
+                                                    iree_b200_parameter_entry_t* out_entry);
+/* Bytes [parameter_offset, parameter_offset + length) of a parameter into host / device memory
+ * (splats are expanded); the call returns when the bytes are in place. */
+iree_b200_status_t iree_b200_parameter_read(const iree_b200_parameter_index_t* index, const char* key,
+                                            uint64_t parameter_offset, void* host_ptr, uint64_t length);
+iree_b200_status_t iree_b200_parameter_load(iree_b200_context_t* context, const iree_b200_parameter_index_t* index,
+                                            const char* key, uint64_t parameter_offset, void* device_ptr,
+                                            uint64_t length);
+/* Writes an archive holding the entries in the order given. */
+iree_b200_status_t iree_b200_parameter_archive_write(const char* path, int64_t entry_count,
+                                                     const iree_b200_parameter_source_t* entries);
 
 /* ---- W4A16 decode without any allocation ---------------------------------------------------------
  * No counterpart in the reference: added for hosts that cannot allocate device memory where

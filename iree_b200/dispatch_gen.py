@@ -36,13 +36,22 @@ class Dispatch:
 @dataclass
 class Plan:
     function: str
-    inputs: List[Dict]             # {"name", "shape", "dtype"}
+    inputs: List[Dict]             # {"name", "shape", "dtype", optional "parameter": "scope::key"}
     outputs: List[Dict]
     transients: List[Dict]         # {"name", "bytes", "zero": bool, "templates": optional kind}
     dispatches: List[Dispatch] = field(default_factory=list)
 
     def to_json(self) -> str:
         return json.dumps(asdict(self), indent=1)
+
+    def bind_parameters(self, bindings: Dict[str, str]) -> "Plan":
+        """Marks inputs as program parameters: {"wq": "model::blk.0.wq"} (scope::key). They are then
+        loaded from a parameter archive instead of arriving as function arguments, the way a
+        compiled program's `#stream.parameter.named<"model"::"blk.0.wq">` globals are."""
+        for decl in self.inputs:
+            if decl["name"] in bindings:
+                decl["parameter"] = bindings[decl["name"]]
+        return self
 
     @staticmethod
     def from_json(text: str) -> "Plan":

@@ -21,8 +21,8 @@ import numpy as np
 from . import runtime as rt
 from .dispatch_gen import Plan
 
-_DTYPES = {"f16": np.float16, "bf16": np.uint16, "i8": np.int8, "si8": np.int8, "ui8": np.uint8, "i32": np.int32,
-           "f32": np.float32}
+_DTYPES = {"f16": np.float16, "bf16": np.uint16, "i8": np.int8, "si8": np.int8, "ui8": np.uint8, "u8": np.uint8,
+           "i32": np.int32, "f32": np.float32}
 
 
 def parse_tensor_flag(text: str):
@@ -41,15 +41,35 @@ def parse_tensor_flag(text: str):
     return arr
 
 
-def execute_plan(ctx: rt.Context, plan: Plan, inputs):
-    """Runs every dispatch of the plan through the raw HAL-level calls; returns the outputs."""
-    if len(inputs) != len(plan.inputs):
-        raise rt.IreeB200Error(3, "function expects %d inputs, %d given" % (len(plan.inputs), len(inputs)))
+def execute_plan(ctx: rt.Context, plan: Plan, inputs, parameters=None):
+    """Runs every dispatch of the plan through the raw HAL-level calls; returns the outputs.
+
+    Inputs the plan binds to a parameter (``"parameter": "scope::key"``, what a compiled program
+    declares as ``#stream.parameter.named<"scope"::"key">``) are loaded from the archives in
+    ``parameters`` (scope -> ParameterIndex) instead of being taken from ``inputs``.
+    """
+    free_inputs = [d for d in plan.inputs if "parameter" not in d]
+    if len(inputs) != len(free_inputs):
+        raise rt.IreeB200Error(3, "function expects %d inputs, %d given" % (len(free_inputs), len(inputs)))
     buffers, owned = {}, []
-    for decl, arr in zip(plan.inputs, inputs):
+    for decl, arr in zip(free_inputs, inputs):
         if list(arr.shape) != list(decl["shape"]):
             raise rt.IreeB200Error(3, "input %s: expected shape %s, got %s" % (decl["name"], decl["shape"], list(arr.shape)))
         buffers[decl["name"]] = ctx.to_device(arr)
+    for decl in plan.inputs:
+        if "parameter" not in decl:
+            continue
+        scope, _, key = decl["parameter"].rpartition("::")
+        index = (parameters or {}).get(scope)
+        if index is None:
+            raise rt.IreeB200Error(5, "no parameter provider registered for scope '%s'" % scope)
+        nbytes = int(np.prod(decl["shape"])) * np.dtype(_DTYPES[decl["dtype"]]).itemsize
+        if index.lookup(key).length != nbytes:
+            raise rt.IreeB200Error(3, "parameter %s holds %d bytes, the program expects %d" % (
+                decl["parameter"], index.lookup(key).length, nbytes))
+        buf = ctx.alloc(max(nbytes, 1))
+        index.load(ctx, key, buf, nbytes)
+        buffers[decl["name"]] = buf
     for decl in plan.outputs:
         n = int(np.prod(decl["shape"])) * np.dtype(_DTYPES[decl["dtype"]]).itemsize
         buffers[decl["name"]] = ctx.alloc(max(n, 1))
@@ -94,6 +114,8 @@ def main(argv=None) -> int:
     ap.add_argument("--module", required=True)
     ap.add_argument("--function", default="")
     ap.add_argument("--input", action="append", default=[])
+    ap.add_argument("--parameters", action="append", default=[],
+                    help="[scope=]file.irpa: parameters of that scope come from the archive (tooling/parameter_util.c)")
     ap.add_argument("--output", action="append", default=[])
     ap.add_argument("--expected_output", action="append", default=[])
     ap.add_argument("--print_statistics", action="store_true")
@@ -106,11 +128,18 @@ def main(argv=None) -> int:
         print("NOT_FOUND: no function @%s in the module (it holds @%s)" % (args.function, plan.function), file=sys.stderr)
         return 1
     inputs = [parse_tensor_flag(t) for t in args.input]
+    from .parameters import ParameterIndex
+    parameters = {}
+    for spec in args.parameters:
+        scope, sep, path = spec.partition("=")
+        if not sep:
+            scope, path = "", spec
+        parameters[scope] = ParameterIndex(path)
     ordinal = int(args.device.split(":")[1]) if ":" in args.device else 0
     ctx = rt.Context(ordinal)
     try:
         print("EXEC @%s" % plan.function)
-        outs = execute_plan(ctx, plan, inputs)
+        outs = execute_plan(ctx, plan, inputs, parameters)
         for i, o in enumerate(outs):
             if i < len(args.output) and args.output[i].startswith("@"):
                 np.save(args.output[i][1:], o)

@@ -1508,14 +1508,17 @@ size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
 
 static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p) {
   const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
-  const int64_t tiles_m = (p->M + 127) / 128;
+  // M >= 256: tiles of 256 rows and at most 128 columns select the kernel's tall variant, which
+  // expands every weight half as often per flop; such a tile costs as much as a 128 x 256 one.
+  const bool tall = p->M >= 256 && (!p->tile_n || p->tile_n <= 128);
+  const int64_t tiles_m = tall ? (p->M + 255) / 256 : (p->M + 127) / 128;
   int best = 0;
   double best_cost = 0;
-  for (int bn = 256; bn >= 32; bn -= 32) {
+  for (int bn = tall ? 128 : 256; bn >= 32; bn -= 32) {
     if (p->tile_n && bn != p->tile_n) continue;
     const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn);
     const int64_t waves = (tiles + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * (400.0 + bn);
+    const double cost = static_cast<double>(waves) * (400.0 + (tall ? 2 * bn : bn));
     if (!best || cost < best_cost * 0.9999) {
       best = bn;
       best_cost = cost;
@@ -1592,7 +1595,8 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     const int32_t constants[6] = {params->M, params->N, params->K, params->ldo, params->n_offset, tile_n};
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 3, bindings));
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
-    const int64_t tiles = static_cast<int64_t>((params->M + 127) / 128) * ((params->N + tile_n - 1) / tile_n);
+    const int tile_rows = (params->M >= 256 && tile_n <= 128) ? 256 : 128;  // the kernel's tall variant
+    const int64_t tiles = static_cast<int64_t>((params->M + tile_rows - 1) / tile_rows) * ((params->N + tile_n - 1) / tile_n);
     const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_gemm");
     return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 3, 6, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);
   }

@@ -38,6 +38,12 @@ constexpr int kW4RawStageBytes = kW4MaxBN * 64;     // 16 KiB: 256 rows x 128 in
 constexpr int kW4Threads = 512;
 constexpr int kW4DequantWarps = 8;
 constexpr int kW4SmemBytes = 1024 + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes + 256;
+// Tall variant (M >= 256 and tiles at most 128 wide): a CTA computes 256 x bn, i.e. two 128-row
+// accumulators that share one expanded weight tile, so every weight is expanded half as often per
+// flop. A stage is then 32 KiB of activations + 16 KiB of weights (the same 48 KiB), and TMEM holds
+// 2 buffers x 2 halves x 128 columns.
+constexpr int kW4TallMaxBN = 128;
+__host__ __device__ constexpr bool w4_tall_variant(int M, int bn) { return M >= 256 && bn <= kW4TallMaxBN; }
 
 struct alignas(128) W4Workspace {
   uint8_t map_a[128];    // f16 [M, K], 128-byte swizzle, box 64 x 128
@@ -50,34 +56,41 @@ __device__ __forceinline__ void w4_report(W4Workspace* ws, uint32_t code, uint32
   if (atomicCAS(&ws->status[0], 0u, code) == 0u) ws->status[1] = info;
 }
 
+template <bool TALL>
 __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, __half* __restrict__ out,
                                             W4Workspace* __restrict__ ws, int M, int N, int K, int ldo, int n_off,
                                             int bn) {
+  constexpr int kHalves = TALL ? 2 : 1;                        // 128-row accumulators per tile
+  constexpr int kTileRows = kHalves * kW4BM;
+  constexpr int kAStageBytes = kHalves * kW4AStageBytes;       // the B tile follows it in the stage
+  constexpr int kAccColumns = TALL ? kW4TallMaxBN : kW4MaxBN;  // TMEM columns per accumulator
+  static_assert(kAStageBytes + kAccColumns * 128 <= kW4StageBytes, "stage layout");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t raw_base = smem_base + kW4Stages * kW4StageBytes;
   const uint32_t bars = raw_base + kW4RawStages * kW4RawStageBytes;
   uint8_t* bars_gen = smem_gen + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes;
-  // barriers: full[3], empty[3], raw_full[2], raw_empty[2], tmem_full[2], tmem_empty[2]
+  // barriers: full[stages], empty[stages], raw_full[2], raw_empty[2], tmem_full[2], tmem_empty[2]
+  constexpr int kS = kW4Stages;
   auto full_bar = [&](int i) { return bars + 8u * i; };
-  auto empty_bar = [&](int i) { return bars + 8u * (3 + i); };
-  auto raw_full_bar = [&](int i) { return bars + 8u * (6 + i); };
-  auto raw_empty_bar = [&](int i) { return bars + 8u * (8 + i); };
-  auto tmem_full_bar = [&](int i) { return bars + 8u * (10 + i); };
-  auto tmem_empty_bar = [&](int i) { return bars + 8u * (12 + i); };
-  const uint32_t tmem_slot = bars + 8u * 14;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * 14);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * 14 + 4);
+  auto empty_bar = [&](int i) { return bars + 8u * (kS + i); };
+  auto raw_full_bar = [&](int i) { return bars + 8u * (2 * kS + i); };
+  auto raw_empty_bar = [&](int i) { return bars + 8u * (2 * kS + 2 + i); };
+  auto tmem_full_bar = [&](int i) { return bars + 8u * (2 * kS + 4 + i); };
+  auto tmem_empty_bar = [&](int i) { return bars + 8u * (2 * kS + 6 + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * kS + 8);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * kS + 8));
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * kS + 8) + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || bn < 32 || bn > kW4MaxBN || (bn & 31);
+  const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || bn < 32 || bn > kAccColumns || (bn & 31);
   if (bad) {
     if (threadIdx.x == 0) w4_report(ws, kStatusBadArgument, 0);
     return;
   }
-  const int tiles_m = (M + kW4BM - 1) / kW4BM;
+  const int tiles_m = (M + kTileRows - 1) / kTileRows;
   const int tiles_n = (N + bn - 1) / bn;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = K / 64;
@@ -144,8 +157,11 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full_bar(st), kW4AStageBytes);
-          tma_load_3d(smem_base + st * kW4StageBytes, ws->map_a, full_bar(st), kb * 64, tm * kW4BM, 0);
+          mbar_arrive_expect_tx(full_bar(st), kAStageBytes);
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h)
+            tma_load_3d(smem_base + st * kW4StageBytes + h * kW4AStageBytes, ws->map_a, full_bar(st), kb * 64,
+                        tm * kTileRows + h * kW4BM, 0);
         }
       }
     }
@@ -164,7 +180,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * kW4MaxBN;
+        const uint32_t d_tmem = tmem_base + buf * kHalves * kAccColumns;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int st = it % kW4Stages;
           const uint32_t ph = (it / kW4Stages) & 1;
@@ -176,13 +192,15 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
           }
           tc_fence_after_sync();
           const uint32_t a_src = smem_base + st * kW4StageBytes;
-          const uint32_t b_src = a_src + kW4AStageBytes;
+          const uint32_t b_src = a_src + kAStageBytes;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t a_desc = make_smem_desc(a_src + k * 32, 16, 1024);
-            const uint64_t b_desc = make_smem_desc(b_src + k * 32, 16, 1024);
-            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t a_desc = make_smem_desc(a_src + h * kW4AStageBytes + k * 32, 16, 1024);
+              const uint64_t b_desc = make_smem_desc(b_src + k * 32, 16, 1024);
+              mma_f16_ss(d_tmem + h * kAccColumns, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
           tc_commit(empty_bar(st));
         }
         if (ok) tc_commit(tmem_full_bar(buf));
@@ -206,10 +224,11 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         break;
       }
       tc_fence_after_sync();
-      const int row = tm * kW4BM + qd * 32 + lane;
+      for (int h = 0; h < kHalves; ++h) {
+      const int row = tm * kTileRows + h * kW4BM + qd * 32 + lane;
       for (int c = 0; c < bn; c += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + buf * kW4MaxBN + c, v);
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + (buf * kHalves + h) * kAccColumns + c, v);
         tc_wait_ld();
         const int col0 = tn * bn + c;
         if (row < M && col0 < N) {
@@ -230,6 +249,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
           }
         }
       }
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
@@ -238,7 +258,9 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
     // -------- dequant: raw int4 (64-byte swizzled rows) -> f16 K-major 128-byte swizzled tile -----
     // Thread r of the 256 handles weight row r of the tile: 64 K per block = 32 raw bytes in,
     // one 128-byte operand row out.
-    const int r = threadIdx.x - 256;
+    // (Tall variant: at most 128 rows, so two threads share a row, one per 16-byte raw chunk.)
+    const int r = TALL ? ((threadIdx.x - 256) & 127) : (threadIdx.x - 256);
+    const int part = TALL ? ((threadIdx.x - 256) >> 7) : 0;
     uint32_t it = 0, raw_it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -278,10 +300,10 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         if (row_live) {
           // Raw stage: row r is 64 bytes; its four 16-byte chunks are XOR-swizzled by (r / 2) % 4.
           const uint8_t* raw_row = smem_gen + kW4Stages * kW4StageBytes + rs * kW4RawStageBytes + r * 64;
-          uint8_t* b_row = smem_gen + st * kW4StageBytes + kW4AStageBytes + r * 128;
+          uint8_t* b_row = smem_gen + st * kW4StageBytes + kAStageBytes + r * 128;
           const int sw_raw = (r >> 1) & 3, sw_b = r & 7;
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = TALL ? part : 0; c < (TALL ? part + 1 : 2); ++c) {
             const int chunk = (kb & 1) * 2 + c;  // 16-byte chunk of the 64-byte raw row
             const uint4 w = *reinterpret_cast<const uint4*>(raw_row + ((chunk ^ sw_raw) << 4));
             const uint32_t words[4] = {w.x, w.y, w.z, w.w};
@@ -340,7 +362,10 @@ extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
 
 extern "C" __global__ void __launch_bounds__(kW4Threads, 1)
     b200_w4a16_gemm(const __half* scales, __half* out, void* ws, int M, int N, int K, int ldo, int n_off, int bn) {
-  w4gemm_body(scales, out, reinterpret_cast<W4Workspace*>(ws), M, N, K, ldo, n_off, bn);
+  if (w4_tall_variant(M, bn))
+    w4gemm_body<true>(scales, out, reinterpret_cast<W4Workspace*>(ws), M, N, K, ldo, n_off, bn);
+  else
+    w4gemm_body<false>(scales, out, reinterpret_cast<W4Workspace*>(ws), M, N, K, ldo, n_off, bn);
 }
 
 // Any M, N and any K that is a multiple of the (even) group size. One thread per output

@@ -133,8 +133,16 @@ def plan_w4a16(function: str, M: int, N: int, K: int, group: int = 128, ldo: Opt
                                         [M, N, K, ldo, n_offset], (max(1, min(N // 16, sm_count // ksplit)), ksplit, 1),
                                         (DECODE_THREADS, 1, 1), DECODE_SMEM[mh]))
     elif group == 128 and K % 128 == 0:
-        bn = choose_tile_n(M, N, 1, 32, sm_count)
-        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+        # M >= 256: 256-row tiles of at most 128 columns (the kernel's tall variant), costed like 128 x 2bn tiles
+        tall = M >= 256
+        rows = 256 if tall else 128
+        bn, best = 0, 0.0
+        for cand in range(128 if tall else 256, 31, -32):
+            t = ((M + rows - 1) // rows) * ((N + cand - 1) // cand)
+            cost = ((t + sm_count - 1) // sm_count) * (400.0 + (2 * cand if tall else cand))
+            if not bn or cost < best * 0.9999:
+                bn, best = cand, cost
+        tiles = ((M + rows - 1) // rows) * ((N + bn - 1) // bn)
         plan.transients.append({"name": "workspace", "bytes": 512, "zero": True,
                                 "host_tensor_maps": {"kind": "w4a16", "M": M, "N": N, "K": K, "tile_n": bn}})
         plan.dispatches.append(Dispatch("b200_w4a16_gemm", ["scales", "out", "workspace"],

@@ -328,7 +328,7 @@ typedef struct {
   int32_t tile_n;    /* 0 = choose (tensor-core kernel only) */
 } iree_b200_w4a16_params_t;
 /* Device workspace the dispatch needs for an N-column weight matrix: tensor maps, status words
- * and the f32 scratch of the decode kernel's split-K reduction. It must be zero-filled once
+ * and the f32 scratch the decode kernel uses when K > 4096. It must be zero-filled once
  * after allocation; the kernels leave the scratch zeroed. One workspace serves one dispatch in
  * flight. */
 size_t iree_b200_w4a16_workspace_bytes(int32_t N);
@@ -481,7 +481,7 @@ iree_b200_status_t iree_b200_parameter_archive_write(const char* path, int64_t e
  * No counterpart in the reference: added for hosts that cannot allocate device memory where
  * they dispatch (inside a stream capture, after handing all memory to their own pool, or on a
  * path that must not take the driver's allocation lock). Same arithmetic and the same kernel
- * body as IREE_B200_W4A16_DECODE, but the split-K scratch is a fixed array inside the
+ * body as IREE_B200_W4A16_DECODE, but the K > 4096 scratch is a fixed array inside the
  * library's device image, so only inputs and outputs are passed; nothing is allocated or freed,
  * here or in any library this calls.
  *   - runs on the CUDA device that is current on the calling thread, on `stream` (a

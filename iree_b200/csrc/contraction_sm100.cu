@@ -162,7 +162,6 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   auto tmem_full_bar = [&](int i) { return bars + 8u * (2 * kStages + i); };
   auto tmem_empty_bar = [&](int i) { return bars + 8u * (2 * kStages + 2 + i); };
   const uint32_t tmem_slot = bars + 8u * (2 * kStages + 4);
-  const uint32_t abort_slot = tmem_slot + 4;
   uint8_t* smem_generic = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* abort_flag =
       reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + 8 * (2 * kStages + 4) + 4);

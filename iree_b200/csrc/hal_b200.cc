@@ -387,6 +387,10 @@ struct iree_hal_b200_device_t {
   // order it against the dispatch stream (created on first use).
   CUstream collective_stream = nullptr;
   CUevent dispatch_done = nullptr, collective_done = nullptr;
+  // Third stream for device -> host copies that run under the next host -> device copy in the
+  // host-buffer entry points (created on first use).
+  CUstream readback_stream = nullptr;
+  CUevent readback_ready = nullptr;
   int sm_count = 0, cc = 0, max_smem = 0;
   char name[128] = {0};
 };
@@ -483,6 +487,11 @@ void iree_hal_b200_device_release(iree_hal_b200_device_t* device) {
     g_cu.cuStreamDestroy(device->collective_stream);
     g_cu.cuEventDestroy(device->dispatch_done);
     g_cu.cuEventDestroy(device->collective_done);
+  }
+  if (device->readback_stream) {
+    g_cu.cuStreamSynchronize(device->readback_stream);
+    g_cu.cuStreamDestroy(device->readback_stream);
+    g_cu.cuEventDestroy(device->readback_ready);
   }
   if (device->stream) {
     g_cu.cuStreamSynchronize(device->stream);
@@ -1295,6 +1304,24 @@ iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int
   return encode_map(dt, elem_bytes, CU_TENSOR_MAP_SWIZZLE_128B, 128, device_ptr, dim0, dim1, dim2, box0, box1, out_map);
 }
 
+// The 512-byte workspace header of a TMA-eligible product, encoded on the host: tensor maps of
+// both operands (for the tile width `bn`), status words zero.
+static iree_b200_status_t encode_workspace_header(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
+                                                  const void* lhs, const void* rhs, int bn, uint8_t* host) {
+  memset(host, 0, IREE_B200_WORKSPACE_BYTES);
+  const int es = elem_bytes_of(params->kind);
+  const uint32_t bk = 128 / es;
+  const uint32_t M = params->M, N = params->N, K = params->K, B = params->batch;
+  const int bf = params->kind == IREE_B200_KIND_BF16;
+  // A box: 128 rows, or 32 in the few-rows variant (the same rule as in the kernels)
+  const uint32_t a_rows = (params->M <= 32 && bn <= 128) ? 32 : 128;
+  B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, lhs, K, M, B, bk, a_rows, host));
+  if (params->rhs_layout == IREE_B200_RHS_NK)
+    return iree_b200_encode_tensor_map(context, es, bf, rhs, K, N, B, bk, use_pairs(context, params) ? bn / 2 : bn,
+                                       host + 128);
+  return iree_b200_encode_tensor_map(context, es, bf, rhs, N, K, B, bk, bk, host + 128);
+}
+
 iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
                                             const void* lhs, const void* rhs, void* workspace, int32_t* out_tile_n) {
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
@@ -1338,17 +1365,7 @@ iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const 
     return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 4, 7, 1, 1, 1);
   }
   uint8_t host[IREE_B200_WORKSPACE_BYTES];
-  memset(host, 0, sizeof host);
-  const int bf = params->kind == IREE_B200_KIND_BF16;
-  // A box: 128 rows, or 32 in the few-rows variant (the same rule as in the kernels)
-  const uint32_t a_rows = (params->M <= 32 && bn <= 128) ? 32 : 128;
-  B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, lhs, K, M, B, bk, a_rows, host));
-  if (params->rhs_layout == IREE_B200_RHS_NK) {
-    B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, K, N, B, bk,
-                                                     use_pairs(context, params) ? bn / 2 : bn, host + 128));
-  } else {
-    B200_RETURN_IF_ERROR(iree_b200_encode_tensor_map(context, es, bf, rhs, N, K, B, bk, bk, host + 128));
-  }
+  B200_RETURN_IF_ERROR(encode_workspace_header(context, params, lhs, rhs, bn, host));
   // The source is pageable, so the driver has consumed it when this returns.
   return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
 }
@@ -1430,6 +1447,28 @@ iree_b200_status_t iree_b200_workspace_status(iree_b200_context_t* context, cons
   }
 }
 
+}  // extern "C"
+
+namespace {
+
+// Device -> host copy of `bytes` on the readback stream, ordered after everything recorded on the
+// dispatch stream so far.
+iree_b200_status_t readback_after_dispatch(iree_hal_b200_device_t* d, const void* src, void* dst, size_t bytes) {
+  if (!d->readback_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->readback_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->readback_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->readback_ready, d->stream), "cuEventRecord");
+  CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->readback_stream, d->readback_ready, 0), "cuStreamWaitEvent");
+  CU_RETURN_IF_ERROR(g_cu.cuMemcpyDtoHAsync(dst, reinterpret_cast<CUdeviceptr>(src), bytes, d->readback_stream),
+                     "cuMemcpyDtoHAsync");
+  return IREE_B200_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
 iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
                                          const void* lhs, const void* rhs, void* out, const float* row_scale,
                                          const float* col_scale) {
@@ -1442,10 +1481,25 @@ iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const ire
   const size_t c_bytes = static_cast<size_t>(params->batch) * params->M * params->N * os;
   if (!c_bytes) return IREE_B200_STATUS_OK;
   const bool requant = params->epilogue == IREE_B200_EPILOGUE_REQUANT_F16;
+  if (requant && (!row_scale || !col_scale))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the requant epilogue needs row and column scales");
   auto* d = context->device;
   auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  // A product whose operands and result are many megabytes spends its time on the bus, not in
+  // the kernel. It is then run as row blocks of the left-hand side: the block's rows go up, its
+  // dispatch runs, and its result comes back on a second stream while the next block goes up, so
+  // the two directions of the link work at the same time.
+  constexpr int kMaxBlocks = 8;
+  int blocks = 1;
+  if (params->batch == 1 && params->M >= 1024 && a_bytes + c_bytes >= (static_cast<size_t>(16) << 20)) {
+    blocks = params->M / 512;
+    if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  }
+  const int block_rows = blocks > 1 ? ((params->M + blocks - 1) / blocks + 255) / 256 * 256 : params->M;
+  if (blocks > 1) blocks = (params->M + block_rows - 1) / block_rows;
   const size_t rs_bytes = requant ? sizeof(float) * params->M : 0, cs_bytes = requant ? sizeof(float) * params->N : 0;
-  const size_t need = up(IREE_B200_WORKSPACE_BYTES) + up(a_bytes) + up(b_bytes) + up(c_bytes) + up(rs_bytes) + up(cs_bytes);
+  const size_t need = up(static_cast<size_t>(blocks) * IREE_B200_WORKSPACE_BYTES) + up(a_bytes) + up(b_bytes) + up(c_bytes) +
+                      up(rs_bytes) + up(cs_bytes);
   if (need > context->arena_size) {
     B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
     if (context->arena) B200_RETURN_IF_ERROR(iree_hal_b200_buffer_free(d, context->arena));
@@ -1455,26 +1509,72 @@ iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const ire
     context->arena_size = need;
   }
   uint8_t* base = static_cast<uint8_t*>(context->arena);
-  void* ws = base;
-  void* da = base + up(IREE_B200_WORKSPACE_BYTES);
-  void* db = static_cast<uint8_t*>(da) + up(a_bytes);
-  void* dc = static_cast<uint8_t*>(db) + up(b_bytes);
-  float* drs = reinterpret_cast<float*>(static_cast<uint8_t*>(dc) + up(c_bytes));
+  uint8_t* ws = base;
+  uint8_t* da = base + up(static_cast<size_t>(blocks) * IREE_B200_WORKSPACE_BYTES);
+  uint8_t* db = da + up(a_bytes);
+  uint8_t* dc = db + up(b_bytes);
+  float* drs = reinterpret_cast<float*>(dc + up(c_bytes));
   float* dcs = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(drs) + up(rs_bytes));
-  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, lhs, da, a_bytes));
+  if (blocks == 1) B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, ws, IREE_B200_WORKSPACE_BYTES, 0));
   B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, rhs, db, b_bytes));
   if (requant) {
-    if (!row_scale || !col_scale)
-      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the requant epilogue needs row and column scales");
     B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, row_scale, drs, rs_bytes));
     B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, col_scale, dcs, cs_bytes));
   }
-  B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, ws, IREE_B200_WORKSPACE_BYTES, 0));
-  B200_RETURN_IF_ERROR(iree_b200_matmul(context, params, da, db, dc, requant ? drs : nullptr, requant ? dcs : nullptr, ws));
-  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(d, dc, out, c_bytes));
-  // Reads the status words back and waits for the stream: the result is in `out` on return.
-  return iree_b200_workspace_status(context, ws);
+  if (blocks == 1) {
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, lhs, da, a_bytes));
+    B200_RETURN_IF_ERROR(iree_b200_matmul(context, params, da, db, dc, requant ? drs : nullptr, requant ? dcs : nullptr, ws));
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(d, dc, out, c_bytes));
+    // Reads the status words back and waits for the stream: the result is in `out` on return.
+    return iree_b200_workspace_status(context, ws);
+  }
+  // Every block's workspace header (tensor maps) is encoded first and uploaded in one copy, so
+  // that no small host copy sits between the large ones.
+  uint8_t headers[kMaxBlocks * IREE_B200_WORKSPACE_BYTES];
+  int32_t block_tile_n[kMaxBlocks] = {0};
+  memset(headers, 0, sizeof headers);
+  for (int b = 0; b < blocks; ++b) {
+    const int row0 = b * block_rows;
+    iree_b200_matmul_params_t bp = *params;
+    bp.M = params->M - row0 < block_rows ? params->M - row0 : block_rows;
+    const uint8_t* a_block = da + static_cast<size_t>(row0) * params->K * es;
+    if (tma_eligible(&bp, a_block, db) && bp.K) {
+      block_tile_n[b] = choose_tile_n(context, &bp);
+      if (!block_tile_n[b]) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tile_n %d is not usable for this layout", bp.tile_n);
+      B200_RETURN_IF_ERROR(encode_workspace_header(context, &bp, a_block, db, block_tile_n[b],
+                                                   headers + static_cast<size_t>(b) * IREE_B200_WORKSPACE_BYTES));
+    }
+  }
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, headers, ws, static_cast<size_t>(blocks) * IREE_B200_WORKSPACE_BYTES));
+  for (int b = 0; b < blocks; ++b) {
+    const int row0 = b * block_rows;
+    iree_b200_matmul_params_t bp = *params;
+    bp.M = params->M - row0 < block_rows ? params->M - row0 : block_rows;
+    const size_t a_off = static_cast<size_t>(row0) * params->K * es, c_off = static_cast<size_t>(row0) * params->N * os;
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, static_cast<const uint8_t*>(lhs) + a_off, da + a_off,
+                                                    static_cast<size_t>(bp.M) * params->K * es));
+    B200_RETURN_IF_ERROR(iree_b200_matmul_run(context, &bp, da + a_off, db, dc + c_off, requant ? drs + row0 : nullptr,
+                                              requant ? dcs : nullptr, ws + static_cast<size_t>(b) * IREE_B200_WORKSPACE_BYTES,
+                                              block_tile_n[b]));
+    B200_RETURN_IF_ERROR(readback_after_dispatch(d, dc + c_off, static_cast<uint8_t*>(out) + c_off,
+                                                 static_cast<size_t>(bp.M) * params->N * os));
+  }
+  // one read of every block's status words, then wait for both streams
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(d, ws, headers, static_cast<size_t>(blocks) * IREE_B200_WORKSPACE_BYTES));
+  B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
+  CU_RETURN_IF_ERROR(g_cu.cuStreamSynchronize(d->readback_stream), "cuStreamSynchronize");
+  for (int b = 0; b < blocks; ++b) {
+    uint32_t status[2];
+    memcpy(status, headers + static_cast<size_t>(b) * IREE_B200_WORKSPACE_BYTES + 384, sizeof status);
+    if (status[0] == 5) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "kernel rejected its arguments (shape / alignment)");
+    if (status[0]) return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[0], status[1]);
+  }
+  return IREE_B200_STATUS_OK;
 }
+
+}  // extern "C"
+
+extern "C" {
 
 // ---- fused int4 dequant + matmul ---------------------------------------------------------------------
 static int w4_variant(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p, const void* a, const void* wq,
@@ -1648,7 +1748,7 @@ iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree
   void* dw = static_cast<uint8_t*>(da) + up(a_bytes);
   void* ds = static_cast<uint8_t*>(dw) + up(w_bytes);
   void* dc = static_cast<uint8_t*>(ds) + up(s_bytes);
-  // The split-K scratch must start at zero; the kernel leaves it zero afterwards, but the arena
+  // The decode scratch (K > 4096) must start at zero; the kernel leaves it zero afterwards, but the arena
   // is shared with other entry points, so it is cleared on every call here (a few hundred KiB).
   B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, ws, ws_bytes, 0));
   B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, a, da, a_bytes));

@@ -4,7 +4,7 @@
 // running inside a CUDA stream capture (allocation is not a capturable operation), a serving
 // loop that has handed every byte of device memory to its own pool, or a real-time path that is
 // not allowed to take the driver's allocation lock. The regular entry point needs a
-// caller-provided workspace for the split-K reduction; this one brings its own, a fixed array
+// caller-provided workspace for the scratch of K > 4096; this one brings its own, a fixed array
 // that lives in the library's device image, so the caller passes nothing but inputs and outputs.
 //
 // The scratch is a file-scope `static __device__` array. In host code that name is only a
@@ -23,7 +23,7 @@
 
 namespace {
 
-// f32 partial sums [16][N] + one arrival counter per 16-row tile, for N up to the stated maximum.
+// f32 partial sums [16][N] (+ one spare word per 16-row tile), for N up to the stated maximum.
 constexpr int kMaxN = IREE_B200_NOALLOC_MAX_N;
 constexpr size_t kScratchBytes = static_cast<size_t>(16) * kMaxN * 4 + static_cast<size_t>(kMaxN / 16) * 4;
 
@@ -104,7 +104,7 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
   if (K > 4096) {
     // Every call shares the array and it keeps what the last call left there. The kernel zeroes
     // what it used, but a call that was cut short would not have, so the part this call will
-    // use is cleared first: the partial sums [16][N] and the counters that follow them.
+    // use is cleared first: the partial sums [16][N] and the spare words that follow them.
     const size_t used = static_cast<size_t>(16) * N * 4 + static_cast<size_t>(N / 16) * 4;
     e = cudaMemsetAsync(scratch, 0, used, s);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(scratch)");

@@ -8,13 +8,14 @@
 // Three kernels:
 //   b200_w4a16_decode_m8 / _m16  M <= 8 / 16: HBM-bound weight streaming. 16 warps each own a
 //       256-wide slice of K and keep the activations of that slice in registers for the whole
-//       kernel; weights go global -> registers -> f16 fragments -> mma.sync (f32 accumulate);
-//       the per-group scale is applied to the f32 group sum. One 32 KiB contiguous block of
-//       weights (16 rows) per tile. K beyond 4096 is split over gridDim.y with an f32 scratch
-//       reduction that cleans up after itself.
+//       kernel; weights go global -> shared (bulk copies into a 4-stage ring, one 32 KiB block of
+//       16 rows per tile) -> f16 fragments -> mma.sync (f32 accumulate); the per-group scale is
+//       applied to the f32 group sum. K beyond 4096 is covered by successive passes of the same
+//       CTA over an f32 scratch that it leaves zeroed.
 //   b200_w4a16_gemm             larger M: tcgen05. Raw int4 tiles and activation tiles arrive by
 //       TMA; 8 warps expand the weights to f16 (exactly the dequant arithmetic above) into the
-//       128-byte-swizzled operand layout; one thread issues kind::f16 MMAs into TMEM.
+//       128-byte-swizzled operand layout; one thread issues kind::f16 MMAs into TMEM. 128-row
+//       tiles, or 256-row tiles sharing one expanded weight tile when M >= 256.
 //   b200_w4a16_generic          any shape with K % group == 0: one thread per output.
 #include <cuda_fp16.h>
 #include <stdint.h>

@@ -220,7 +220,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
     auto produce = [&](int jp) -> bool {
       if (jp >= my_tiles || warp != jp % kDecodeWarps) return true;
       const int st = jp % kDecodeStages;
-      if (!__all_sync(0xffffffffu, mbar_wait(wempty_bar(st), ((jp / kDecodeStages) & 1) ^ 1, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait<false>(wempty_bar(st), ((jp / kDecodeStages) & 1) ^ 1, abort_flag))) {
         *abort_flag = 1;
         return false;
       }
@@ -316,7 +316,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
     auto finalize = [&](int jf) -> bool {
       const int slot = jf % kDecodeSlots;
       const int tile = blockIdx.x + jf * gridDim.x;
-      if (!__all_sync(0xffffffffu, mbar_wait(pfull_bar(slot), (jf / kDecodeSlots) & 1, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait<false>(pfull_bar(slot), (jf / kDecodeSlots) & 1, abort_flag))) {
         *abort_flag = 1;
         return false;
       }
@@ -365,7 +365,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
     bool ok = true;
     for (int j = 0; j < my_tiles && ok; ++j) {
       const int st = j % kDecodeStages;
-      if (!__all_sync(0xffffffffu, mbar_wait(wfull_bar(st), (j / kDecodeStages) & 1, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait<false>(wfull_bar(st), (j / kDecodeStages) & 1, abort_flag))) {
         *abort_flag = 1;
         break;
       }
@@ -452,7 +452,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
       // ---- leave this K chunk's partial sums in the tile's slot ------------------------------------
       {
         const int slot = j % kDecodeSlots;
-        if (!__all_sync(0xffffffffu, mbar_wait(pempty_bar(slot), ((j / kDecodeSlots) & 1) ^ 1, abort_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait<false>(pempty_bar(slot), ((j / kDecodeSlots) & 1) ^ 1, abort_flag))) {
           *abort_flag = 1;
           break;
         }

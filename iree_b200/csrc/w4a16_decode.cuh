@@ -138,11 +138,12 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 #endif
 
 // The weights enter the MMA as the biased halves the bit trick produces, without a subtract:
-//   low nibbles  -> 1032 + w        (0x6400 | (n ^ 8))
-//   high nibbles -> 1152 + 16 w     (0x6400 | ((n ^ 8) << 4))
-// Low- and high-nibble weights accumulate separately; with S = sum of the activations that met
-// them, the group sum is (d_lo - 1032 S_lo) + (d_hi / 16 - 72 S_hi). All of this is exact for
-// integer data and loses < 1e-4 relative on normal data (f32 accumulation of terms ~1e3 |a|).
+//   low nibbles  -> 1032 + w      0x6400 | (n ^ 8): the nibble sits in the last mantissa bits of 1024
+//   high nibbles ->   72 + w      0x5400 | ((n ^ 8) << 4): in f16, 64 has a mantissa step of 1/16, so
+//                                 a nibble four bits up adds exactly its value
+// Both feed the same accumulator; with S_lo / S_hi the sums of the activations that met the low /
+// high nibbles, the group sum is d - (1032 S_lo + 72 S_hi). All of this is exact for integer data
+// and loses < 1e-4 relative on normal data (f32 accumulation of terms ~1e3 |a|).
 template <int MH>
 __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const uint8_t* __restrict__ wq,
                                             const __half* __restrict__ scales, __half* __restrict__ out,
@@ -409,11 +410,11 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
       if (has_chunk) {
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          float dlo[MH][4], dhi[MH][4];
+          float d[MH][4];
 #pragma unroll
           for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) dlo[mh][c] = dhi[mh][c] = 0.f;
+            for (int c = 0; c < 4; ++c) d[mh][c] = 0.f;
           const uint32_t wl[4] = {w[s][0].x, w[s][0].y, w[s][0].z, w[s][0].w};  // weight row g
           const uint32_t wh[4] = {w[s][1].x, w[s][1].y, w[s][1].z, w[s][1].w};  // weight row g + 8
 #pragma unroll
@@ -423,14 +424,14 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
             const uint32_t lo_b = lop3_and_xor(wh[i], 0x000f000fu, 0x64086408u);
             const uint32_t lo_c = lop3_and_xor(l8, 0x000f000fu, 0x64086408u);     // (w2, w6) + 1032
             const uint32_t lo_d = lop3_and_xor(h8, 0x000f000fu, 0x64086408u);
-            const uint32_t hi_a = lop3_and_xor(wl[i], 0x00f000f0u, 0x64806480u);  // 16 (w1, w5) + 1152
-            const uint32_t hi_b = lop3_and_xor(wh[i], 0x00f000f0u, 0x64806480u);
-            const uint32_t hi_c = lop3_and_xor(l8, 0x00f000f0u, 0x64806480u);     // 16 (w3, w7) + 1152
-            const uint32_t hi_d = lop3_and_xor(h8, 0x00f000f0u, 0x64806480u);
+            const uint32_t hi_a = lop3_and_xor(wl[i], 0x00f000f0u, 0x54805480u);  // (w1, w5) + 72
+            const uint32_t hi_b = lop3_and_xor(wh[i], 0x00f000f0u, 0x54805480u);
+            const uint32_t hi_c = lop3_and_xor(l8, 0x00f000f0u, 0x54805480u);     // (w3, w7) + 72
+            const uint32_t hi_d = lop3_and_xor(h8, 0x00f000f0u, 0x54805480u);
 #pragma unroll
             for (int mh = 0; mh < MH; ++mh) {
-              mma_m16n8k16(dlo[mh], lo_a, lo_b, lo_c, lo_d, bfrag[mh][s][i][0], bfrag[mh][s][i][2]);
-              mma_m16n8k16(dhi[mh], hi_a, hi_b, hi_c, hi_d, bfrag[mh][s][i][1], bfrag[mh][s][i][3]);
+              mma_m16n8k16(d[mh], lo_a, lo_b, lo_c, lo_d, bfrag[mh][s][i][0], bfrag[mh][s][i][2]);
+              mma_m16n8k16(d[mh], hi_a, hi_b, hi_c, hi_d, bfrag[mh][s][i][1], bfrag[mh][s][i][3]);
             }
           }
           // One step is exactly one scale group of rows g and g + 8.
@@ -441,7 +442,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
             const float2 off = MH == 2 ? bias_smem[(2 * mh + s) * 32] : make_float2(bias[mh][s][0], bias[mh][s][1]);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              const float group_sum = fmaf(dhi[mh][c], 0.0625f, dlo[mh][c]) - ((c & 1) ? off.y : off.x);
+              const float group_sum = d[mh][c] - ((c & 1) ? off.y : off.x);
               acc[mh][c] = fmaf(c < 2 ? s_lo : s_hi, group_sum, acc[mh][c]);
             }
           }

@@ -308,6 +308,9 @@ def run_b200(args, wl):
     # first weight tiles, before the dispatch ahead of them has finished; stream order of every
     # read of an earlier result is kept by the kernels themselves.
     ctx.set_dispatch_overlap(True)
+    if world > 1 and int(os.environ.get("IREE_B200_RESERVED_SMS", "0")):
+        # optional: leave SMs free for the collective's blocks (measured at 2 GPUs: no gain, off by default)
+        ctx.set_reserved_sms(int(os.environ["IREE_B200_RESERVED_SMS"]))
 
     channel = None
     if world > 1:

@@ -364,6 +364,12 @@ iree_b200_status_t iree_b200_w4a16_run_sequence(iree_b200_context_t* context, co
  * exports that order themselves on the device with overlap, and every other export normally.
  * Off by default. */
 iree_b200_status_t iree_b200_context_set_dispatch_overlap(iree_b200_context_t* context, int32_t enable);
+/* The kernels are persistent: a dispatch fills every SM with one block for its whole duration, so
+ * a collective enqueued on another stream (iree_hal_b200_command_buffer_all_gather_overlapped)
+ * would only get SMs when the dispatch ends. Reserving `count` SMs makes the operator entry
+ * points size their grids (and choose tiles) for the remaining ones, so that the collective's
+ * blocks run beside the dispatch. 0 (the default) uses every SM. */
+iree_b200_status_t iree_b200_context_set_reserved_sms(iree_b200_context_t* context, int32_t count);
 
 /* ---- data-tiled entry points: pack / unpack / mmt4d -------------------------------------------
  *

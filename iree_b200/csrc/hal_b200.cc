@@ -1109,7 +1109,19 @@ struct iree_b200_context_t {
   size_t arena_size = 0;
   bool arena_w4_clean = true;
   bool dispatch_overlap = false;
+  // SMs the operator entry points leave free (for collectives that run beside the dispatches)
+  int reserved_sms = 0;
 };
+
+namespace {
+// SMs the persistent kernels of this context may fill: all of them, less the reserved ones, even.
+int usable_sms(const iree_b200_context_t* ctx) {
+  int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  sms -= ctx->reserved_sms;
+  if (sms < 2) sms = 2;
+  return sms & ~1;
+}
+}  // namespace
 
 namespace {
 
@@ -1170,7 +1182,7 @@ bool tma_eligible(const iree_b200_matmul_params_t* p, const void* lhs, const voi
 bool use_pairs(const iree_b200_context_t* ctx, const iree_b200_matmul_params_t* p) {
   if (p->flags & IREE_B200_FLAG_SINGLE_CTA) return false;
   if (p->flags & IREE_B200_FLAG_PAIR_CTAS) return true;
-  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const int sms = usable_sms(ctx);
   const int64_t tiles = static_cast<int64_t>((p->M + 255) / 256) * ((p->N + 255) / 256) * p->batch;
   return p->M >= 256 && tiles >= sms / 2 && p->K >= 512;
 }
@@ -1180,7 +1192,7 @@ int choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_matmul_params_
   const bool pairs = use_pairs(ctx, p);
   // In pair mode each CTA holds half a tile: the half must be whole 128-byte column chunks.
   const int chunk = (p->rhs_layout == IREE_B200_RHS_KN) ? (pairs ? 2 : 1) * 128 / es : (pairs ? 64 : 32);
-  const int sms = (ctx->device->sm_count > 0 ? ctx->device->sm_count : 148) / (pairs ? 2 : 1);
+  const int sms = usable_sms(ctx) / (pairs ? 2 : 1);
   const int64_t tiles_m = (p->M + (pairs ? 255 : 127)) / (pairs ? 256 : 128);
   int best = 0;
   double best_score = -1;
@@ -1262,6 +1274,13 @@ iree_b200_status_t iree_b200_context_set_dispatch_overlap(iree_b200_context_t* c
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_set_dispatch_overlap(context->command_buffer, enable));
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_set_dispatch_overlap(context->command_buffer, 0));
   context->dispatch_overlap = enable != 0;
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_b200_context_set_reserved_sms(iree_b200_context_t* context, int32_t count) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
+  if (count < 0 || count > sms - 2) return fail(IREE_B200_STATUS_OUT_OF_RANGE, "cannot reserve %d of %d SMs", count, sms);
+  context->reserved_sms = count;
   return IREE_B200_STATUS_OK;
 }
 iree_hal_b200_device_t* iree_b200_context_device(iree_b200_context_t* c) { return c ? c->device : nullptr; }
@@ -1401,7 +1420,7 @@ iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree
   }
   if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
   if (tile_n <= 0) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "run() needs the tile_n that prepare() returned");
-  const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
+  const int sms = usable_sms(context);
   uint32_t grid;
   if (pairs) {
     const int64_t tiles =
@@ -1607,7 +1626,7 @@ size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
 }
 
 static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p) {
-  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const int sms = usable_sms(ctx);
   // M >= 256: tiles of 256 rows and at most 128 columns select the kernel's tall variant, which
   // expands every weight half as often per flop; such a tile costs as much as a 128 x 256 one.
   const bool tall = p->M >= 256 && (!p->tile_n || p->tile_n <= 128);
@@ -1661,7 +1680,7 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
   if (!a || !wq || !scales || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
   auto* cb = context->command_buffer;
   auto* exe = context->executable;
-  const int sms = context->device->sm_count > 0 ? context->device->sm_count : 148;
+  const int sms = usable_sms(context);
   if (variant == IREE_B200_W4A16_DECODE) {
     if (params->group_size != 128 || params->M > 16 || params->N % 16 || params->K % 256 || params->K > 16384)
       return fail(IREE_B200_STATUS_INVALID_ARGUMENT,
@@ -1849,7 +1868,7 @@ iree_b200_status_t tiling_dispatch(iree_b200_context_t* ctx, bool pack, int es, 
                           : (es == 1 ? "b200_unpack_b8" : es == 2 ? "b200_unpack_b16" : "b200_unpack_b32");
   const int32_t ord = iree_hal_b200_executable_lookup(ctx->executable, name);
   if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export %s missing from the executable", name);
-  const int sms = ctx->device->sm_count > 0 ? ctx->device->sm_count : 148;
+  const int sms = usable_sms(ctx);
   const uint32_t grid = tiling_grid(t0, t1, t2, t3, kernel_flags, es, sms);
   auto* cb = ctx->command_buffer;
   iree_hal_b200_descriptor_set_binding_t bindings[2] = {{0, const_cast<void*>(in)}, {1, out}};

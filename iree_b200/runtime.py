@@ -216,6 +216,10 @@ class Context:
         """Lets exports that order themselves on the device start before the dispatch ahead has finished."""
         check(library().iree_b200_context_set_dispatch_overlap(self.handle, C.c_int32(1 if enable else 0)))
 
+    def set_reserved_sms(self, count: int) -> None:
+        """Leaves `count` SMs free of the persistent kernels (for collectives running beside them)."""
+        check(library().iree_b200_context_set_reserved_sms(self.handle, C.c_int32(count)))
+
     def begin_graph(self) -> None:
         check(library().iree_hal_b200_command_buffer_begin_graph(self.command_buffer))
 

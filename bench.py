@@ -295,6 +295,33 @@ def dist_broadcast_bytes(world, rank, data, size):
     return bytes(t.numpy().tobytes())
 
 
+def make_peer_gather(ctx, channel, rank, world, gathers):
+    """All-gather by peer copies when IREE_B200_ALLGATHER=peer asks for it (default: the NCCL collective)."""
+    if channel is None or os.environ.get("IREE_B200_ALLGATHER", "nccl") == "nccl":
+        return None
+    from iree_b200.sharding import PeerGather
+    return PeerGather(ctx, channel, rank, world, gathers)
+
+
+def verify_gather(ctx, world, rank, send_buffers, gather_buffers, slot_bytes):
+    """Every slot of every receive buffer must hold the block the owning rank computed (checksums
+    travel over the control plane). Run after the timed region, with all streams idle."""
+    import torch
+    import torch.distributed as dist
+    mine = torch.zeros(len(send_buffers), dtype=torch.int64)
+    for k, b in enumerate(send_buffers):
+        mine[k] = int(b.download(np.uint16, (slot_bytes // 2,)).astype(np.uint64).sum() & np.uint64(0x7fffffffffffffff))
+    everyone = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    bad = 0
+    for k, g in enumerate(gather_buffers):
+        host = g.download(np.uint16, (world, slot_bytes // 2))
+        for p in range(world):
+            got = int(host[p].astype(np.uint64).sum() & np.uint64(0x7fffffffffffffff))
+            bad += got != int(everyone[p][k])
+    return bad
+
+
 def run_b200(args, wl):
     import ctypes as C
     import iree_b200 as ib
@@ -358,6 +385,8 @@ def run_b200(args, wl):
 
         gathers = [ctx.alloc(world * int(np.prod(out_shape)) * np.dtype(out_dtype).itemsize) for _ in sets] \
             if channel is not None else None
+        peer = make_peer_gather(ctx, channel, rank, world, gathers)
+        out_bytes = int(np.prod(out_shape)) * np.dtype(out_dtype).itemsize
 
         def step(i):
             p, da, db, dc, ws, bn, rs, cs = sets[i % n_sets]
@@ -365,7 +394,9 @@ def run_b200(args, wl):
                 # the operand set about to be overwritten was read by a gather n_sets steps ago
                 rt.check(lib.iree_hal_b200_command_buffer_join_collectives(ctx.command_buffer))
             ctx.matmul_run(p, da, db, dc, ws, bn, rs, cs)
-            if channel is not None:
+            if peer is not None:
+                peer.gather(i % n_sets, dc, out_bytes)   # copy engines, beside the next steps' dispatches
+            elif channel is not None:
                 # the gather of this step overlaps the next steps' dispatches (second stream)
                 rt.check(lib.iree_hal_b200_command_buffer_all_gather_overlapped(
                     ctx.command_buffer, channel, C.c_int32(etype), C.c_void_p(dc.ptr),
@@ -397,7 +428,7 @@ def run_b200(args, wl):
         workload_desc, l2_note = state.desc, state.l2_note
     else:
         from iree_b200 import w4a16 as w4
-        state = w4.bench_state(ctx, wl, rank, world, channel)
+        state = w4.bench_state(ctx, wl, rank, world, channel, make_peer_gather)
         step, check, e2e_step = state.step, state.check, state.e2e_step
         ops, byts, h2d, d2h = state.ops, state.bytes, state.h2d, state.d2h
         workload_desc, l2_note = state.desc, state.l2_note
@@ -443,6 +474,18 @@ def run_b200(args, wl):
     sec_per_step = ms / 1e3 / args.steps
     clock_summary = clocks.summary(t_begin, t_end)
 
+    gather_mismatches = None
+    if world > 1 and args.verify:
+        ctx.synchronize()
+        dist_barrier(world)
+        if wl.family == "matmul":
+            gather_mismatches = verify_gather(ctx, world, rank, [x[3] for x in sets], gathers, out_bytes)
+        else:
+            gather_mismatches = verify_gather(ctx, world, rank, [x[4] for x in state.sets], state.gathers,
+                                              wl.M * (wl.N // world if getattr(wl, "sharded", False) else wl.N) * 2)
+        gather_mismatches = int(dist_max(world, float(gather_mismatches)))
+        dist_barrier(world)
+
     # ---- end to end through host buffers ----------------------------------------------------
     e2e_steps = max(1, min(args.steps, int(os.environ.get("IREE_B200_E2E_STEPS", "10"))))
     e2e_step()
@@ -481,7 +524,9 @@ def run_b200(args, wl):
             "config": {"workload": workload_desc, "name": wl.name, "l2": l2_note,
                        "submission": ("CUDA graph of %d dispatches" % args.steps if world == 1 else "stream") +
                                      ", programmatic dependent launch for the decode exports",
-                       "parallelism": "1 rank" if world == 1 else "N-sharded x%d + all-gather (NCCL channel)" % world},
+                       "parallelism": "1 rank" if world == 1 else "N-sharded x%d + all-gather (%s)" % (
+                           world, "NCCL" if os.environ.get("IREE_B200_ALLGATHER", "nccl") == "nccl"
+                           else "peer copies over NVLink by the copy engines + channel barrier")},
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": r_unit,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_note,
                          "frac_of_burst_peak": (achieved / (float(peaks["bf16_tflops"]) * scale)) if wl.bound == "tensor" else None,
@@ -490,6 +535,8 @@ def run_b200(args, wl):
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_sec * 1e3},
             "gpu_launches": int(launches), "clocks": clock_summary,
         }
+        if gather_mismatches is not None:
+            line["config"]["gather_mismatches"] = gather_mismatches
         if world == 1:
             line["cpu_baseline"] = cpu_arm(wl)
         print(json.dumps(line), flush=True)
@@ -520,6 +567,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2_f16_4096")
+    ap.add_argument("--verify", action="store_true",
+                    help="N > 1: after the timed region, check every rank's gathered buffers against the owners' checksums")
     args = ap.parse_args()
     table = workloads()
     if args.workload not in table:

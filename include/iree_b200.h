@@ -220,6 +220,27 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command
                                                            const void* send_device_ptr, void* recv_device_ptr,
                                                            size_t element_count);
 
+/* Device memory of other ranks (processes) of the same node. `export` yields an opaque
+ * IREE_HAL_B200_PEER_HANDLE_SIZE-byte handle for a buffer allocated here; the owner ships it to
+ * its peers by any means and they `import` it, which gives a device pointer valid in the
+ * importing process (NVLink / NVSwitch peer access), to be released with `unimport` before the
+ * owner frees the buffer. (The reference has no counterpart: its collectives go through NCCL only,
+ * runtime/src/iree/hal/drivers/cuda/nccl_channel.c.) */
+#define IREE_HAL_B200_PEER_HANDLE_SIZE 64
+iree_b200_status_t iree_hal_b200_buffer_export(iree_hal_b200_device_t* device, void* device_ptr, void* out_handle);
+iree_b200_status_t iree_hal_b200_buffer_import(iree_hal_b200_device_t* device, const void* handle, void** out_device_ptr);
+iree_b200_status_t iree_hal_b200_buffer_unimport(iree_hal_b200_device_t* device, void* device_ptr);
+/* All-gather by peer copies: this rank's `byte_count` bytes go into slot `rank` of every rank's
+ * receive buffer (recv_device_ptrs[p] = rank p's buffer as imported here; the entry of this rank
+ * is its own buffer) through the copy engines, on the collective stream, after everything
+ * recorded on the dispatch stream so far; a channel barrier follows on the same stream, so that
+ * iree_hal_b200_command_buffer_join_collectives() orders the dispatch stream after the arrival
+ * of every rank's block in this rank's buffer. No SM takes part, which is what lets it run
+ * beside the persistent dispatches. */
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather_peer_copies(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                        iree_hal_b200_channel_t* channel,
+                                                                        const void* send_device_ptr, size_t byte_count,
+                                                                        void* const* recv_device_ptrs);
 /* The same collective on the device's second stream: it starts when everything recorded before it
  * has run, and dispatches recorded after it do not wait for it (the reference keeps a second
  * stream beside the dispatch stream as well, cuda_device.c). join_collectives makes the dispatch

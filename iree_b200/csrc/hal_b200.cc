@@ -86,6 +86,10 @@ struct CudaSymbols {
   CU_FN(cuGraphLaunch, CUgraphExec, CUstream)
   CU_FN(cuGraphExecDestroy, CUgraphExec)
   // optional (programmatic dependent launch); dispatch overlap is refused when they are missing
+  CU_FN(cuIpcGetMemHandle, CUipcMemHandle*, CUdeviceptr)
+  CU_FN(cuIpcOpenMemHandle, CUdeviceptr*, CUipcMemHandle, unsigned)
+  CU_FN(cuIpcCloseMemHandle, CUdeviceptr)
+  CU_FN(cuMemcpyDtoDAsync, CUdeviceptr, CUdeviceptr, size_t, CUstream)
   CU_FN(cuLaunchKernelEx, const CUlaunchConfig*, CUfunction, void**, void**)
   CU_FN(cuGraphAddDependencies_v2, CUgraph, const CUgraphNode*, const CUgraphNode*, const CUgraphEdgeData*, size_t)
   CU_FN(cuGetErrorName, CUresult, const char**)
@@ -157,6 +161,10 @@ iree_b200_status_t ensure_cuda() {
       LOAD(cuGetErrorString, "cuGetErrorString")
       LOAD(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
 #undef LOAD
+      load_sym(g_cu.handle, "cuIpcGetMemHandle", g_cu.cuIpcGetMemHandle);
+      load_sym(g_cu.handle, "cuIpcOpenMemHandle_v2", g_cu.cuIpcOpenMemHandle);
+      load_sym(g_cu.handle, "cuIpcCloseMemHandle", g_cu.cuIpcCloseMemHandle);
+      load_sym(g_cu.handle, "cuMemcpyDtoDAsync_v2", g_cu.cuMemcpyDtoDAsync);
       load_sym(g_cu.handle, "cuLaunchKernelEx", g_cu.cuLaunchKernelEx);
       load_sym(g_cu.handle, "cuGraphAddDependencies_v2", g_cu.cuGraphAddDependencies_v2);
       if (!ok) {
@@ -203,6 +211,7 @@ struct NcclSymbols {
   int (*ncclCommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   int (*ncclCommDestroy)(ncclComm_t) = nullptr;
   int (*ncclAllGather)(const void*, void*, size_t, int, ncclComm_t, CUstream) = nullptr;
+  int (*ncclAllReduce)(const void*, void*, size_t, int, int, ncclComm_t, CUstream) = nullptr;  // optional
   int (*ncclGroupStart)() = nullptr;
   int (*ncclGroupEnd)() = nullptr;
   const char* (*ncclGetErrorString)(int) = nullptr;
@@ -235,6 +244,7 @@ iree_b200_status_t ensure_nccl() {
       ok = load_sym(g_nccl.handle, "ncclCommInitRank", g_nccl.ncclCommInitRank) && ok;
       ok = load_sym(g_nccl.handle, "ncclCommDestroy", g_nccl.ncclCommDestroy) && ok;
       ok = load_sym(g_nccl.handle, "ncclAllGather", g_nccl.ncclAllGather) && ok;
+      load_sym(g_nccl.handle, "ncclAllReduce", g_nccl.ncclAllReduce);
       ok = load_sym(g_nccl.handle, "ncclGroupStart", g_nccl.ncclGroupStart) && ok;
       ok = load_sym(g_nccl.handle, "ncclGroupEnd", g_nccl.ncclGroupEnd) && ok;
       ok = load_sym(g_nccl.handle, "ncclGetErrorString", g_nccl.ncclGetErrorString) && ok;
@@ -432,6 +442,7 @@ struct iree_hal_b200_channel_t {
   iree_hal_b200_device_t* device = nullptr;
   ncclComm_t comm = nullptr;
   int32_t rank = 0, count = 1;
+  void* barrier_word = nullptr;  // 4 bytes reduced by the channel barrier (allocated on first use)
 };
 
 extern "C" {
@@ -970,6 +981,7 @@ iree_b200_status_t iree_hal_b200_channel_create(iree_hal_b200_device_t* device, 
 void iree_hal_b200_channel_release(iree_hal_b200_channel_t* channel) {
   if (!channel) return;
   if (channel->comm) g_nccl.ncclCommDestroy(channel->comm);
+  if (channel->barrier_word) iree_hal_b200_buffer_free(channel->device, channel->barrier_word);
   delete channel;
 }
 int32_t iree_hal_b200_channel_rank(const iree_hal_b200_channel_t* channel) { return channel ? channel->rank : 0; }
@@ -1027,6 +1039,85 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather_overlapped(iree_hal_b
   CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->collective_stream, d->dispatch_done, 0), "cuStreamWaitEvent");
   return all_gather_on(command_buffer, channel, element_type, send_device_ptr, recv_device_ptr, element_count,
                        d->collective_stream);
+}
+
+// ---- peer memory: buffers of other ranks (processes) on the same node -----------------------------------
+iree_b200_status_t iree_hal_b200_buffer_export(iree_hal_b200_device_t* device, void* device_ptr, void* out_handle) {
+  if (!device || !device_ptr || !out_handle) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (!g_cu.cuIpcGetMemHandle) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver cannot share device memory");
+  static_assert(sizeof(CUipcMemHandle) == IREE_HAL_B200_PEER_HANDLE_SIZE, "handle size");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CUipcMemHandle h;
+  CU_RETURN_IF_ERROR(g_cu.cuIpcGetMemHandle(&h, reinterpret_cast<CUdeviceptr>(device_ptr)), "cuIpcGetMemHandle");
+  memcpy(out_handle, &h, sizeof h);
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_buffer_import(iree_hal_b200_device_t* device, const void* handle, void** out_device_ptr) {
+  if (!device || !handle || !out_device_ptr) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  *out_device_ptr = nullptr;
+  if (!g_cu.cuIpcOpenMemHandle) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver cannot share device memory");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CUipcMemHandle h;
+  memcpy(&h, handle, sizeof h);
+  CUdeviceptr p = 0;
+  CU_RETURN_IF_ERROR(g_cu.cuIpcOpenMemHandle(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS), "cuIpcOpenMemHandle");
+  *out_device_ptr = reinterpret_cast<void*>(p);
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_buffer_unimport(iree_hal_b200_device_t* device, void* device_ptr) {
+  if (!device || !device_ptr) return IREE_B200_STATUS_OK;
+  if (!g_cu.cuIpcCloseMemHandle) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver cannot share device memory");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  CU_RETURN_IF_ERROR(g_cu.cuIpcCloseMemHandle(reinterpret_cast<CUdeviceptr>(device_ptr)), "cuIpcCloseMemHandle");
+  return IREE_B200_STATUS_OK;
+}
+
+// All-gather by peer copies: this rank's block goes into slot `rank` of every rank's receive
+// buffer through the copy engines (no SM is used, so it runs beside a persistent dispatch that
+// fills them all), on the collective stream, after everything recorded on the dispatch stream so
+// far. A channel barrier (a one-word all-reduce) follows on the same stream: when the collective
+// stream of a rank has passed it, every rank has finished the copies it enqueued before its own
+// barrier, i.e. that rank's receive buffer is complete.
+iree_b200_status_t iree_hal_b200_command_buffer_all_gather_peer_copies(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                        iree_hal_b200_channel_t* channel,
+                                                                        const void* send_device_ptr, size_t byte_count,
+                                                                        void* const* recv_device_ptrs) {
+  if (!command_buffer || !channel || !recv_device_ptrs || (byte_count && !send_device_ptr))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (command_buffer->recording)
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "collectives cannot be recorded into a graph");
+  if (!g_cu.cuMemcpyDtoDAsync || !g_nccl.ncclAllReduce)
+    return fail(IREE_B200_STATUS_UNAVAILABLE, "peer copies need cuMemcpyDtoDAsync and ncclAllReduce");
+  iree_hal_b200_device_t* d = command_buffer->device;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  if (!d->collective_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->collective_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->dispatch_done, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->collective_done, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  if (!channel->barrier_word) {
+    B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(d, 256, &channel->barrier_word));
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, channel->barrier_word, 256, 0));
+    B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
+  }
+  CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->dispatch_done, d->stream), "cuEventRecord");
+  CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->collective_stream, d->dispatch_done, 0), "cuStreamWaitEvent");
+  for (int32_t i = 0; i < channel->count; ++i) {
+    // start with the neighbour so that the ranks do not all write to the same peer at once
+    const int32_t p = (channel->rank + 1 + i) % channel->count;
+    if (!recv_device_ptrs[p]) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "receive buffer of rank %d is NULL", p);
+    uint8_t* dst = static_cast<uint8_t*>(recv_device_ptrs[p]) + static_cast<size_t>(channel->rank) * byte_count;
+    if (byte_count)
+      CU_RETURN_IF_ERROR(g_cu.cuMemcpyDtoDAsync(reinterpret_cast<CUdeviceptr>(dst),
+                                                reinterpret_cast<CUdeviceptr>(send_device_ptr), byte_count,
+                                                d->collective_stream),
+                         "cuMemcpyDtoDAsync");
+  }
+  // ncclInt32 = 2, ncclSum = 0
+  B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclAllReduce(channel->barrier_word, channel->barrier_word, 1, 2, 0, channel->comm,
+                                                       d->collective_stream),
+                                  "ncclAllReduce"));
+  return IREE_B200_STATUS_OK;
 }
 
 iree_b200_status_t iree_hal_b200_command_buffer_join_collectives(iree_hal_b200_command_buffer_t* command_buffer) {

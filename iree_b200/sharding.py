@@ -31,3 +31,54 @@ def assemble(gathered: np.ndarray) -> np.ndarray:
     """[world, M, N/world] (all-gather order) -> [M, N] row-major."""
     world, M, n = gathered.shape
     return np.ascontiguousarray(np.transpose(gathered, (1, 0, 2)).reshape(M, world * n))
+
+
+class PeerGather:
+    """All-gather of per-rank blocks by peer copies (``iree_hal_b200_command_buffer_all_gather_peer_copies``).
+
+    Every rank owns ``len(gather_buffers)`` receive buffers; their handles travel to the other ranks
+    over the ``torch.distributed`` control plane once, each rank imports its peers' buffers, and
+    from then on ``gather(k, send)`` puts this rank's block into slot ``rank`` of receive buffer k on
+    every rank with the copy engines. One process per GPU, all on one node.
+    """
+
+    def __init__(self, ctx, channel, rank: int, world: int, gather_buffers):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from . import runtime as rt
+        self.ctx, self.channel, self.rank, self.world = ctx, channel, rank, world
+        self.lib = rt.library()
+        self._C, self._rt = C, rt
+        n = len(gather_buffers)
+        mine = torch.zeros(n * 64, dtype=torch.uint8)
+        for k, buf in enumerate(gather_buffers):
+            h = C.create_string_buffer(64)
+            rt.check(self.lib.iree_hal_b200_buffer_export(ctx.device, C.c_void_p(buf.ptr), h))
+            mine[k * 64:(k + 1) * 64] = torch.frombuffer(bytearray(h.raw), dtype=torch.uint8)
+        everyone = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        self.imported = []
+        self.tables = []
+        for k, buf in enumerate(gather_buffers):
+            table = (C.c_void_p * world)()
+            for p in range(world):
+                if p == rank:
+                    table[p] = buf.ptr
+                    continue
+                ptr = C.c_void_p()
+                raw = bytes(everyone[p][k * 64:(k + 1) * 64].numpy().tobytes())
+                rt.check(self.lib.iree_hal_b200_buffer_import(ctx.device, raw, C.byref(ptr)))
+                self.imported.append(ptr.value)
+                table[p] = ptr.value
+            self.tables.append(table)
+
+    def gather(self, k: int, send_buffer, nbytes: int) -> None:
+        C = self._C
+        self._rt.check(self.lib.iree_hal_b200_command_buffer_all_gather_peer_copies(
+            self.ctx.command_buffer, self.channel, C.c_void_p(send_buffer.ptr), C.c_size_t(nbytes), self.tables[k]))
+
+    def close(self) -> None:
+        for ptr in self.imported:
+            self.lib.iree_hal_b200_buffer_unimport(self.ctx.device, self._C.c_void_p(ptr))
+        self.imported = []

@@ -33,7 +33,7 @@ class _BenchState:
     pass
 
 
-def bench_state(ctx: rt.Context, wl, rank: int, world: int, channel):
+def bench_state(ctx: rt.Context, wl, rank: int, world: int, channel, make_peer_gather=None):
     """Buffers and step functions for bench.py's W4A16 workloads.
 
     With more than one rank the weight rows are sharded along N; every rank computes its
@@ -63,13 +63,16 @@ def bench_state(ctx: rt.Context, wl, rank: int, world: int, channel):
         variant, tile_n = ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
         sets.append((p, da, dw, ds, dc, ws, variant, tile_n))
     gathers = [ctx.alloc(world * M * n_local * 2) for _ in sets] if channel is not None else None
+    peer = make_peer_gather(ctx, channel, rank, world, gathers) if make_peer_gather else None
 
     def step(i):
         p, da, dw, ds, dc, ws, variant, tile_n = sets[i % n_sets]
         if channel is not None and i % n_sets == 0:
             rt.check(lib.iree_hal_b200_command_buffer_join_collectives(ctx.command_buffer))
         ctx.w4a16_run(p, da, dw, ds, dc, ws, variant, tile_n)
-        if channel is not None:
+        if peer is not None:
+            peer.gather(i % n_sets, dc, M * n_local * 2)   # copy engines, beside the following dispatches
+        elif channel is not None:
             # overlaps the following dispatches on the device's second stream
             rt.check(lib.iree_hal_b200_command_buffer_all_gather_overlapped(
                 ctx.command_buffer, channel, C.c_int32(1), C.c_void_p(dc.ptr), C.c_void_p(gathers[i % n_sets].ptr),
@@ -87,6 +90,7 @@ def bench_state(ctx: rt.Context, wl, rank: int, world: int, channel):
         ctx.w4a16_host(p, pa, pw, ps, host_out)
 
     st.step, st.check, st.e2e_step = step, check, e2e_step
+    st.gathers, st.sets, st.peer = gathers, sets, peer
     st.ops = 2.0 * M * n_local * K
     st.bytes = float(wq.nbytes + s.nbytes + a.nbytes + M * n_local * 2)
     st.h2d = a.nbytes + wq.nbytes + s.nbytes

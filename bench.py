@@ -295,9 +295,17 @@ def dist_broadcast_bytes(world, rank, data, size):
     return bytes(t.numpy().tobytes())
 
 
+def allgather_mode(block_bytes):
+    """IREE_B200_ALLGATHER=peer|nccl; by default peer copies (copy engines, no SMs) for blocks of a
+    megabyte or more and the NCCL collective below that, where its lower latency wins."""
+    mode = os.environ.get("IREE_B200_ALLGATHER", "auto")
+    if mode == "auto":
+        mode = "peer" if block_bytes >= (1 << 20) else "nccl"
+    return mode
+
+
 def make_peer_gather(ctx, channel, rank, world, gathers):
-    """All-gather by peer copies when IREE_B200_ALLGATHER=peer asks for it (default: the NCCL collective)."""
-    if channel is None or os.environ.get("IREE_B200_ALLGATHER", "nccl") == "nccl":
+    if channel is None or allgather_mode(gathers[0].nbytes // world) == "nccl":
         return None
     from iree_b200.sharding import PeerGather
     return PeerGather(ctx, channel, rank, world, gathers)
@@ -525,7 +533,7 @@ def run_b200(args, wl):
                        "submission": ("CUDA graph of %d dispatches" % args.steps if world == 1 else "stream") +
                                      ", programmatic dependent launch for the decode exports",
                        "parallelism": "1 rank" if world == 1 else "N-sharded x%d + all-gather (%s)" % (
-                           world, "NCCL" if os.environ.get("IREE_B200_ALLGATHER", "nccl") == "nccl"
+                           world, "NCCL" if allgather_mode(d2h) == "nccl"
                            else "peer copies over NVLink by the copy engines + channel barrier")},
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": r_unit,
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_note,

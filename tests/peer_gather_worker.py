@@ -1,0 +1,61 @@
+"""Worker of tests/test_gpu_multi.py: one rank of an all-gather by peer copies (run under torchrun)."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import iree_b200 as ib  # noqa: E402
+from iree_b200 import runtime as rt  # noqa: E402
+from iree_b200.sharding import PeerGather  # noqa: E402
+
+
+def main() -> int:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    ctx = ib.Context(local)
+    lib = ib.library()
+    ident = C.create_string_buffer(128)
+    if rank == 0:
+        rt.check(lib.iree_hal_b200_channel_create_id(ident, C.c_size_t(128)))
+    t = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        t[:] = torch.frombuffer(bytearray(ident.raw), dtype=torch.uint8)
+    dist.broadcast(t, src=0)
+    channel = C.c_void_p()
+    rt.check(lib.iree_hal_b200_channel_create(ctx.device, bytes(t.numpy().tobytes()), C.c_size_t(128), C.c_int32(rank),
+                                              C.c_int32(world), C.byref(channel)))
+    n = 1 << 20  # int32 elements per rank and buffer
+    rounds, buffers = 6, 2
+    gathers = [ctx.alloc(world * n * 4).fill(0xEE) for _ in range(buffers)]
+    send = ctx.alloc(n * 4)
+    peer = PeerGather(ctx, channel, rank, world, gathers)
+    ok = True
+    for r in range(rounds):
+        block = (np.arange(n, dtype=np.int32) * (rank + 1) + 1000 * r).astype(np.int32)
+        send.upload(block)
+        peer.gather(r % buffers, send, n * 4)
+        rt.check(lib.iree_hal_b200_command_buffer_join_collectives(ctx.command_buffer))
+        ctx.synchronize()
+        got = gathers[r % buffers].download(np.int32, (world, n))
+        for p in range(world):
+            want = (np.arange(n, dtype=np.int32) * (p + 1) + 1000 * r).astype(np.int32)
+            ok = ok and np.array_equal(got[p], want)
+        dist.barrier()  # nobody overwrites `send` or a receive buffer while a peer still checks
+    peer.close()
+    lib.iree_hal_b200_channel_release(channel)
+    flag = torch.tensor([1 if ok else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("PEER_GATHER_OK" if int(flag[0]) else "PEER_GATHER_MISMATCH", flush=True)
+    ctx.close()
+    return 0 if int(flag[0]) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

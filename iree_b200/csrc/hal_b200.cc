@@ -1142,7 +1142,7 @@ constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
 // weight ring (4 stages of 16 rows x 2048 B), scale ring (4 x 4 KiB), 4 slots of 16 per-warp partials, barriers
 constexpr uint32_t kDecodeSmemM8 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 4 + 8) * 8 + 16;
 constexpr uint32_t kDecodeSmemM16 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 4 + 8) * 8 + 16 + 16 * 4 * 32 * 8;
-constexpr uint32_t kW4SmemBytes = 1024 + 3 * (128 * 128 + 256 * 128) + 2 * (256 * 64) + 256;
+constexpr uint32_t kW4SmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 4 * (128 * 64) + 256;  // the 256-row variant: 4 + 4 stages
 // staging region of the pack / unpack kernels: 64 rows of at most 512 bytes, 16 bytes of padding per row
 constexpr uint32_t kTilingStageBytes = 64 * (2 * 256 + 16);
 

@@ -38,7 +38,12 @@ constexpr int kW4StageBytes = kW4AStageBytes + kW4BStageBytes;
 constexpr int kW4RawStageBytes = kW4MaxBN * 64;     // 16 KiB: 256 rows x 128 int4
 constexpr int kW4Threads = 512;
 constexpr int kW4DequantWarps = 8;
-constexpr int kW4SmemBytes = 1024 + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes + 256;
+// The tall variant (below) needs raw stages of half the size and a stage more of each kind.
+constexpr int kW4TallStages = 4;
+constexpr int kW4TallRawStages = 4;
+constexpr int kW4SmemBytes = 1024 + kW4TallStages * kW4StageBytes + kW4TallRawStages * (kW4RawStageBytes / 2) + 256;
+static_assert(kW4SmemBytes >= 1024 + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes + 256, "128-row variant");
+static_assert(kW4SmemBytes <= 232448, "per-CTA shared memory limit");
 // Tall variant (M >= 256 and tiles at most 128 wide): a CTA computes 256 x bn, i.e. two 128-row
 // accumulators that share one expanded weight tile, so every weight is expanded half as often per
 // flop. A stage is then 32 KiB of activations + 16 KiB of weights (the same 48 KiB), and TMEM holds
@@ -66,23 +71,26 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   constexpr int kAStageBytes = kHalves * kW4AStageBytes;       // the B tile follows it in the stage
   constexpr int kAccColumns = TALL ? kW4TallMaxBN : kW4MaxBN;  // TMEM columns per accumulator
   static_assert(kAStageBytes + kAccColumns * 128 <= kW4StageBytes, "stage layout");
+  constexpr int kS = TALL ? kW4TallStages : kW4Stages;               // f16 operand stages
+  constexpr int kRS = TALL ? kW4TallRawStages : kW4RawStages;        // raw int4 stages
+  constexpr int kRawBytes = kAccColumns * 64;                        // one group (128 K) of every tile row
+  static_assert(1024 + kS * kW4StageBytes + kRS * kRawBytes + 256 <= kW4SmemBytes, "shared memory");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t raw_base = smem_base + kW4Stages * kW4StageBytes;
-  const uint32_t bars = raw_base + kW4RawStages * kW4RawStageBytes;
-  uint8_t* bars_gen = smem_gen + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes;
-  // barriers: full[stages], empty[stages], raw_full[2], raw_empty[2], tmem_full[2], tmem_empty[2]
-  constexpr int kS = kW4Stages;
+  const uint32_t raw_base = smem_base + kS * kW4StageBytes;
+  const uint32_t bars = raw_base + kRS * kRawBytes;
+  uint8_t* bars_gen = smem_gen + kS * kW4StageBytes + kRS * kRawBytes;
+  // barriers: full[stages], empty[stages], raw_full[raw stages], raw_empty[raw stages], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int i) { return bars + 8u * i; };
   auto empty_bar = [&](int i) { return bars + 8u * (kS + i); };
   auto raw_full_bar = [&](int i) { return bars + 8u * (2 * kS + i); };
-  auto raw_empty_bar = [&](int i) { return bars + 8u * (2 * kS + 2 + i); };
-  auto tmem_full_bar = [&](int i) { return bars + 8u * (2 * kS + 4 + i); };
-  auto tmem_empty_bar = [&](int i) { return bars + 8u * (2 * kS + 6 + i); };
-  const uint32_t tmem_slot = bars + 8u * (2 * kS + 8);
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * kS + 8));
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * kS + 8) + 4);
+  auto raw_empty_bar = [&](int i) { return bars + 8u * (2 * kS + kRS + i); };
+  auto tmem_full_bar = [&](int i) { return bars + 8u * (2 * kS + 2 * kRS + i); };
+  auto tmem_empty_bar = [&](int i) { return bars + 8u * (2 * kS + 2 * kRS + 2 + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * kS + 2 * kRS + 4);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * kS + 2 * kRS + 4));
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * kS + 2 * kRS + 4) + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -97,11 +105,11 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   const int num_kb = K / 64;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kW4Stages; ++i) {
-      mbar_init(full_bar(i), 1 + kW4DequantWarps);  // TMA producer + one arrival per dequant warp
+    for (int i = 0; i < kS; ++i) {
+      mbar_init(full_bar(i), 1 + (TALL ? kW4DequantWarps / 2 : kW4DequantWarps));  // TMA producer + the stage's dequant warps
       mbar_init(empty_bar(i), 1);
     }
-    for (int i = 0; i < kW4RawStages; ++i) {
+    for (int i = 0; i < kRS; ++i) {
       mbar_init(raw_full_bar(i), 1);
       mbar_init(raw_empty_bar(i), kW4DequantWarps);
     }
@@ -138,8 +146,8 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         tile_coords(t, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           if ((kb & 1) == 0) {
-            const int rs = raw_it % kW4RawStages;
-            const uint32_t rph = (raw_it / kW4RawStages) & 1;
+            const int rs = raw_it % kRS;
+            const uint32_t rph = (raw_it / kRS) & 1;
             if (!mbar_wait(raw_empty_bar(rs), rph ^ 1, abort_flag)) {
               w4_report(ws, kStatusTimeoutEmpty, 0x10000u | raw_it);
               *abort_flag = 1;
@@ -147,11 +155,11 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
               break;
             }
             mbar_arrive_expect_tx(raw_full_bar(rs), bn * 64);
-            tma_load_3d(raw_base + rs * kW4RawStageBytes, ws->map_w, raw_full_bar(rs), (kb >> 1) * 64, tn * bn, 0);
+            tma_load_3d(raw_base + rs * kRawBytes, ws->map_w, raw_full_bar(rs), (kb >> 1) * 64, tn * bn, 0);
             ++raw_it;
           }
-          const int st = it % kW4Stages;
-          const uint32_t ph = (it / kW4Stages) & 1;
+          const int st = it % kS;
+          const uint32_t ph = (it / kS) & 1;
           if (!mbar_wait(empty_bar(st), ph ^ 1, abort_flag)) {
             w4_report(ws, kStatusTimeoutEmpty, it);
             *abort_flag = 1;
@@ -183,8 +191,8 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kHalves * kAccColumns;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int st = it % kW4Stages;
-          const uint32_t ph = (it / kW4Stages) & 1;
+          const int st = it % kS;
+          const uint32_t ph = (it / kS) & 1;
           if (!mbar_wait(full_bar(st), ph, abort_flag)) {
             w4_report(ws, kStatusTimeoutDequant, it);
             *abort_flag = 1;
@@ -257,26 +265,39 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
     }
   } else if (warp >= 8) {
     // -------- dequant: raw int4 (64-byte swizzled rows) -> f16 K-major 128-byte swizzled tile -----
-    // Thread r of the 256 handles weight row r of the tile: 64 K per block = 32 raw bytes in,
-    // one 128-byte operand row out.
-    // (Tall variant: at most 128 rows, so two threads share a row, one per 16-byte raw chunk.)
-    const int r = TALL ? ((threadIdx.x - 256) & 127) : (threadIdx.x - 256);
-    const int part = TALL ? ((threadIdx.x - 256) >> 7) : 0;
-    uint32_t it = 0, raw_it = 0;
+    // A thread expands one weight row of one K block: 32 raw bytes in, one 128-byte operand row
+    // out. 128 x bn tiles: the 256 threads take the (up to) 256 rows of every K block. Tall
+    // variant (at most 128 rows): two groups of 128 threads take alternate K blocks, so that one
+    // group's stores and proxy fence drain while the other group computes.
+    const int td = threadIdx.x - 256;
+    const int r = TALL ? (td & 127) : td;
+    const int grp = TALL ? (td >> 7) : 0;
+    constexpr int kStep = TALL ? 2 : 1;
+    const int groups = K >> 7;
+    // Scales of eight consecutive groups arrive as one 16-byte load, one load ahead of their use.
+    const bool vec_scales = (groups & 7) == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0;
+    uint32_t it_base = 0, raw_it_base = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it_base += num_kb, raw_it_base += num_kb >> 1) {
       int tm, tn;
       tile_coords(t, tm, tn);
       const int n = tn * bn + r;
       const bool row_live = r < bn;
-      const __half* srow = scales + static_cast<size_t>(n < N ? n : 0) * (K >> 7);
+      const bool has_scales = row_live && n < N;
+      const __half* srow = scales + static_cast<size_t>(n < N ? n : 0) * groups;
       __half2 s2 = __half2half2(__float2half_rn(0.f));
-      // The scale of the next group is fetched one group ahead so that its latency is hidden.
-      __half next_scale = (row_live && n < N) ? srow[0] : __float2half_rn(0.f);
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int rs = raw_it % kW4RawStages;
-        if ((kb & 1) == 0) {
-          const uint32_t rph = (raw_it / kW4RawStages) & 1;
+      uint4 sc_cur = make_uint4(0, 0, 0, 0), sc_next = make_uint4(0, 0, 0, 0);
+      __half next_scale = __float2half_rn(0.f);
+      if (has_scales) {
+        if (vec_scales) sc_next = *reinterpret_cast<const uint4*>(srow);
+        else next_scale = srow[0];
+      }
+      for (int kb = grp; kb < num_kb; kb += kStep) {
+        const uint32_t it = it_base + kb;
+        const uint32_t raw_it = raw_it_base + (kb >> 1);
+        const int rs = raw_it % kRS;
+        if (TALL || (kb & 1) == 0) {
+          const uint32_t rph = (raw_it / kRS) & 1;
           if (!__all_sync(0xffffffffu, mbar_wait(raw_full_bar(rs), rph, abort_flag))) {
             if (lane == 0) {
               w4_report(ws, kStatusTimeoutFull, 0x10000u | raw_it);
@@ -285,11 +306,21 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
             ok = false;
             break;
           }
-          s2 = __half2half2(next_scale);
-          if (row_live && n < N && kb + 2 < num_kb) next_scale = srow[(kb >> 1) + 1];
+          const int g = kb >> 1;
+          if (vec_scales) {
+            if ((g & 7) == 0) {
+              sc_cur = sc_next;
+              if (has_scales && g + 8 < groups) sc_next = *reinterpret_cast<const uint4*>(srow + g + 8);
+            }
+            const uint32_t word = (g & 4) ? ((g & 2) ? sc_cur.w : sc_cur.z) : ((g & 2) ? sc_cur.y : sc_cur.x);
+            s2 = as_half2(__byte_perm(word, 0u, (g & 1) ? 0x3232u : 0x1010u));
+          } else {
+            s2 = __half2half2(next_scale);
+            if (has_scales && g + 1 < groups) next_scale = srow[g + 1];
+          }
         }
-        const int st = it % kW4Stages;
-        const uint32_t ph = (it / kW4Stages) & 1;
+        const int st = it % kS;
+        const uint32_t ph = (it / kS) & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(st), ph ^ 1, abort_flag))) {
           if (lane == 0) {
             w4_report(ws, kStatusTimeoutEmpty, 0x20000u | it);
@@ -300,11 +331,11 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         }
         if (row_live) {
           // Raw stage: row r is 64 bytes; its four 16-byte chunks are XOR-swizzled by (r / 2) % 4.
-          const uint8_t* raw_row = smem_gen + kW4Stages * kW4StageBytes + rs * kW4RawStageBytes + r * 64;
+          const uint8_t* raw_row = smem_gen + kS * kW4StageBytes + rs * kRawBytes + r * 64;
           uint8_t* b_row = smem_gen + st * kW4StageBytes + kAStageBytes + r * 128;
           const int sw_raw = (r >> 1) & 3, sw_b = r & 7;
 #pragma unroll
-          for (int c = TALL ? part : 0; c < (TALL ? part + 1 : 2); ++c) {
+          for (int c = 0; c < 2; ++c) {
             const int chunk = (kb & 1) * 2 + c;  // 16-byte chunk of the 64-byte raw row
             const uint4 w = *reinterpret_cast<const uint4*>(raw_row + ((chunk ^ sw_raw) << 4));
             const uint32_t words[4] = {w.x, w.y, w.z, w.w};
@@ -326,9 +357,8 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(full_bar(st));
-          if (kb & 1) mbar_arrive(raw_empty_bar(rs));
+          if (TALL || (kb & 1)) mbar_arrive(raw_empty_bar(rs));
         }
-        if (kb & 1) ++raw_it;
       }
     }
   }

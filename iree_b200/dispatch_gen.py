@@ -16,7 +16,7 @@ from dataclasses import dataclass, field, asdict
 from typing import Dict, List, Optional, Tuple
 
 GEMM_THREADS, GEMM_SMEM = 256, 197888
-W4_THREADS, W4_SMEM = 512, 181504
+W4_THREADS, W4_SMEM = 512, 230656
 DECODE_THREADS, DECODE_SMEM = 512, {8: 180368, 16: 229520}
 SM_COUNT = 148
 

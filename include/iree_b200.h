@@ -346,7 +346,7 @@ typedef struct {
   int32_t ldo;       /* output row pitch in elements */
   int32_t n_offset;  /* first output column */
   int32_t variant;   /* IREE_B200_W4A16_* */
-  int32_t tile_n;    /* 0 = choose (tensor-core kernel only) */
+  int32_t tile_n;    /* 0 = choose (tensor-core kernel only; else a multiple of 16 up to 128) */
 } iree_b200_w4a16_params_t;
 /* Device workspace the dispatch needs for an N-column weight matrix: tensor maps, status words
  * and the f32 scratch the decode kernel uses when K > 4096. It must be zero-filled once

@@ -1142,7 +1142,7 @@ constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
 // weight ring (4 stages of 16 rows x 2048 B), scale ring (4 x 4 KiB), 4 slots of 16 per-warp partials, barriers
 constexpr uint32_t kDecodeSmemM8 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 4 + 8) * 8 + 16;
 constexpr uint32_t kDecodeSmemM16 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 4 + 8) * 8 + 16 + 16 * 4 * 32 * 8;
-constexpr uint32_t kW4SmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 4 * (128 * 64) + 256;  // the 256-row variant: 4 + 4 stages
+constexpr uint32_t kW4SmemBytes = 1024 + 224 * 1024 + 256;  // operand stages + raw stages of either variant
 // staging region of the pack / unpack kernels: 64 rows of at most 512 bytes, 16 bytes of padding per row
 constexpr uint32_t kTilingStageBytes = 64 * (2 * 256 + 16);
 
@@ -1718,13 +1718,14 @@ size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
 
 static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p) {
   const int sms = usable_sms(ctx);
-  // M >= 256: tiles of 256 rows and at most 128 columns select the kernel's tall variant, which
-  // expands every weight half as often per flop; such a tile costs as much as a 128 x 256 one.
-  const bool tall = p->M >= 256 && (!p->tile_n || p->tile_n <= 128);
+  // Tiles are a multiple of 16 and at most 128 columns wide. M >= 256 runs the kernel's 256-row
+  // variant, which expands every weight half as often per flop; below that the 128-row variant
+  // streams the weights once and the narrowest one-wave tile wins.
+  const bool tall = p->M >= 256;
   const int64_t tiles_m = tall ? (p->M + 255) / 256 : (p->M + 127) / 128;
   int best = 0;
   double best_cost = 0;
-  for (int bn = tall ? 128 : 256; bn >= 32; bn -= 32) {
+  for (int bn = 128; bn >= 16; bn -= 16) {
     if (p->tile_n && bn != p->tile_n) continue;
     const int64_t tiles = tiles_m * ((p->N + bn - 1) / bn);
     const int64_t waves = (tiles + sms - 1) / sms;
@@ -1805,7 +1806,7 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     const int32_t constants[6] = {params->M, params->N, params->K, params->ldo, params->n_offset, tile_n};
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 3, bindings));
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
-    const int tile_rows = (params->M >= 256 && tile_n <= 128) ? 256 : 128;  // the kernel's tall variant
+    const int tile_rows = params->M >= 256 ? 256 : 128;  // the kernel's 256-row variant
     const int64_t tiles = static_cast<int64_t>((params->M + tile_rows - 1) / tile_rows) * ((params->N + tile_n - 1) / tile_n);
     const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_gemm");
     return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 3, 6, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);

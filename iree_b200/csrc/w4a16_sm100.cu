@@ -29,27 +29,23 @@ namespace b200 {
 // tcgen05 kernel for larger M
 // =============================================================================================
 constexpr int kW4BM = 128;
-constexpr int kW4MaxBN = 256;
-constexpr int kW4Stages = 3;                        // f16 operand stages (A tile + expanded B tile)
-constexpr int kW4RawStages = 2;                     // raw int4 stages, each 128 K = one scale group
+constexpr int kW4MaxBN = 128;                       // tile width: a multiple of 16 up to this
 constexpr int kW4AStageBytes = kW4BM * 128;         // 16 KiB: 128 rows x 64 f16
-constexpr int kW4BStageBytes = kW4MaxBN * 128;      // 32 KiB
-constexpr int kW4StageBytes = kW4AStageBytes + kW4BStageBytes;
-constexpr int kW4RawStageBytes = kW4MaxBN * 64;     // 16 KiB: 256 rows x 128 int4
+constexpr int kW4BStageBytes = kW4MaxBN * 128;      // 16 KiB: the expanded weights of one K block
+constexpr int kW4RawStageBytes = kW4MaxBN * 64;     // 8 KiB: 128 rows x 128 int4 = one scale group
 constexpr int kW4Threads = 512;
-constexpr int kW4DequantWarps = 8;
-// The tall variant (below) needs raw stages of half the size and a stage more of each kind.
-constexpr int kW4TallStages = 4;
-constexpr int kW4TallRawStages = 4;
-constexpr int kW4SmemBytes = 1024 + kW4TallStages * kW4StageBytes + kW4TallRawStages * (kW4RawStageBytes / 2) + 256;
-static_assert(kW4SmemBytes >= 1024 + kW4Stages * kW4StageBytes + kW4RawStages * kW4RawStageBytes + 256, "128-row variant");
+constexpr int kW4DequantWarps = 8;                  // two groups of four, alternating K blocks
+// Two variants, chosen from M: 128 x bn tiles below M = 256 (weights stream once: many raw stages
+// in flight), and 256 x bn tiles from there on, i.e. two 128-row accumulators sharing one expanded
+// weight tile, so that every weight is expanded half as often per flop. Both fill the same shared
+// memory: 5 x 32 KiB + 8 x 8 KiB, or 4 x 48 KiB + 4 x 8 KiB.
+__host__ __device__ constexpr bool w4_tall_variant(int M) { return M >= 256; }
+constexpr int kW4Stages = 5, kW4RawStages = 8;
+constexpr int kW4TallStages = 4, kW4TallRawStages = 4;
+constexpr int kW4SmemBytes = 1024 + 224 * 1024 + 256;
+static_assert(kW4Stages * (kW4AStageBytes + kW4BStageBytes) + kW4RawStages * kW4RawStageBytes <= 224 * 1024, "128-row variant");
+static_assert(kW4TallStages * (2 * kW4AStageBytes + kW4BStageBytes) + kW4TallRawStages * kW4RawStageBytes <= 224 * 1024, "256-row variant");
 static_assert(kW4SmemBytes <= 232448, "per-CTA shared memory limit");
-// Tall variant (M >= 256 and tiles at most 128 wide): a CTA computes 256 x bn, i.e. two 128-row
-// accumulators that share one expanded weight tile, so every weight is expanded half as often per
-// flop. A stage is then 32 KiB of activations + 16 KiB of weights (the same 48 KiB), and TMEM holds
-// 2 buffers x 2 halves x 128 columns.
-constexpr int kW4TallMaxBN = 128;
-__host__ __device__ constexpr bool w4_tall_variant(int M, int bn) { return M >= 256 && bn <= kW4TallMaxBN; }
 
 struct alignas(128) W4Workspace {
   uint8_t map_a[128];    // f16 [M, K], 128-byte swizzle, box 64 x 128
@@ -69,18 +65,17 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   constexpr int kHalves = TALL ? 2 : 1;                        // 128-row accumulators per tile
   constexpr int kTileRows = kHalves * kW4BM;
   constexpr int kAStageBytes = kHalves * kW4AStageBytes;       // the B tile follows it in the stage
-  constexpr int kAccColumns = TALL ? kW4TallMaxBN : kW4MaxBN;  // TMEM columns per accumulator
-  static_assert(kAStageBytes + kAccColumns * 128 <= kW4StageBytes, "stage layout");
-  constexpr int kS = TALL ? kW4TallStages : kW4Stages;               // f16 operand stages
-  constexpr int kRS = TALL ? kW4TallRawStages : kW4RawStages;        // raw int4 stages
-  constexpr int kRawBytes = kAccColumns * 64;                        // one group (128 K) of every tile row
-  static_assert(1024 + kS * kW4StageBytes + kRS * kRawBytes + 256 <= kW4SmemBytes, "shared memory");
+  constexpr int kStageBytes = kAStageBytes + kW4BStageBytes;
+  constexpr int kAccColumns = kW4MaxBN;                        // TMEM columns per accumulator
+  constexpr int kS = TALL ? kW4TallStages : kW4Stages;         // f16 operand stages
+  constexpr int kRS = TALL ? kW4TallRawStages : kW4RawStages;  // raw int4 stages, one scale group each
+  constexpr int kRawBytes = kW4RawStageBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t raw_base = smem_base + kS * kW4StageBytes;
+  const uint32_t raw_base = smem_base + kS * kStageBytes;
   const uint32_t bars = raw_base + kRS * kRawBytes;
-  uint8_t* bars_gen = smem_gen + kS * kW4StageBytes + kRS * kRawBytes;
+  uint8_t* bars_gen = smem_gen + kS * kStageBytes + kRS * kRawBytes;
   // barriers: full[stages], empty[stages], raw_full[raw stages], raw_empty[raw stages], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int i) { return bars + 8u * i; };
   auto empty_bar = [&](int i) { return bars + 8u * (kS + i); };
@@ -94,7 +89,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || bn < 32 || bn > kAccColumns || (bn & 31);
+  const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || bn < 16 || bn > kAccColumns || (bn & 15);
   if (bad) {
     if (threadIdx.x == 0) w4_report(ws, kStatusBadArgument, 0);
     return;
@@ -106,7 +101,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kS; ++i) {
-      mbar_init(full_bar(i), 1 + (TALL ? kW4DequantWarps / 2 : kW4DequantWarps));  // TMA producer + the stage's dequant warps
+      mbar_init(full_bar(i), 1 + kW4DequantWarps / 2);  // TMA producer + the K block's dequant group
       mbar_init(empty_bar(i), 1);
     }
     for (int i = 0; i < kRS; ++i) {
@@ -135,29 +130,15 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   };
 
   if (warp == 0) {
-    // -------- TMA producer: activation tiles every K block, raw weights every second one --------
+    // -------- TMA producer of the activation tiles: one per K block -----------------------------
     if (lane == 0) {
       tensormap_fence_acquire(ws->map_a);
-      tensormap_fence_acquire(ws->map_w);
-      uint32_t it = 0, raw_it = 0;
+      uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          if ((kb & 1) == 0) {
-            const int rs = raw_it % kRS;
-            const uint32_t rph = (raw_it / kRS) & 1;
-            if (!mbar_wait(raw_empty_bar(rs), rph ^ 1, abort_flag)) {
-              w4_report(ws, kStatusTimeoutEmpty, 0x10000u | raw_it);
-              *abort_flag = 1;
-              ok = false;
-              break;
-            }
-            mbar_arrive_expect_tx(raw_full_bar(rs), bn * 64);
-            tma_load_3d(raw_base + rs * kRawBytes, ws->map_w, raw_full_bar(rs), (kb >> 1) * 64, tn * bn, 0);
-            ++raw_it;
-          }
           const int st = it % kS;
           const uint32_t ph = (it / kS) & 1;
           if (!mbar_wait(empty_bar(st), ph ^ 1, abort_flag)) {
@@ -169,8 +150,32 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
           mbar_arrive_expect_tx(full_bar(st), kAStageBytes);
 #pragma unroll
           for (int h = 0; h < kHalves; ++h)
-            tma_load_3d(smem_base + st * kW4StageBytes + h * kW4AStageBytes, ws->map_a, full_bar(st), kb * 64,
+            tma_load_3d(smem_base + st * kStageBytes + h * kW4AStageBytes, ws->map_a, full_bar(st), kb * 64,
                         tm * kTileRows + h * kW4BM, 0);
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // -------- TMA producer of the raw weights: one scale group (128 K) per raw stage. It runs as
+    // far ahead as the raw ring allows, also into the next tile, whatever the operand stages do.
+    if (lane == 0) {
+      tensormap_fence_acquire(ws->map_w);
+      uint32_t raw_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tm, tn);
+        for (int g = 0; g < (num_kb >> 1); ++g, ++raw_it) {
+          const int rs = raw_it % kRS;
+          const uint32_t rph = (raw_it / kRS) & 1;
+          if (!mbar_wait(raw_empty_bar(rs), rph ^ 1, abort_flag)) {
+            w4_report(ws, kStatusTimeoutEmpty, 0x10000u | raw_it);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(raw_full_bar(rs), bn * 64);
+          tma_load_3d(raw_base + rs * kRawBytes, ws->map_w, raw_full_bar(rs), g * 64, tn * bn, 0);
         }
       }
     }
@@ -200,7 +205,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_src = smem_base + st * kW4StageBytes;
+          const uint32_t a_src = smem_base + st * kStageBytes;
           const uint32_t b_src = a_src + kAStageBytes;
 #pragma unroll
           for (int h = 0; h < kHalves; ++h)
@@ -244,6 +249,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
           __half* dst = out + static_cast<size_t>(row) * ldo + n_off + col0;
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
+            if (c + j >= bn) break;  // bn is a multiple of 16: the tile ends inside this 32-column read
             if (vec_ok && col0 + j + 7 < N) {
               uint4 o;
               o.x = as_u32(__floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
@@ -266,13 +272,12 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   } else if (warp >= 8) {
     // -------- dequant: raw int4 (64-byte swizzled rows) -> f16 K-major 128-byte swizzled tile -----
     // A thread expands one weight row of one K block: 32 raw bytes in, one 128-byte operand row
-    // out. 128 x bn tiles: the 256 threads take the (up to) 256 rows of every K block. Tall
-    // variant (at most 128 rows): two groups of 128 threads take alternate K blocks, so that one
-    // group's stores and proxy fence drain while the other group computes.
+    // out. Two groups of 128 threads take alternate K blocks, so that one group's stores and
+    // proxy fence drain while the other group computes.
     const int td = threadIdx.x - 256;
-    const int r = TALL ? (td & 127) : td;
-    const int grp = TALL ? (td >> 7) : 0;
-    constexpr int kStep = TALL ? 2 : 1;
+    const int r = td & 127;
+    const int grp = td >> 7;
+    constexpr int kStep = 2;
     const int groups = K >> 7;
     // Scales of eight consecutive groups arrive as one 16-byte load, one load ahead of their use.
     const bool vec_scales = (groups & 7) == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0;
@@ -296,7 +301,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         const uint32_t it = it_base + kb;
         const uint32_t raw_it = raw_it_base + (kb >> 1);
         const int rs = raw_it % kRS;
-        if (TALL || (kb & 1) == 0) {
+        {
           const uint32_t rph = (raw_it / kRS) & 1;
           if (!__all_sync(0xffffffffu, mbar_wait(raw_full_bar(rs), rph, abort_flag))) {
             if (lane == 0) {
@@ -331,8 +336,8 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         }
         if (row_live) {
           // Raw stage: row r is 64 bytes; its four 16-byte chunks are XOR-swizzled by (r / 2) % 4.
-          const uint8_t* raw_row = smem_gen + kS * kW4StageBytes + rs * kRawBytes + r * 64;
-          uint8_t* b_row = smem_gen + st * kW4StageBytes + kAStageBytes + r * 128;
+          const uint8_t* raw_row = smem_gen + kS * kStageBytes + rs * kRawBytes + r * 64;
+          uint8_t* b_row = smem_gen + st * kStageBytes + kAStageBytes + r * 128;
           const int sw_raw = (r >> 1) & 3, sw_b = r & 7;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
@@ -357,7 +362,7 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(full_bar(st));
-          if (TALL || (kb & 1)) mbar_arrive(raw_empty_bar(rs));
+          mbar_arrive(raw_empty_bar(rs));
         }
       }
     }
@@ -393,7 +398,7 @@ extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
 
 extern "C" __global__ void __launch_bounds__(kW4Threads, 1)
     b200_w4a16_gemm(const __half* scales, __half* out, void* ws, int M, int N, int K, int ldo, int n_off, int bn) {
-  if (w4_tall_variant(M, bn))
+  if (w4_tall_variant(M))
     w4gemm_body<true>(scales, out, reinterpret_cast<W4Workspace*>(ws), M, N, K, ldo, n_off, bn);
   else
     w4gemm_body<false>(scales, out, reinterpret_cast<W4Workspace*>(ws), M, N, K, ldo, n_off, bn);

@@ -16,7 +16,7 @@ from dataclasses import dataclass, field, asdict
 from typing import Dict, List, Optional, Tuple
 
 GEMM_THREADS, GEMM_SMEM = 256, 197888
-W4_THREADS, W4_SMEM = 512, 230656
+W4_THREADS, W4_SMEM = 512, 230656  # 1024 + 224 KiB + 256
 DECODE_THREADS, DECODE_SMEM = 512, {8: 180368, 16: 229520}
 SM_COUNT = 148
 
@@ -133,11 +133,11 @@ def plan_w4a16(function: str, M: int, N: int, K: int, group: int = 128, ldo: Opt
                                         [M, N, K, ldo, n_offset], (max(1, min(N // 16, sm_count // ksplit)), ksplit, 1),
                                         (DECODE_THREADS, 1, 1), DECODE_SMEM[mh]))
     elif group == 128 and K % 128 == 0:
-        # M >= 256: 256-row tiles of at most 128 columns (the kernel's tall variant), costed like 128 x 2bn tiles
+        # tiles: a multiple of 16, at most 128 columns; M >= 256 runs the kernel's 256-row variant
         tall = M >= 256
         rows = 256 if tall else 128
         bn, best = 0, 0.0
-        for cand in range(128 if tall else 256, 31, -32):
+        for cand in range(128, 15, -16):
             t = ((M + rows - 1) // rows) * ((N + cand - 1) // cand)
             cost = ((t + sm_count - 1) // sm_count) * (400.0 + (2 * cand if tall else cand))
             if not bn or cost < best * 0.9999:

@@ -39,6 +39,18 @@ def test_exact_on_integer_data(ctx, variant):
         assert (got == want).all(), (variant, M, N, K, np.abs(got.astype(np.float32) - want.astype(np.float32)).max())
 
 
+@pytest.mark.parametrize("tile_n", [16, 48, 80, 112, 128])
+def test_tensor_core_tile_widths(ctx, tile_n):
+    """Every tile width the tensor-core kernel accepts (multiples of 16 up to 128), on shapes with
+    ragged edges in M and N, for the 128-row and the 256-row variant and several tiles per CTA."""
+    rng = np.random.default_rng(40 + tile_n)
+    for (M, N, K) in [(40, 3 * tile_n + 8, 384), (300, 2 * tile_n + 24, 256), (520, 151 * 16, 128)]:
+        a, wq, s = exact_case(rng, M, N, K)
+        got = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM, tile_n=tile_n)
+        want = oracle.w4a16(a, wq, s, threads=THREADS)
+        assert (got == want).all(), (tile_n, M, N, K)
+
+
 def test_generic_other_group_sizes(ctx):
     rng = np.random.default_rng(22)
     for group in (32, 64, 256):

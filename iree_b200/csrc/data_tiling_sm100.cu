@@ -218,8 +218,22 @@ __device__ __forceinline__ void tiling_body(T* __restrict__ rm, T* __restrict__ 
     else if (E4 > 1 && step == E4) *reinterpret_cast<uint32_t*>(p) = v.w[0];
     else *p = v.e[0];
   };
+  // Bytes, transposed tiles two elements deep (the VNNI-style right-hand side, e.g. 16 x 2): a
+  // 16-byte unit is eight columns of two consecutive staged rows, interleaved. The unit starts at
+  // d = 0 and at a multiple of eight columns, so both rows are read as one aligned 8-byte word.
+  const bool interleave2 = sizeof(T) == 1 && ti && o3 == 2 && tl_step == 16 && (g.tile1 % 8) == 0;
   auto staged_read = [&](const TlUnit& x) -> Vec {
     if (tl_contiguous) return load_vec(staged_at(x.base_r, x.base_c, x.c, x.d), tl_step);
+    if (interleave2) {
+      const uint2 a = *reinterpret_cast<const uint2*>(staged_at(x.base_r, x.base_c, x.c, 0));
+      const uint2 b = *reinterpret_cast<const uint2*>(staged_at(x.base_r, x.base_c, x.c, 1));
+      Vec v;
+      v.w[0] = __byte_perm(a.x, b.x, 0x5140);
+      v.w[1] = __byte_perm(a.x, b.x, 0x7362);
+      v.w[2] = __byte_perm(a.y, b.y, 0x5140);
+      v.w[3] = __byte_perm(a.y, b.y, 0x7362);
+      return v;
+    }
     Vec v;
     uint32_t c = x.c, d = x.d;
 #pragma unroll

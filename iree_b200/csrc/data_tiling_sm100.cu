@@ -222,8 +222,28 @@ __device__ __forceinline__ void tiling_body(T* __restrict__ rm, T* __restrict__ 
   // 16-byte unit is eight columns of two consecutive staged rows, interleaved. The unit starts at
   // d = 0 and at a multiple of eight columns, so both rows are read as one aligned 8-byte word.
   const bool interleave2 = sizeof(T) == 1 && ti && o3 == 2 && tl_step == 16 && (g.tile1 % 8) == 0;
+  // Tiles whose rows are 2, 4 or 8 bytes long (K0 = 2 for bytes, ...), not transposed: a 16-byte
+  // unit is 8, 4 or 2 whole tile rows, each an aligned word of its own staged row.
+  const uint32_t run_bytes = (!ti && tl_step == E16 && (o3 * sizeof(T) == 2 || o3 * sizeof(T) == 4 || o3 * sizeof(T) == 8))
+                                 ? o3 * (uint32_t)sizeof(T) : 0u;
   auto staged_read = [&](const TlUnit& x) -> Vec {
     if (tl_contiguous) return load_vec(staged_at(x.base_r, x.base_c, x.c, x.d), tl_step);
+    if (run_bytes) {
+      Vec v;
+      if (run_bytes == 2) {
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j)
+          reinterpret_cast<uint16_t*>(&v)[j] = *reinterpret_cast<const uint16_t*>(staged_at(x.base_r, x.base_c, x.c + j, 0));
+      } else if (run_bytes == 4) {
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) v.w[j] = *reinterpret_cast<const uint32_t*>(staged_at(x.base_r, x.base_c, x.c + j, 0));
+      } else {
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j)
+          reinterpret_cast<uint2*>(&v)[j] = *reinterpret_cast<const uint2*>(staged_at(x.base_r, x.base_c, x.c + j, 0));
+      }
+      return v;
+    }
     if (interleave2) {
       const uint2 a = *reinterpret_cast<const uint2*>(staged_at(x.base_r, x.base_c, x.c, 0));
       const uint2 b = *reinterpret_cast<const uint2*>(staged_at(x.base_r, x.base_c, x.c, 1));

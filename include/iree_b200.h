@@ -336,7 +336,9 @@ iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int
  * that owns a slice of N writes into the full-width buffer (ldo = N, n_offset = 0 otherwise). */
 enum {
   IREE_B200_W4A16_AUTO = 0,
-  IREE_B200_W4A16_DECODE = 1,  /* M <= 16, N % 16 == 0, K % 256 == 0, group 128: weight streaming */
+  IREE_B200_W4A16_DECODE = 1,  /* M <= 16, N % 16 == 0, K % 256 == 0, K <= 16384, group 128, and `a`, `wq`,
+                                  `scales` on 16-byte boundaries (INVALID_ARGUMENT otherwise; AUTO then
+                                  picks another variant): weight streaming */
   IREE_B200_W4A16_GEMM = 2,    /* group 128, K % 128 == 0: tcgen05 with in-kernel dequantisation */
   IREE_B200_W4A16_GENERIC = 3, /* anything else */
 };
@@ -349,9 +351,9 @@ typedef struct {
   int32_t tile_n;    /* 0 = choose (tensor-core kernel only; else a multiple of 16 up to 128) */
 } iree_b200_w4a16_params_t;
 /* Device workspace the dispatch needs for an N-column weight matrix: tensor maps, status words
- * and the f32 scratch the decode kernel uses when K > 4096. It must be zero-filled once
- * after allocation; the kernels leave the scratch zeroed. One workspace serves one dispatch in
- * flight. */
+ * and the scratch the decode kernel uses when K > 4096 (a counter per 16-row tile and an f32
+ * partial tile per tile and 4096-wide K slice). It must be zero-filled once after allocation;
+ * the kernels leave the counters at zero. One workspace serves one dispatch in flight. */
 size_t iree_b200_w4a16_workspace_bytes(int32_t N);
 iree_b200_status_t iree_b200_w4a16(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                    const void* a, const void* wq, const void* scales, void* out, void* workspace);
@@ -434,7 +436,11 @@ iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void*
  * and the accumulator is tiled (and added, with ACCUMULATE) by the pack kernel; `workspace` is a
  * zero-filled device buffer of iree_b200_uk_mmt4d_workspace_bytes() bytes, 256-byte aligned.
  * Types: S8S8S32 (bit-exact), F16F16F32, BF16BF16F32, F16F16F16, BF16BF16BF16 (f32 accumulation
- * in tensor-core order; ACCUMULATE only with 32-bit outputs); other types: UNIMPLEMENTED. */
+ * in tensor-core order; ACCUMULATE only with 32-bit outputs); other types: UNIMPLEMENTED. The
+ * 16-bit-output types always accumulate in f32 and round once at the end, i.e. they behave as the
+ * reference does with IREE_UK_FLAG_MMT4D_SKIP_INTERMEDIATE_ROUNDINGS (0x400) set, whether or not
+ * the caller passes that flag (without it the reference's generic tile rounds to the narrow type
+ * after every K0 step, mmt4d_tile_generic.c). */
 size_t iree_b200_uk_mmt4d_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
                                           uint32_t flags);
 iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* lhs_buffer, int64_t lhs_offset,
@@ -512,18 +518,27 @@ iree_b200_status_t iree_b200_parameter_archive_write(const char* path, int64_t e
  * library's device image, so only inputs and outputs are passed; nothing is allocated or freed,
  * here or in any library this calls.
  *   - runs on the CUDA device that is current on the calling thread, on `stream` (a
- *     cudaStream_t; NULL = the default stream); all pointers are device pointers;
- *   - 1 <= M <= 16, N a multiple of 16 and at most IREE_B200_NOALLOC_MAX_N (OUT_OF_RANGE beyond
- *     it), K a multiple of 256, group size 128; out[m * ldo + n_offset + n] receives the result;
+ *     cudaStream_t; NULL = the default stream); all pointers are device pointers; `a`, `wq` and
+ *     `scales` must start on 16-byte boundaries (INVALID_ARGUMENT otherwise: the kernel reads
+ *     them with 16-byte loads and bulk copies);
+ *   - 1 <= M <= 16; N a multiple of 16 and at most IREE_B200_NOALLOC_MAX_N; K a multiple of 256
+ *     and at most 16384; group size 128. K runs in slices of 4096 and the built-in scratch holds
+ *     N * slices <= 2 * IREE_B200_NOALLOC_MAX_N, i.e. the full N up to K = 8192 and half of it
+ *     at K = 16384 (OUT_OF_RANGE beyond either limit); out[m * ldo + n_offset + n] receives the
+ *     result;
  *   - the first call on each device looks up the scratch array's address; make that first call
  *     before starting any stream capture;
- *   - every call on a device shares the one scratch array (about 2 MiB, held by every GPU that
+ *   - every call on a device shares the one scratch array (about 4 MiB, held by every GPU that
  *     loads the library until the process exits): calls that overlap on the GPU race, so keep
- *     them on one stream or order them yourself. */
+ *     them on one stream or order them yourself;
+ *   - a bounded wait that runs out inside the kernel leaves the result partly unwritten and is
+ *     reported by iree_b200_w4a16_decode_noalloc_status(), to be called once the stream has been
+ *     synchronised: DEADLINE_EXCEEDED (and the record is cleared), else OK. */
 #define IREE_B200_NOALLOC_MAX_N 32768
 iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, const void* wq, const void* scales, void* out,
                                                   int32_t M, int32_t N, int32_t K, int32_t ldo, int32_t n_offset,
                                                   void* stream);
+iree_b200_status_t iree_b200_w4a16_decode_noalloc_status(void);
 
 #ifdef __cplusplus
 }

@@ -1124,6 +1124,12 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather_peer_copies(iree_hal_
   }
   CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->dispatch_done, d->stream), "cuEventRecord");
   CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->collective_stream, d->dispatch_done, 0), "cuStreamWaitEvent");
+  // Barrier ahead of the copies: every rank's collective stream has waited for that rank's dispatch
+  // stream, so once all ranks have passed it, whatever a peer recorded earlier that still reads its
+  // receive buffer (from the buffer's previous use) has finished before anybody writes into it.
+  B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclAllReduce(channel->barrier_word, channel->barrier_word, 1, 2, 0, channel->comm,
+                                                       d->collective_stream),
+                                  "ncclAllReduce"));
   CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->copies_go, d->collective_stream), "cuEventRecord");
   // One copy engine moves a fraction of what the links carry, so the copies to different peers
   // run side by side on streams of their own, and a block of 64 MiB or more goes as two pieces.
@@ -1182,9 +1188,17 @@ namespace {
 
 constexpr uint32_t kGemmThreads = 256;
 constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
-// weight ring (4 stages of 16 rows x 2048 B), scale ring (4 x 4 KiB), 4 slots of 16 per-warp partials, barriers
-constexpr uint32_t kDecodeSmemM8 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 1 * 4 + (2 * 4 + 8) * 8 + 16;
-constexpr uint32_t kDecodeSmemM16 = 4 * 16 * 2048 + 4 * 4096 + 4 * 16 * 32 * 4 * 2 * 4 + (2 * 4 + 8) * 8 + 16 + 16 * 4 * 32 * 8;
+// weight ring (4 stages of 16 rows at a pitch of 2048 + 64 B), scale ring (4 x 4 KiB), 3 slots of 16 per-warp
+// chunk sums, the per-warp offsets, barriers (decode_smem_bytes in w4a16_decode.cuh)
+constexpr uint32_t kDecodeSmemM8 = 4 * 16 * 2112 + 4 * 4096 + 3 * 16 * 32 * 16 * 1 + 16 * 1 * 2 * 32 * 8 + 128;
+constexpr uint32_t kDecodeSmemM16 = 4 * 16 * 2112 + 4 * 4096 + 3 * 16 * 32 * 16 * 2 + 16 * 2 * 2 * 32 * 8 + 128;
+// K per CTA of the decode kernels, and the scratch they need beyond one slice: a counter per 16-row
+// tile (padded to 256 bytes), then one 1 KiB partial tile per tile and slice (DecodeScratchLayout).
+constexpr int kDecodeSliceK = 4096, kDecodeMaxSlices = 4;
+size_t decode_counter_bytes(int64_t N) { return (static_cast<size_t>(N / 16) * 4 + 255) & ~static_cast<size_t>(255); }
+size_t decode_scratch_bytes(int64_t N, int slices) {
+  return decode_counter_bytes(N) + static_cast<size_t>(N / 16) * slices * 1024;
+}
 constexpr uint32_t kW4SmemBytes = 1024 + 224 * 1024 + 256;  // operand stages + raw stages of either variant
 // staging region of the pack / unpack kernels: 64 rows of at most 512 bytes, 16 bytes of padding per row
 constexpr uint32_t kTilingStageBytes = 64 * (2 * 256 + 16);
@@ -1241,7 +1255,6 @@ struct iree_b200_context_t {
   // not pay for cuMemAlloc / cuMemFree.
   void* arena = nullptr;
   size_t arena_size = 0;
-  bool arena_w4_clean = true;
   bool dispatch_overlap = false;
   // SMs the operator entry points leave free (for collectives that run beside the dispatches)
   int reserved_sms = 0;
@@ -1588,16 +1601,22 @@ iree_b200_status_t iree_b200_matmul(iree_b200_context_t* context, const iree_b20
 
 iree_b200_status_t iree_b200_workspace_status(iree_b200_context_t* context, const void* workspace) {
   if (!context || !workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
-  uint32_t status[2] = {0, 0};
+  uint32_t status[3] = {0, 0, 0};
   B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(context->device, static_cast<const uint8_t*>(workspace) + 384,
                                                   status, sizeof status));
   B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
-  switch (status[0]) {
-    case 0: return IREE_B200_STATUS_OK;
-    case 5: return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "kernel rejected its arguments (shape / alignment)");
-    default:
-      return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[0], status[1]);
+  if (status[0] == 0) return IREE_B200_STATUS_OK;
+  if (status[0] == 5) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "kernel rejected its arguments (shape / alignment)");
+  if (status[0] >= 16 && status[2] > 0) {
+    // A decode dispatch that gave up may have left tile counters of its slice reduction behind
+    // (status word 2 is its N): clear them and the status words, so the workspace is usable again.
+    uint8_t* ws = static_cast<uint8_t*>(const_cast<void*>(workspace));
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + IREE_B200_WORKSPACE_BYTES,
+                                                   decode_counter_bytes(status[2]), 0));
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + 384, 128, 0));
+    B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
   }
+  return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[0], status[1]);
 }
 
 }  // extern "C"
@@ -1735,7 +1754,9 @@ static int w4_variant(const iree_b200_context_t* ctx, const iree_b200_w4a16_para
   if (p->variant != IREE_B200_W4A16_AUTO) return p->variant;
   const bool aligned = !(reinterpret_cast<uintptr_t>(a) % 16) && !(reinterpret_cast<uintptr_t>(wq) % 16) &&
                        !(reinterpret_cast<uintptr_t>(scales) % 2) && !(reinterpret_cast<uintptr_t>(out) % 2);
-  if (p->group_size == 128 && aligned && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0 && p->K <= 16384)
+  // The decode kernel fetches scale rows with bulk copies: they need a 16-byte aligned base as well.
+  const bool scales16 = !(reinterpret_cast<uintptr_t>(scales) % 16);
+  if (p->group_size == 128 && aligned && scales16 && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0 && p->K <= 16384)
     return IREE_B200_W4A16_DECODE;
   if (p->group_size == 128 && aligned && p->K % 128 == 0) return IREE_B200_W4A16_GEMM;
   return IREE_B200_W4A16_GENERIC;
@@ -1747,16 +1768,15 @@ static iree_b200_status_t w4_validate(const iree_b200_w4a16_params_t* p) {
   if (p->group_size <= 0 || (p->group_size & 1) || p->K % p->group_size)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "K (%d) must be a multiple of an even group size (%d)", p->K,
                 p->group_size);
-  if (p->ldo < p->n_offset + p->N || p->n_offset < 0)
-    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "output pitch %d cannot hold columns [%d, %d)", p->ldo, p->n_offset,
-                p->n_offset + p->N);
+  if (p->n_offset < 0 || static_cast<int64_t>(p->ldo) < static_cast<int64_t>(p->n_offset) + p->N)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "output pitch %d cannot hold columns [%d, %lld)", p->ldo, p->n_offset,
+                static_cast<long long>(p->n_offset) + p->N);
   return IREE_B200_STATUS_OK;
 }
 
 size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
-  const size_t n = N > 0 ? static_cast<size_t>(N) : 0;
-  const size_t scratch = 16 * n * 4 + (n / 16 + 1) * 4;
-  return (IREE_B200_WORKSPACE_BYTES + scratch + 255) & ~static_cast<size_t>(255);
+  const int64_t n = N > 0 ? N : 0;
+  return (IREE_B200_WORKSPACE_BYTES + decode_scratch_bytes(n, kDecodeMaxSlices) + 255) & ~static_cast<size_t>(255);
 }
 
 static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p) {
@@ -1820,26 +1840,33 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     if (params->group_size != 128 || params->M > 16 || params->N % 16 || params->K % 256 || params->K > 16384)
       return fail(IREE_B200_STATUS_INVALID_ARGUMENT,
                   "the decode kernel needs M <= 16, N %% 16 == 0, K %% 256 == 0, K <= 16384, group 128");
-    const int ksplit = 1;  // K beyond 4096 is covered by passes inside the kernel
+    // Bulk copies (weights, scales) and 16-byte loads (activations): a misaligned base would fault on the device.
+    if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(wq) % 16) ||
+        (reinterpret_cast<uintptr_t>(scales) % 16))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT,
+                  "the decode kernel needs activations, weights and scales on 16-byte boundaries");
     if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
-    void* scratch = static_cast<uint8_t*>(workspace) + IREE_B200_WORKSPACE_BYTES;
     iree_hal_b200_descriptor_set_binding_t bindings[5] = {{0, const_cast<void*>(a)},
                                                           {1, const_cast<void*>(wq)},
                                                           {2, const_cast<void*>(scales)},
                                                           {3, out},
-                                                          {4, scratch}};
+                                                          {4, workspace}};
     const int32_t constants[5] = {params->M, params->N, params->K, params->ldo, params->n_offset};
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 5, bindings));
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
     const int32_t ord = iree_hal_b200_executable_lookup(exe, params->M <= 8 ? "b200_w4a16_decode_m8" : "b200_w4a16_decode_m16");
+    // One CTA per SM; the CTAs that hold the K slices of the same tiles sit next to each other.
     const int tiles = params->N / 16;
-    int gx = sms / ksplit;
-    if (gx < 1) gx = 1;
-    if (gx > tiles) gx = tiles;
+    const int slices = (params->K + kDecodeSliceK - 1) / kDecodeSliceK;
+    int walkers = sms / slices;
+    if (walkers < 1) walkers = 1;
+    if (walkers > tiles) walkers = tiles;
+    const int gx = walkers * slices;
     // The decode exports order themselves on the device, so they may overlap the dispatch ahead.
-    cb->overlap = context->dispatch_overlap;
-    const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 5, 5, gx, ksplit, 1);
-    cb->overlap = false;
+    const bool saved_overlap = cb->overlap;  // what the caller set on the command buffer itself survives
+    cb->overlap = saved_overlap || context->dispatch_overlap;
+    const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 5, 5, gx, 1, 1);
+    cb->overlap = saved_overlap;
     return st;
   }
   if (variant == IREE_B200_W4A16_GEMM) {
@@ -1886,15 +1913,13 @@ iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree
   auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
   const size_t ws_bytes = iree_b200_w4a16_workspace_bytes(params->N);
   const size_t need = up(ws_bytes) + up(a_bytes) + up(w_bytes) + up(s_bytes) + up(c_bytes);
-  if (need > context->arena_size || !context->arena_w4_clean) {
+  if (need > context->arena_size) {
     B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
-    if (need > context->arena_size) {
-      if (context->arena) B200_RETURN_IF_ERROR(iree_hal_b200_buffer_free(d, context->arena));
-      context->arena = nullptr;
-      context->arena_size = 0;
-      B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(d, need, &context->arena));
-      context->arena_size = need;
-    }
+    if (context->arena) B200_RETURN_IF_ERROR(iree_hal_b200_buffer_free(d, context->arena));
+    context->arena = nullptr;
+    context->arena_size = 0;
+    B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(d, need, &context->arena));
+    context->arena_size = need;
   }
   uint8_t* base = static_cast<uint8_t*>(context->arena);
   void* ws = base;

@@ -6,12 +6,12 @@
 // owns a slice of N can write straight into the full-width result).
 //
 // Three kernels:
-//   b200_w4a16_decode_m8 / _m16  M <= 8 / 16: HBM-bound weight streaming. 16 warps each own a
-//       256-wide slice of K and keep the activations of that slice in registers for the whole
-//       kernel; weights go global -> shared (bulk copies into a 4-stage ring, one 32 KiB block of
-//       16 rows per tile) -> f16 fragments -> mma.sync (f32 accumulate); the per-group scale is
-//       applied to the f32 group sum. K beyond 4096 is covered by successive passes of the same
-//       CTA over an f32 scratch that it leaves zeroed.
+//   b200_w4a16_decode_m8 / _m16  M <= 8 / 16: HBM-bound weight streaming (w4a16_decode.cuh). 16 warps
+//       each own a 256-wide chunk of a 4096-wide K slice and keep the activations of that chunk in
+//       registers for the whole kernel; weights go global -> shared (bulk copies into a 4-stage
+//       ring, 16 rows per tile) -> f16 fragments -> mma.sync (f32 accumulate); the per-group scale
+//       is applied to the f32 group sum. K beyond 4096 is split over CTAs; the last CTA to finish
+//       a tile adds the slices' f32 partial tiles from a global scratch.
 //   b200_w4a16_gemm             larger M: tcgen05. Raw int4 tiles and activation tiles arrive by
 //       TMA; 8 warps expand the weights to f16 (exactly the dequant arithmetic above) into the
 //       128-byte-swizzled operand layout; one thread issues kind::f16 MMAs into TMEM. 128-row
@@ -385,15 +385,17 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
 
 using namespace b200;
 
+// Binding 4 is the dispatch's workspace: status words at byte 384, the slice-reduction scratch
+// (DecodeScratchLayout) from byte 512 on.
 extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
-    b200_w4a16_decode_m8(const __half* a, const uint8_t* wq, const __half* scales, __half* out, float* scratch, int M,
+    b200_w4a16_decode_m8(const __half* a, const uint8_t* wq, const __half* scales, __half* out, uint8_t* ws, int M,
                          int N, int K, int ldo, int n_off) {
-  decode_body<1>(a, wq, scales, out, scratch, M, N, K, ldo, n_off);
+  decode_body<1>(a, wq, scales, out, ws + 512, reinterpret_cast<uint32_t*>(ws + 384), M, N, K, ldo, n_off);
 }
 extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
-    b200_w4a16_decode_m16(const __half* a, const uint8_t* wq, const __half* scales, __half* out, float* scratch, int M,
+    b200_w4a16_decode_m16(const __half* a, const uint8_t* wq, const __half* scales, __half* out, uint8_t* ws, int M,
                           int N, int K, int ldo, int n_off) {
-  decode_body<2>(a, wq, scales, out, scratch, M, N, K, ldo, n_off);
+  decode_body<2>(a, wq, scales, out, ws + 512, reinterpret_cast<uint32_t*>(ws + 384), M, N, K, ldo, n_off);
 }
 
 extern "C" __global__ void __launch_bounds__(kW4Threads, 1)

@@ -7,7 +7,7 @@ sequence as ``hal.dispatch.extern`` ops. A plan is plain data (JSON-serialisable
 ``iree_b200.run_module`` executes through the HAL-shaped layer of the C ABI (executable create,
 push constants, descriptor set, dispatch), i.e. through the kernel ABI itself and not through the
 operator-level C entry points. The export table must stay identical to ``kEntries`` in
-``csrc/hal_b200.cc`` and to the table in INTEGRATION.md.
+``csrc/hal_b200.cc``.
 """
 from __future__ import annotations
 
@@ -17,7 +17,8 @@ from typing import Dict, List, Optional, Tuple
 
 GEMM_THREADS, GEMM_SMEM = 256, 197888
 W4_THREADS, W4_SMEM = 512, 230656  # 1024 + 224 KiB + 256
-DECODE_THREADS, DECODE_SMEM = 512, {8: 180368, 16: 229520}
+DECODE_THREADS, DECODE_SMEM = 512, {8: 184448, 16: 217216}
+DECODE_SLICE_K = 4096           # K per CTA of the decode kernels; K beyond it is split over CTAs
 SM_COUNT = 148
 
 ELEM_BYTES = {"f16": 2, "bf16": 2, "i8": 1, "i32": 4, "f32": 4}
@@ -126,11 +127,15 @@ def plan_w4a16(function: str, M: int, N: int, K: int, group: int = 128, ldo: Opt
     outputs = [{"name": "out", "shape": [M, ldo], "dtype": "f16"}]
     plan = Plan(function, inputs, outputs, [])
     if group == 128 and M <= 16 and N % 16 == 0 and K % 256 == 0 and K <= 16384:
-        ksplit = 1  # K beyond 4096 is covered by passes inside the kernel
-        plan.transients.append({"name": "scratch", "bytes": 16 * N * 4 + (N // 16 + 1) * 4, "zero": True})
+        # workspace: 512-byte header (status words at byte 384), a counter per 16-row tile padded to 256
+        # bytes, one 1 KiB f32 partial tile per tile and K slice (only touched when K spans several slices)
+        slices = (K + DECODE_SLICE_K - 1) // DECODE_SLICE_K
+        counters = ((N // 16) * 4 + 255) // 256 * 256
+        plan.transients.append({"name": "workspace", "bytes": 512 + counters + (N // 16) * slices * 1024, "zero": True})
         mh = 8 if M <= 8 else 16
-        plan.dispatches.append(Dispatch("b200_w4a16_decode_m%d" % mh, ["a", "wq", "scales", "out", "scratch"],
-                                        [M, N, K, ldo, n_offset], (max(1, min(N // 16, sm_count // ksplit)), ksplit, 1),
+        walkers = max(1, min(N // 16, sm_count // slices))
+        plan.dispatches.append(Dispatch("b200_w4a16_decode_m%d" % mh, ["a", "wq", "scales", "out", "workspace"],
+                                        [M, N, K, ldo, n_offset], (walkers * slices, 1, 1),
                                         (DECODE_THREADS, 1, 1), DECODE_SMEM[mh]))
     elif group == 128 and K % 128 == 0:
         # tiles: a multiple of 16, at most 128 columns; M >= 256 runs the kernel's 256-row variant

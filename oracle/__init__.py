@@ -84,6 +84,46 @@ def ref_lib():
     return _ref
 
 
+_conv = None
+
+
+def have_conv_ref() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "libuk_conv.so"))
+
+
+def conv_ref_lib():
+    """The reference's software f16 / bf16 conversions (builtins/ukernel/common.h:664-790)."""
+    global _conv
+    if _conv is None:
+        path = os.path.join(_HERE, "_ref", "libuk_conv.so")
+        if not os.path.exists(path):
+            build()
+        _conv = C.CDLL(path)
+    return _conv
+
+
+_CONV = {"f16_to_f32": (0, np.uint16, np.float32), "f32_to_f16": (1, np.float32, np.uint16),
+         "bf16_to_f32": (2, np.uint16, np.float32), "f32_to_bf16": (3, np.float32, np.uint16)}
+
+
+def convert_port(which: str, x: np.ndarray) -> np.ndarray:
+    """The restatement's conversion `which` over an array (raw 16-bit patterns as uint16)."""
+    code, din, dout = _CONV[which]
+    x = np.ascontiguousarray(x, din)
+    out = np.empty(x.shape, dout)
+    port_lib().oracle_convert_n(C.c_int(code), _ptr(x), _ptr(out), C.c_int64(x.size))
+    return out
+
+
+def convert_ref(which: str, x: np.ndarray) -> np.ndarray:
+    """The reference's own conversion `which` over an array."""
+    _, din, dout = _CONV[which]
+    x = np.ascontiguousarray(x, din)
+    out = np.empty(x.shape, dout)
+    getattr(conv_ref_lib(), "uk_conv_%s_n" % which)(_ptr(x), _ptr(out), C.c_int64(x.size))
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # Tile choice of the llvm-cpu data-tiling on x86-64 (restated from
 # compiler/src/iree/compiler/Codegen/Common/CPU/CPUMaterializeEncodingPass.cpp:168-277 and

@@ -65,6 +65,16 @@ static inline uint16_t f32_to_bf16(float f) {
 uint16_t oracle_f32_to_f16(float f) { return f32_to_f16(f); }
 float oracle_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
 uint16_t oracle_f32_to_bf16(float f) { return f32_to_bf16(f); }
+float oracle_bf16_to_f32(uint16_t b) { return bf16_to_f32(b); }
+// Array forms: which = 0 f16 -> f32, 1 f32 -> f16, 2 bf16 -> f32, 3 f32 -> bf16.
+void oracle_convert_n(int which, const void* in, void* out, idx_t n) {
+  for (idx_t i = 0; i < n; ++i) {
+    if (which == 0) ((float*)out)[i] = f16_to_f32(((const uint16_t*)in)[i]);
+    else if (which == 1) ((uint16_t*)out)[i] = f32_to_f16(((const float*)in)[i]);
+    else if (which == 2) ((float*)out)[i] = bf16_to_f32(((const uint16_t*)in)[i]);
+    else ((uint16_t*)out)[i] = f32_to_bf16(((const float*)in)[i]);
+  }
+}
 
 static int lhs_elem_size(int type) {
   switch (type) {

@@ -168,3 +168,67 @@ def test_f16_conversions_round_to_nearest_even(built):
         assert lib.oracle_f32_to_f16(C.c_float(v)) == int(np.float32(v).astype(np.float16).view(np.uint16)), v
     x = np.float32(1.00390625)  # bf16 tie: rounds to even
     assert lib.oracle_f32_to_bf16(C.c_float(float(x))) == 0x3F80
+
+
+def test_conversions_against_the_reference_routines(built):
+    """The restatement's f16 / bf16 <-> f32 conversions (compiler _Float16) against the
+    reference's own software routines (builtins/ukernel/common.h:664-790, compiled from the
+    header where it lies) over all 65 536 16-bit patterns and a seeded f32 sample.
+
+    They agree bit for bit on every value both can represent as a normal number. Where they
+    differ is stated here and checked, so the difference cannot grow unnoticed:
+      * 16 -> 32 bit: the reference routine returns zero for subnormal inputs (exponent field 0)
+        and a canonical quiet NaN for every NaN; hardware conversion (and _Float16) keeps
+        subnormals and NaN payloads.
+      * 32 -> 16 bit: identical for 2^-14 <= |x| < 65520 and for zero and infinity. Below 2^-14
+        the routine does not produce IEEE subnormals; in [65520, 131072) it leaves the exponent
+        field saturated with mantissa bits set (a NaN pattern) where IEEE rounds to infinity.
+    The reference's AVX-512 tile functions, which are what llvm-cpu runs on this host, convert in
+    hardware (arch/x86_64/mmt4d_x86_64_avx512_base.c:68-131) like the restatement.
+    """
+    if not oracle.have_conv_ref():
+        pytest.skip("oracle/_ref/libuk_conv.so not built (reference checkout absent)")
+    patterns = np.arange(65536, dtype=np.uint16)
+    for which, exp_shift, exp_max in (("f16_to_f32", 10, 31), ("bf16_to_f32", 7, 255)):
+        mine = oracle.convert_port(which, patterns).view(np.uint32)
+        ref = oracle.convert_ref(which, patterns).view(np.uint32)
+        exp = (patterns >> exp_shift) & exp_max
+        man = patterns & ((1 << exp_shift) - 1)
+        special = ((exp == 0) & (man != 0)) | ((exp == exp_max) & (man != 0))   # subnormal or NaN
+        assert (mine[~special] == ref[~special]).all(), which
+        sub = (exp == 0) & (man != 0)
+        assert (ref[sub] & 0x7fffffff == 0).all(), which + ": the reference routine flushes subnormals"
+        assert (mine[sub] & 0x7fffffff != 0).all(), which + ": the restatement keeps them"
+    rng = np.random.default_rng(0)
+    f16_values = patterns.view(np.float16).astype(np.float32)
+    finite = f16_values[np.isfinite(f16_values)]
+    order = np.sort(finite)
+    midpoints = ((order[:-1].astype(np.float64) + order[1:].astype(np.float64)) / 2).astype(np.float32)
+    x = np.concatenate([rng.standard_normal(1 << 18).astype(np.float32) * s for s in (1e-6, 1e-4, 1e-2, 1, 100, 3e4, 1e5)]
+                       + [finite, midpoints, np.array([0.0, -0.0, np.inf, -np.inf, 65504.0, 65519.99, 65520.0], np.float32)])
+    mine, ref = oracle.convert_port("f32_to_f16", x), oracle.convert_ref("f32_to_f16", x)
+    ax = np.abs(x)
+    agree_zone = ((ax >= 2.0 ** -14) & (ax < 65520.0)) | (ax == 0) | np.isinf(x) | (ax >= 131072.0)
+    assert (mine[agree_zone] == ref[agree_zone]).all()
+    assert agree_zone.sum() > 1_000_000
+    # every rounding tie inside the normal range is in the agree zone: both round to nearest even
+    ties = midpoints[(np.abs(midpoints) >= 2.0 ** -14) & (np.abs(midpoints) < 65520.0)]
+    assert (oracle.convert_port("f32_to_f16", ties) == oracle.convert_ref("f32_to_f16", ties)).all() and len(ties) > 60000
+    differ = mine != ref
+    assert ((ax[differ] < 2.0 ** -14) | ((ax[differ] >= 65520.0) & (ax[differ] < 131072.0))).all()
+    # f32 -> bf16: no difference anywhere on the sample (NaN inputs excluded: payloads differ by design)
+    assert (oracle.convert_port("f32_to_bf16", x) == oracle.convert_ref("f32_to_bf16", x)).all()
+
+
+def test_conversion_difference_zone_is_outside_the_benchmark_data(built):
+    """The value ranges the W4A16 / requant restatements are used on stay inside the zone where
+    the restatement's conversions equal the reference's: dequantised weights f16(w * s) with
+    |w| <= 8 and s in [0.005, 0.05] are either zero or at least 0.005 in magnitude, and outputs
+    of the benchmark configurations are far below 65520."""
+    a, wq, s = workloads.c4_w4a16(4, N=64, K=1024, seed=3)
+    w = workloads.unpack_int4(wq).astype(np.float16).reshape(64, 8, 128)
+    wd = (w * s[:, :, None]).astype(np.float16)
+    mag = np.abs(wd.astype(np.float32))
+    assert ((mag == 0) | (mag >= 2.0 ** -14)).all()
+    out = oracle.w4a16(a, wq, s).astype(np.float32)
+    assert np.abs(out).max() < 65520.0 and ((np.abs(out) == 0) | (np.abs(out) >= 2.0 ** -14)).mean() > 0.999

@@ -16,7 +16,8 @@ from iree_b200 import runtime as rt
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLDEN = os.path.join(HERE, "golden", "irpa")
-REFERENCE = "/root/reference/runtime/src/iree/io/formats/irpa/testdata"
+# same variable and default as oracle/Makefile
+REFERENCE = os.path.join(os.environ.get("REFERENCE", "/root/reference"), "runtime/src/iree/io/formats/irpa/testdata")
 
 
 def check_fixture(name, index, value_bytes=True):

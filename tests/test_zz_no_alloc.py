@@ -8,11 +8,13 @@ rtol = atol = 1e-2, is the bar). Collected last on purpose: a run that stops at 
 failure has then already run every other test.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
 
 import iree_b200 as ib
+import oracle
 from iree_b200 import workloads
 
 pytestmark = pytest.mark.gpu
@@ -36,6 +38,8 @@ def test_noalloc_matches_regular_entry_point_twice(ctx, M, N, K):
     ctx.w4a16(p, da, dw, ds, ref_out, ws)
     ctx.workspace_status(ws)
     want = ref_out.download(np.float16, (M, N))
+    # and directly against the CPU oracle, so the check does not rest on the other entry point alone
+    cpu = oracle.w4a16(a, wq, s, threads=os.cpu_count() or 1)
     out = ctx.alloc(M * N * 2)
     for call in range(2):                      # the second call reuses whatever the first left in the scratch
         out.fill(0x7E)
@@ -44,6 +48,8 @@ def test_noalloc_matches_regular_entry_point_twice(ctx, M, N, K):
         np.testing.assert_allclose(got.astype(np.float32), want.astype(np.float32), rtol=RTOL, atol=ATOL,
                                    err_msg="call %d" % call)
         assert (got == want).all(), "call %d" % call
+        np.testing.assert_allclose(got.astype(np.float32), cpu.astype(np.float32), rtol=RTOL, atol=ATOL,
+                                   err_msg="call %d against the CPU oracle" % call)
     for x in (da, dw, ds, ref_out, ws, out):
         x.free()
 
@@ -71,4 +77,25 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(ctx):
     assert "32768" in ib.last_error()
     assert _noalloc(ctx, d, d, d, d, 17, 16, 256, 16, 0) == 3              # INVALID_ARGUMENT: M > 16
     assert _noalloc(ctx, d, d, d, d, 1, 16, 100, 16, 0) == 3               # K not a multiple of 256
+    assert _noalloc(ctx, d, d, d, d, 1, 16, 16384 + 256, 16, 0) == 3       # K above 16384
+    assert _noalloc(ctx, d, d, d, d, 1, 16400, 16384, 16400, 0) == 11      # four K slices: half the columns at most
+    assert _noalloc(ctx, d, d, d, d, 1, 32768, 8192, 32768, 0) != 11       # two K slices: the full width fits
+    ctx.synchronize()
+    d.free()
+
+
+def test_noalloc_refuses_misaligned_operands_and_reports_status(ctx):
+    """A caller that sub-allocates from its own pool may hand in a pointer at an 8-byte offset; the
+    kernel would fault on it, so the entry point has to refuse it with a status (nothing runs)."""
+    class Shifted:                                                       # stands in for a pool sub-allocation
+        def __init__(self, ptr):
+            self.ptr = ptr
+    d = ctx.alloc(4096)
+    odd = Shifted(d.ptr + 8)
+    assert _noalloc(ctx, odd, d, d, d, 1, 16, 256, 16, 0) == 3 and "16-byte" in ib.last_error()
+    assert _noalloc(ctx, d, odd, d, d, 1, 16, 256, 16, 0) == 3
+    assert _noalloc(ctx, d, d, odd, d, 1, 16, 256, 16, 0) == 3
+    # no dispatch of this process has given up a wait: the shared status record reads OK
+    ctx.synchronize()
+    assert ib.library().iree_b200_w4a16_decode_noalloc_status() == 0, ib.last_error()
     d.free()

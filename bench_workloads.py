@@ -130,19 +130,21 @@ def describe(wl, world, steps):
                 else "replicas x%d" % world)}
 
 
-def allgather_mode(block_bytes):
+def allgather_mode(block_bytes, push_ok=False):
     """IREE_B200_ALLGATHER=push|peer|nccl. Default: the W4A16 tensor-core kernel pushes its output
     tiles into every rank's result buffer from its epilogue (push); dispatches that cannot do that
     use peer copies (copy engines) for blocks of a megabyte or more and the NCCL collective below."""
     mode = os.environ.get("IREE_B200_ALLGATHER", "auto")
     if mode == "auto":
+        mode = "push" if push_ok else ("peer" if block_bytes >= (1 << 20) else "nccl")
+    if mode == "push" and not push_ok:
         mode = "peer" if block_bytes >= (1 << 20) else "nccl"
     return mode
 
 
 def gather_mode_name(wl, world):
     block = wl.M * local_n(wl, world) * 2
-    mode = allgather_mode(block)
+    mode = allgather_mode(block, push_ok=wl.family == "w4a16" and wl.M >= 256 and local_n(wl, world) % 8 == 0)
     return {"nccl": "NCCL all-gather through the channel",
             "peer": "peer copies over NVLink by the copy engines + channel barrier",
             "push": "epilogue stores into every rank's result buffer over NVLink + arrival flags"}[mode]
@@ -287,7 +289,7 @@ def w4a16_state(ctx, wl, rank, world, channel):
         a, wq, s = gen.c4_w4a16(M, N=wl.N, K=K)
     st.ops, st.bytes = algorithmic(wl, n_local)
     n_sets = set_count(wq.nbytes + s.nbytes + a.nbytes + M * n_local * 2, 24)
-    mode = allgather_mode(M * n_local * 2) if channel is not None else None
+    mode = allgather_mode(M * n_local * 2, push_ok=M >= 256 and (rank * n_local) % 8 == 0) if channel is not None else None
     push = None
     if mode == "push":
         from iree_b200.sharding import PushGather
@@ -298,11 +300,13 @@ def w4a16_state(ctx, wl, rank, world, channel):
         ws = st.track(ctx.w4a16_workspace(n_local))
         if push is not None:
             dc = push.result(k)
-            p = rt.W4A16Params(M, n_local, K, 128, wl.N, rank * n_local, rt.W4A16_AUTO, 0)
+            p = rt.W4A16Params(M, n_local, K, 128, wl.N, rank * n_local, rt.W4A16_GEMM_WT, 0)
+            push.prepare(k, p, da, dw, ds, ws)
+            variant, tile_n = rt.W4A16_GEMM_WT, 128
         else:
             dc = st.alloc(M * n_local * 2)
             p = rt.W4A16Params(M, n_local, K, 128, n_local, 0, rt.W4A16_AUTO, 0)
-        variant, tile_n = ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
+            variant, tile_n = ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
         st.sets.append((p, da, dw, ds, dc, ws, variant, tile_n))
     if channel is not None and push is None:
         st.gathers = [st.alloc(world * M * n_local * 2) for _ in st.sets]
@@ -314,7 +318,7 @@ def w4a16_state(ctx, wl, rank, world, channel):
     def step(i):
         p, da, dw, ds, dc, ws, variant, tile_n = st.sets[i % n_sets]
         if push is not None:
-            push.run(i, p, da, dw, ds, ws, variant, tile_n)
+            push.run(i, p, ds, ws)
             return
         if channel is not None and i % n_sets == 0:
             rt.check(lib.iree_hal_b200_command_buffer_join_collectives(ctx.command_buffer))

@@ -341,6 +341,9 @@ enum {
                                   picks another variant): weight streaming */
   IREE_B200_W4A16_GEMM = 2,    /* group 128, K % 128 == 0: tcgen05 with in-kernel dequantisation */
   IREE_B200_W4A16_GENERIC = 3, /* anything else */
+  IREE_B200_W4A16_GEMM_WT = 4, /* GEMM's preconditions, M >= 256, result base and pitch on 16-byte boundaries,
+                                  n_offset % 8 == 0: tcgen05 with the dequantised weights as the tensor-memory
+                                  operand, results leave through TMA stores */
 };
 typedef struct {
   int32_t M, N, K;
@@ -363,6 +366,33 @@ iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const i
 iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                        const void* a, const void* wq, const void* scales, void* out, void* workspace,
                                        int32_t variant, int32_t tile_n);
+/* N-sharded form of the dispatch for the ranks of one channel (no counterpart in the reference, whose
+ * programs follow the sharded dispatch with an all-gather collective,
+ * runtime/src/iree/hal/drivers/cuda/nccl_channel.c:342-359): rank `rank` of `world` owns weight rows
+ * [n_offset, n_offset + N) and its kernel stores its column block into EVERY rank's full-width
+ * [M, ldo] result from its epilogue, so that no collective follows the dispatch.
+ *   results[p]  rank p's result buffer as mapped into this process (iree_hal_b200_buffer_import; the
+ *               entry of this rank is its own buffer); 16-byte aligned, ldo * 2 a multiple of 16;
+ *   flags[p]    rank p's arrival words, `world` uint32 each, zero-filled once (mapped the same way);
+ *   epoch       a value that grows with every use of this set of result buffers, starting at 1.
+ * prepare_push writes the workspace (tensor maps of every destination, flag pointers); run_push
+ * dispatches the kernel, which raises word `rank` of every rank's flags to `epoch` once all of its
+ * stores have completed; wait_arrivals enqueues the consumer side on this rank: a small kernel that
+ * returns when all `world` words of this rank's own flags have reached `epoch`. Its wait is bounded
+ * (about two seconds): iree_b200_workspace_status(workspace) then reports DEADLINE_EXCEEDED.
+ * Reuse rule: a rank may start the dispatch that overwrites a result buffer only after its own
+ * wait_arrivals for the previous use of that buffer, and whatever reads a result on a rank must be
+ * ordered on that rank's stream before its next dispatch into another buffer of the rotation (two
+ * buffers in rotation are enough). Needs M >= 256 and the GEMM_WT preconditions. */
+iree_b200_status_t iree_b200_w4a16_prepare_push(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                                const void* a, const void* wq, const void* scales,
+                                                void* const* results, void* const* flags, int32_t world,
+                                                int32_t rank, void* workspace);
+iree_b200_status_t iree_b200_w4a16_run_push(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                            const void* scales, void* result, void* workspace, int32_t world,
+                                            int32_t rank, int32_t epoch);
+iree_b200_status_t iree_b200_w4a16_wait_arrivals(iree_b200_context_t* context, const void* own_flags, void* workspace,
+                                                 int32_t world, int32_t epoch);
 /* Host-buffer form (copies in, runs, copies out, waits). With ldo != N the existing contents of
  * `out` are uploaded first so that columns outside the slice survive. */
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,

@@ -38,7 +38,7 @@ namespace HAL = IREE::HAL;
 
 constexpr int64_t kGemmThreads = 256, kGemmSmem = 197888;
 constexpr int64_t kW4GemmThreads = 512, kW4GemmSmem = 181504;
-constexpr int64_t kDecodeThreads = 512, kDecodeSmemM8 = 184448, kDecodeSmemM16 = 217216;
+constexpr int64_t kDecodeThreads = 512, kDecodeSmemM8 = 180864, kDecodeSmemM16 = 213632;
 
 enum class ElemKind { F16, BF16, I8, Unsupported };
 

@@ -460,6 +460,11 @@ int32_t iree_b200_internal_set_error(int32_t code, const char* message) {
   return code;
 }
 
+static iree_b200_status_t encode_decode_weight_map(const void* wq, int32_t N, int32_t K, void* out_map);
+int32_t iree_b200_internal_encode_decode_weight_map(const void* wq, int32_t N, int32_t K, void* out_map) {
+  return encode_decode_weight_map(wq, N, K, out_map);
+}
+
 // ---- device ----------------------------------------------------------------------------------
 iree_b200_status_t iree_hal_b200_device_create(int32_t ordinal, iree_hal_b200_device_t** out_device) {
   if (!out_device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_device is NULL");
@@ -1188,10 +1193,10 @@ namespace {
 
 constexpr uint32_t kGemmThreads = 256;
 constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
-// weight ring (4 stages of 16 rows at a pitch of 2048 + 64 B), scale ring (4 x 4 KiB), 3 slots of 16 per-warp
+// weight ring (4 stages of 16 rows x 2048 B + 128 B), scale ring (4 x 4 KiB), 3 slots of 16 per-warp
 // chunk sums, the per-warp offsets, barriers (decode_smem_bytes in w4a16_decode.cuh)
-constexpr uint32_t kDecodeSmemM8 = 4 * 16 * 2112 + 4 * 4096 + 3 * 16 * 32 * 16 * 1 + 16 * 1 * 2 * 32 * 8 + 128;
-constexpr uint32_t kDecodeSmemM16 = 4 * 16 * 2112 + 4 * 4096 + 3 * 16 * 32 * 16 * 2 + 16 * 2 * 2 * 32 * 8 + 128;
+constexpr uint32_t kDecodeSmemM8 = 4 * (16 * 2048 + 128) + 4 * 4096 + 3 * 16 * 32 * 16 * 1 + 16 * 1 * 2 * 32 * 8 + 128;
+constexpr uint32_t kDecodeSmemM16 = 4 * (16 * 2048 + 128) + 4 * 4096 + 3 * 16 * 32 * 16 * 2 + 16 * 2 * 2 * 32 * 8 + 128;
 // K per CTA of the decode kernels, and the scratch they need beyond one slice: a counter per 16-row
 // tile (padded to 256 bytes), then one 1 KiB partial tile per tile and slice (DecodeScratchLayout).
 constexpr int kDecodeSliceK = 4096, kDecodeMaxSlices = 4;
@@ -1200,6 +1205,9 @@ size_t decode_scratch_bytes(int64_t N, int slices) {
   return decode_counter_bytes(N) + static_cast<size_t>(N / 16) * slices * 1024;
 }
 constexpr uint32_t kW4SmemBytes = 1024 + 224 * 1024 + 256;  // operand stages + raw stages of either variant
+// b200_w4a16_gemm_wt: 4 activation stages of 32 KiB, 6 raw stages of 8 KiB, 2 staging tiles of 16 KiB, barriers
+constexpr uint32_t kW4WtSmemBytes = 1024 + 4 * 32768 + 6 * 8192 + 2 * 16384 + 512;
+constexpr int kWtMaxDestinations = 8;
 // staging region of the pack / unpack kernels: 64 rows of at most 512 bytes, 16 bytes of padding per row
 constexpr uint32_t kTilingStageBytes = 64 * (2 * 256 + 16);
 
@@ -1234,6 +1242,8 @@ const EntryDecl kEntries[] = {
     {"b200_w4a16_decode_m8", {512, 1, 1}, kDecodeSmemM8},
     {"b200_w4a16_decode_m16", {512, 1, 1}, kDecodeSmemM16},
     {"b200_w4a16_gemm", {512, 1, 1}, kW4SmemBytes},
+    {"b200_w4a16_gemm_wt", {512, 1, 1}, kW4WtSmemBytes},
+    {"b200_wait_arrivals", {32, 1, 1}, 0},
     {"b200_w4a16_generic", {256, 1, 1}, 0},
     {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b16", {256, 1, 1}, kTilingStageBytes},
@@ -1758,7 +1768,13 @@ static int w4_variant(const iree_b200_context_t* ctx, const iree_b200_w4a16_para
   const bool scales16 = !(reinterpret_cast<uintptr_t>(scales) % 16);
   if (p->group_size == 128 && aligned && scales16 && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0 && p->K <= 16384)
     return IREE_B200_W4A16_DECODE;
-  if (p->group_size == 128 && aligned && p->K % 128 == 0) return IREE_B200_W4A16_GEMM;
+  if (p->group_size == 128 && aligned && p->K % 128 == 0) {
+    // Many rows: the kernel with the weights as the tensor-memory operand; it leaves its results by
+    // TMA stores, which need the result on 16-byte boundaries.
+    const bool out16 = !(reinterpret_cast<uintptr_t>(out) % 16) && (static_cast<int64_t>(p->ldo) * 2) % 16 == 0 &&
+                       p->n_offset % 8 == 0;
+    return (p->M >= 256 && out16) ? IREE_B200_W4A16_GEMM_WT : IREE_B200_W4A16_GEMM;
+  }
   return IREE_B200_W4A16_GENERIC;
 }
 
@@ -1801,6 +1817,76 @@ static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a1
   return best;
 }
 
+// The decode kernels' view of the weights when K spans several 4096-wide slices: [N, K / 16] 8-byte
+// elements, box 256 x 8 (eight rows of one slice, 16 KiB), no swizzle.
+static iree_b200_status_t encode_decode_weight_map(const void* wq, int32_t N, int32_t K, void* out_map) {
+  B200_RETURN_IF_ERROR(ensure_cuda());
+  if ((reinterpret_cast<uintptr_t>(wq) % 16) || (K % 256))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "weights must start on a 16-byte boundary and K must be a multiple of 256");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K) / 16, static_cast<cuuint64_t>(N)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) / 2};
+  const cuuint32_t box[2] = {256, 8};
+  const cuuint32_t estrides[2] = {1, 1};
+  CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(wq), dims, strides,
+                                                 box, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                     "cuTensorMapEncodeTiled(weights)");
+  memcpy(out_map, &map, 128);
+  return IREE_B200_STATUS_OK;
+}
+
+// Rank-2 row-major f16 tensor [rows, cols] with row pitch `pitch_bytes`, no swizzle: the output maps of
+// b200_w4a16_gemm_wt (box: 128 columns x 64 rows).
+static iree_b200_status_t encode_output_map(const void* device_ptr, uint32_t cols, uint32_t rows, uint64_t pitch_bytes,
+                                            void* out_map) {
+  B200_RETURN_IF_ERROR(ensure_cuda());
+  if ((reinterpret_cast<uintptr_t>(device_ptr) % 16) || pitch_bytes % 16)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "result base and row pitch must be multiples of 16 bytes");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {128, 64};
+  const cuuint32_t estrides[2] = {1, 1};
+  CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(device_ptr), dims,
+                                                 strides, box, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                     "cuTensorMapEncodeTiled(result)");
+  memcpy(out_map, &map, 128);
+  return IREE_B200_STATUS_OK;
+}
+
+// Workspace of b200_w4a16_gemm_wt: operand maps, zeroed status words, one output map per destination and
+// (several ranks) the pointers to every rank's arrival words. 512 + 1024 + 64 bytes.
+constexpr size_t kWtWorkspaceBytes = 512 + kWtMaxDestinations * 128 + kWtMaxDestinations * 8;
+static iree_b200_status_t w4_prepare_wt(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                        const void* a, const void* wq, void* const* results, void* const* flags,
+                                        int32_t world, void* workspace) {
+  if (world < 1 || world > kWtMaxDestinations)
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "1 to %d destinations", kWtMaxDestinations);
+  if (params->n_offset % 8)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "n_offset must be a multiple of 8 (TMA stores start on 16-byte boundaries)");
+  uint8_t host[kWtWorkspaceBytes];
+  memset(host, 0, sizeof host);
+  B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, 128, a, params->K,
+                                  params->M, 1, 64, 128, host));
+  B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_64B, 64, wq, params->K / 2,
+                                  params->N, 1, 64, 128, host + 128));
+  for (int32_t p = 0; p < world; ++p) {
+    if (!results[p]) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "result buffer of rank %d is NULL", p);
+    // columns beyond this rank's block are outside the map, so a ragged last tile cannot touch them
+    B200_RETURN_IF_ERROR(encode_output_map(results[p], static_cast<uint32_t>(params->n_offset + params->N),
+                                           static_cast<uint32_t>(params->M), static_cast<uint64_t>(params->ldo) * 2,
+                                           host + 512 + 128 * p));
+    if (flags) {
+      const uint64_t f = reinterpret_cast<uint64_t>(flags[p]);
+      memcpy(host + 512 + kWtMaxDestinations * 128 + 8 * p, &f, 8);
+    }
+  }
+  return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
+}
+
 iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                            const void* a, const void* wq, const void* scales, const void* out,
                                            void* workspace, int32_t* out_variant, int32_t* out_tile_n) {
@@ -1809,11 +1895,25 @@ iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const i
   const int variant = w4_variant(context, params, a, wq, scales, out);
   if (out_variant) *out_variant = variant;
   if (out_tile_n) *out_tile_n = 0;
-  if (variant != IREE_B200_W4A16_GEMM || !params->M || !params->N) return IREE_B200_STATUS_OK;
+  if (variant == IREE_B200_W4A16_DECODE && params->K > kDecodeSliceK && params->N) {
+    // K beyond one slice: the kernel fetches its weight tiles through a tensor map at the start of the workspace
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 128))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
+    uint8_t map[128];
+    B200_RETURN_IF_ERROR(encode_decode_weight_map(wq, params->N, params->K, map));
+    return iree_hal_b200_transfer_h2d(context->device, map, workspace, sizeof map);
+  }
+  if ((variant != IREE_B200_W4A16_GEMM && variant != IREE_B200_W4A16_GEMM_WT) || !params->M || !params->N)
+    return IREE_B200_STATUS_OK;
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 128))
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
   if (params->group_size != 128 || params->K % 128)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the tensor-core kernel needs group size 128 and K %% 128 == 0");
+  if (variant == IREE_B200_W4A16_GEMM_WT) {
+    if (out_tile_n) *out_tile_n = 128;
+    void* results[1] = {const_cast<void*>(out)};
+    return w4_prepare_wt(context, params, a, wq, results, nullptr, 1, workspace);
+  }
   const int bn = w4_choose_tile_n(context, params);
   if (!bn) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tile_n %d is not usable", params->tile_n);
   if (out_tile_n) *out_tile_n = bn;
@@ -1824,6 +1924,67 @@ iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const i
   B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_64B, 64, wq, params->K / 2,
                                   params->N, 1, 64, bn, host + 128));
   return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
+}
+
+static iree_b200_status_t w4_run_wt(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                    const void* scales, void* out, void* workspace, int32_t world, int32_t rank,
+                                    int32_t epoch) {
+  if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
+  if (params->group_size != 128 || params->K % 128 || params->n_offset % 8)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "this kernel needs group size 128, K %% 128 == 0 and n_offset %% 8 == 0");
+  auto* cb = context->command_buffer;
+  iree_hal_b200_descriptor_set_binding_t bindings[3] = {{0, const_cast<void*>(scales)}, {1, out}, {2, workspace}};
+  const int32_t constants[7] = {params->M, params->N, params->K, params->ldo, params->n_offset, (world << 8) | rank, epoch};
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 3, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+  const int sms = usable_sms(context);
+  const int64_t tiles = static_cast<int64_t>((params->M + 255) / 256) * ((params->N + 127) / 128);
+  const int32_t ord = iree_hal_b200_executable_lookup(context->executable, "b200_w4a16_gemm_wt");
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_w4a16_gemm_wt missing from the executable");
+  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 3, 7, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);
+}
+
+iree_b200_status_t iree_b200_w4a16_prepare_push(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                                const void* a, const void* wq, const void* scales,
+                                                void* const* results, void* const* flags, int32_t world,
+                                                int32_t rank, void* workspace) {
+  if (!context || !results || !flags) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  B200_RETURN_IF_ERROR(w4_validate(params));
+  if (rank < 0 || rank >= world) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "rank %d is not in a channel of %d", rank, world);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 128))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
+  if (params->group_size != 128 || params->K % 128 || params->M < 256 || (reinterpret_cast<uintptr_t>(a) % 16) ||
+      (reinterpret_cast<uintptr_t>(wq) % 16) || (reinterpret_cast<uintptr_t>(scales) % 2))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT,
+                "the pushing dispatch needs M >= 256, group size 128, K %% 128 == 0 and 16-byte aligned operands");
+  for (int32_t p = 0; p < world; ++p)
+    if (!flags[p]) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "arrival words of rank %d are NULL", p);
+  return w4_prepare_wt(context, params, a, wq, results, flags, world, workspace);
+}
+
+iree_b200_status_t iree_b200_w4a16_run_push(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                            const void* scales, void* result, void* workspace, int32_t world,
+                                            int32_t rank, int32_t epoch) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  B200_RETURN_IF_ERROR(w4_validate(params));
+  if (world < 1 || world > kWtMaxDestinations || rank < 0 || rank >= world)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "rank %d is not in a channel of %d (at most %d)", rank, world, kWtMaxDestinations);
+  if (!scales || !result) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
+  return w4_run_wt(context, params, scales, result, workspace, world, rank, epoch);
+}
+
+iree_b200_status_t iree_b200_w4a16_wait_arrivals(iree_b200_context_t* context, const void* own_flags, void* workspace,
+                                                 int32_t world, int32_t epoch) {
+  if (!context || !own_flags || !workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (world < 1 || world > kWtMaxDestinations) return fail(IREE_B200_STATUS_OUT_OF_RANGE, "1 to %d ranks", kWtMaxDestinations);
+  auto* cb = context->command_buffer;
+  iree_hal_b200_descriptor_set_binding_t bindings[2] = {{0, const_cast<void*>(own_flags)}, {1, workspace}};
+  const int32_t constants[2] = {world, epoch};
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 2, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+  const int32_t ord = iree_hal_b200_executable_lookup(context->executable, "b200_wait_arrivals");
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_wait_arrivals missing from the executable");
+  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 2, 2, 1, 1, 1);
 }
 
 iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
@@ -1881,6 +2042,7 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_gemm");
     return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 3, 6, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);
   }
+  if (variant == IREE_B200_W4A16_GEMM_WT) return w4_run_wt(context, params, scales, out, workspace, 1, 0, 0);
   if (variant == IREE_B200_W4A16_GENERIC) {
     iree_hal_b200_descriptor_set_binding_t bindings[4] = {
         {0, const_cast<void*>(a)}, {1, const_cast<void*>(wq)}, {2, const_cast<void*>(scales)}, {3, out}};

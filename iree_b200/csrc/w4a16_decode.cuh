@@ -89,10 +89,14 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 // Work is cut along N into tiles of 16 weight rows and along K into slices of 4096. A CTA owns
 // one K slice for its whole life and walks over every (grid / slices)-th tile; its 16 warps each
 // own a 256-wide chunk of the slice and keep the activations of that chunk in registers, already
-// in the order the MMAs want them. Weight rows of a tile travel global -> shared by bulk copies
-// (one per row, all issued by one instruction of the warp on duty) into a four-stage ring guarded
-// by full / empty mbarriers; staged rows are 64 bytes further apart than their length, so that
-// the two rows a quarter warp reads with one 16-byte load instruction fall into different banks.
+// in the order the MMAs want them. A tile travels global -> shared as two blocks of eight rows
+// into a four-stage ring guarded by full / empty mbarriers: two bulk copies when the CTA's slice
+// is the whole row (the blocks are contiguous in memory), else two TMA boxes from a tensor map in
+// the workspace (issuing one copy per row would cost the issuing warp ~130 cycles each, more than
+// the rows take to arrive). Even / odd fragment rows are taken from different blocks, and on the
+// bulk-copy path the second block is staged 64 bytes off the first block's bank alignment, so that
+// the two rows a quarter warp reads with one 16-byte load instruction fall into different banks
+// (a TMA box must land on a 128-byte boundary: there the two rows share their banks).
 //
 // A warp turns its 16 x 128 bytes of a tile into f16 MMA operands with two logic operations per
 // register: the nibbles become the biased halves 1032 + w (low nibbles, 0x6400 | n ^ 8) and
@@ -117,15 +121,15 @@ constexpr int kDecodeTileRows = 16;                          // weight rows per 
 constexpr int kDecodeStages = 4;                             // weight tiles resident in shared memory
 constexpr int kDecodeSlots = 3;                              // tiles whose chunk sums are live at the same time
 constexpr int kDecodeFinalizeLag = 2;                        // a tile is reduced this many tiles behind the main loop
-constexpr int kDecodeRowPitch = kDecodeSliceK / 2 + 64;      // staged row pitch: 2048 B of data + 64 B
-constexpr int kDecodeStageBytes = kDecodeTileRows * kDecodeRowPitch;
+constexpr int kDecodeHalfSkew = 64;                          // bulk-copy path: the second eight rows sit this far off the first block's banks
+constexpr int kDecodeStageBytes = kDecodeTileRows * (kDecodeSliceK / 2) + 128;  // two blocks of 8 rows x <= 2048 B + skew
 constexpr int kDecodeScaleStageBytes = 16 * 128 * 2;         // 16 rows x up to 128 groups of f16
 constexpr int kDecodeBarrierBytes = 128;                     // 14 mbarriers + the abort word
 static_assert(kDecodeSlots > kDecodeFinalizeLag, "a slot must be reduced before the main loop needs it again");
 
 // Dynamic shared memory:
-//   weight ring  [stage][row][pitch]            the tile's rows of the CTA's K slice
-//   scale ring   [stage][4096 B]                the tile's scale rows (whole rows, or the slice's 64 bytes of each)
+//   weight ring  [stage]{[8][pitch], 64 B, [8][pitch]}  the tile's rows of the CTA's K slice, pitch = slice bytes per row
+//   scale ring   [stage][4096 B]                the tile's scale rows (whole rows: one contiguous copy)
 //   chunk sums   [slot][warp][lane][MH] float4  MMA fragment order; doubles as the staging area of the prologue
 //   offsets      [warp][MH][step][lane] float2  the constant part of each group sum, per output column
 //   mbarriers    weights full / empty per stage, chunk sums full / empty per slot; abort word
@@ -185,8 +189,8 @@ __device__ __forceinline__ bool decode_wait(uint32_t bar, uint32_t parity, volat
 template <int MH>
 __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const uint8_t* __restrict__ wq,
                                             const __half* __restrict__ scales, __half* __restrict__ out,
-                                            void* __restrict__ scratch, uint32_t* __restrict__ status, int M, int N,
-                                            int K, int ldo, int n_off) {
+                                            void* __restrict__ scratch, uint32_t* __restrict__ status,
+                                            const void* __restrict__ wmap, int M, int N, int K, int ldo, int n_off) {
   extern __shared__ __align__(128) uint8_t decode_smem[];
   constexpr int kWRingBytes = kDecodeStages * kDecodeStageBytes;
   constexpr int kSRingBytes = kDecodeStages * kDecodeScaleStageBytes;
@@ -219,24 +223,23 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   // that every arrival count is the constant 16.
   const bool has_chunk = warp < active_warps;
   const int kc = k_slice0 + warp * kDecodeChunkK;
-  const uint32_t slice_row_bytes = active_warps * (kDecodeChunkK / 2);
-  // Scale rows: with one slice the tile's rows are one contiguous block; with several, the 64
-  // bytes of each row that belong to this slice are fetched row by row when every slice's share
-  // is a multiple of 16 bytes, else the whole rows are.
-  const bool sliced_scales = slices > 1 && (K & 1023) == 0;
-  const uint32_t srow_pitch = sliced_scales ? static_cast<uint32_t>(active_warps) * 4u : static_cast<uint32_t>(groups_per_row) * 2u;
+  // Staged layout of a tile: rows 0..7 at `pitch` bytes each, then (bulk-copy path: 64 bytes off the
+  // bank alignment) rows 8..15. Fragment row g (and g + 8) of the MMA is tile row (g & 1) * 8 + (g >> 1) (+ 4): a
+  // quarter warp holds one even and one odd g, i.e. one row of each block.
+  const uint32_t pitch = slices == 1 ? static_cast<uint32_t>(row_bytes) : static_cast<uint32_t>(kDecodeSliceK / 2);
+  const uint32_t half_bytes = 8 * pitch;
+  const uint32_t half_pitch = half_bytes + (slices == 1 ? kDecodeHalfSkew : 0);  // second block's offset in the stage
+  const int tile_row = (g & 1) * 8 + (g >> 1);  // of fragment row g; fragment row g + 8 is tile row + 4
+  const uint32_t srow_pitch = static_cast<uint32_t>(groups_per_row) * 2u;
   const uint32_t scale_tile_bytes = kDecodeTileRows * srow_pitch;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kDecodeStages; ++i) {
-      mbar_init(wfull_bar(i), 1);
-      mbar_init(wempty_bar(i), kDecodeWarps);
-    }
-    for (int i = 0; i < kDecodeSlots; ++i) {
-      mbar_init(pfull_bar(i), kDecodeWarps);
-      mbar_init(pempty_bar(i), 1);
-    }
-    *abort_flag = 0;
+  if (threadIdx.x < 2 * kDecodeStages + 2 * kDecodeSlots) {
+    // one barrier per thread: weights full (1 arrival), weights empty (16), chunk sums full (16), empty (1)
+    const int i = threadIdx.x;
+    const bool sixteen = (i >= kDecodeStages && i < 2 * kDecodeStages) ||
+                         (i >= 2 * kDecodeStages && i < 2 * kDecodeStages + kDecodeSlots);
+    mbar_init(bars + 8u * i, sixteen ? kDecodeWarps : 1);
+    if (i == 0) *abort_flag = 0;
     mbar_fence_init();
   }
   // The next kernel on the stream may be scheduled as soon as this one's blocks leave their SMs:
@@ -246,21 +249,23 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   __syncthreads();
 
   // Feeding the weight ring is a side job that rotates over the warps (tile jp is fetched by warp
-  // jp % 16). Lanes 0..15 copy one weight row each; lane 16 (or lanes 16..31, one row each) the scales.
+  // jp % 16): lanes 0 and 1 fetch the two eight-row blocks, lane 2 the scale rows.
+  if (slices > 1 && threadIdx.x == 0) tensormap_fence_acquire(wmap);
   auto produce = [&](int jp) -> bool {
     const int st = jp % kDecodeStages;
     if (!decode_wait(wempty_bar(st), ((jp / kDecodeStages) & 1) ^ 1, abort_flag, status, kStatusDecodeStage, jp, N))
       return false;
     const size_t row0 = static_cast<size_t>(walker + jp * walkers) * kDecodeTileRows;
-    if (lane == 0) mbar_arrive_expect_tx(wfull_bar(st), kDecodeTileRows * slice_row_bytes + scale_tile_bytes);
+    // a TMA box always delivers its full 8 x 2048 bytes (columns past the row's end arrive as zeros)
+    if (lane == 0) mbar_arrive_expect_tx(wfull_bar(st), 2 * half_bytes + scale_tile_bytes);
     __syncwarp();
-    if (lane < kDecodeTileRows) {
-      bulk_load(wring + st * kDecodeStageBytes + lane * kDecodeRowPitch, wq + (row0 + lane) * row_bytes + (k_slice0 >> 1),
-                slice_row_bytes, wfull_bar(st));
-    } else if (sliced_scales) {
-      bulk_load(sring + st * kDecodeScaleStageBytes + (lane - 16) * srow_pitch,
-                scales + (row0 + lane - 16) * groups_per_row + (k_slice0 >> 7), srow_pitch, wfull_bar(st));
-    } else if (lane == 16) {
+    if (lane < 2) {
+      const uint32_t dst = wring + st * kDecodeStageBytes + lane * half_pitch;
+      if (slices == 1)
+        bulk_load(dst, wq + (row0 + 8 * lane) * row_bytes, half_bytes, wfull_bar(st));
+      else
+        tma_load_2d(dst, wmap, wfull_bar(st), slice * (kDecodeSliceK / 16), static_cast<int>(row0) + 8 * lane);
+    } else if (lane == 2) {
       bulk_load(sring + st * kDecodeScaleStageBytes, scales + row0 * groups_per_row, scale_tile_bytes, wfull_bar(st));
     }
     return true;
@@ -339,7 +344,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   // Adds the K chunks of tile jf in chunk order (so the result does not depend on arrival order),
   // frees the slot and writes the 16 x M results (one slice) or hands the partial tile to the
   // slice reduction. One warp per tile, in rotation.
-  // Fragment order: vals[mh][c] is weight row g + 8 (c / 2), activation row 2 q + (c & 1) + 8 mh.
+  // Fragment order: vals[mh][c] is tile row tile_row + 4 (c / 2), activation row 2 q + (c & 1) + 8 mh.
   auto finalize = [&](int jf) -> bool {
     const int slot = jf % kDecodeSlots;
     const int tile = walker + jf * walkers;
@@ -383,13 +388,16 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh)
         __stcg(parts + slice * 64 + mh, make_float4(vals[mh][0], vals[mh][1], vals[mh][2], vals[mh][3]));
-      __threadfence();
-      __syncwarp();
+      __syncwarp();  // orders the lanes' stores before lane 0's fence
       uint32_t arrived = 0;
-      if (lane == 0) arrived = atomicAdd(&counters[tile], 1u);
+      if (lane == 0) {
+        __threadfence();
+        arrived = atomicAdd(&counters[tile], 1u);
+      }
       arrived = __shfl_sync(0xffffffffu, arrived, 0);
       if (arrived != static_cast<uint32_t>(slices - 1)) return true;
-      __threadfence();
+      if (lane == 0) __threadfence();
+      __syncwarp();
       float total[MH][4];
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh)
@@ -416,16 +424,16 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
     for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const int r = g + 8 * (c >> 1), m = 2 * q + (c & 1) + 8 * mh;
+        const int r = tile_row + 4 * (c >> 1), m = 2 * q + (c & 1) + 8 * mh;
         if (m < M) out[static_cast<size_t>(m) * ldo + n_off + tile * kDecodeTileRows + r] = __float2half_rn(vals[mh][c]);
       }
     return true;
   };
 
-  // Per-thread addresses inside a stage: weights of rows g / g + 8 at this warp's chunk and this
-  // thread's 16-byte column; scales of the chunk's two groups (adjacent f16) of the same rows.
-  const uint32_t w_addr0 = wring + g * kDecodeRowPitch + warp * (kDecodeChunkK / 2) + 16 * q;
-  const uint32_t s_addr0 = sring + g * srow_pitch + (sliced_scales ? 0u : static_cast<uint32_t>(k_slice0 >> 6)) + warp * 4;
+  // Per-thread addresses inside a stage: weights of this thread's two tile rows at this warp's chunk
+  // and this thread's 16-byte column; scales of the chunk's two groups (adjacent f16) of the same rows.
+  const uint32_t w_addr0 = wring + (g & 1) * half_pitch + (g >> 1) * pitch + warp * (kDecodeChunkK / 2) + 16 * q;
+  const uint32_t s_addr0 = sring + tile_row * srow_pitch + static_cast<uint32_t>(k_slice0 >> 6) + warp * 4;
   const uint32_t sum_addr0 = sums + (warp * 32 + lane) * 16 * MH;
 
   for (int j = 0; j < my_tiles && ok; ++j) {
@@ -438,10 +446,10 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
 #pragma unroll
       for (int s = 0; s < 2; ++s)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) w[s][h] = lds128(wa + 64 * s + h * 8 * kDecodeRowPitch);
+        for (int h = 0; h < 2; ++h) w[s][h] = lds128(wa + 64 * s + h * 4 * pitch);
       const uint32_t sa = s_addr0 + st * kDecodeScaleStageBytes;
       sc[0] = lds32(sa);
-      sc[1] = lds32(sa + 8 * srow_pitch);
+      sc[1] = lds32(sa + 4 * srow_pitch);
     }
     __syncwarp();  // the whole warp has read this stage
     if (lane == 0) mbar_arrive(wempty_bar(st));
@@ -458,7 +466,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[mh][c] = 0.f;
     if (has_chunk) {
-      // One step is exactly one scale group of rows g and g + 8.
+      // One step is exactly one scale group of the thread's two tile rows.
       const float2 s_g = __half22float2(as_half2(sc[0]));
       const float2 s_g8 = __half22float2(as_half2(sc[1]));
 #pragma unroll
@@ -472,8 +480,8 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
           d[mh][2] = o.x;
           d[mh][3] = o.y;
         }
-        const uint32_t wl[4] = {w[s][0].x, w[s][0].y, w[s][0].z, w[s][0].w};  // weight row g
-        const uint32_t wh[4] = {w[s][1].x, w[s][1].y, w[s][1].z, w[s][1].w};  // weight row g + 8
+        const uint32_t wl[4] = {w[s][0].x, w[s][0].y, w[s][0].z, w[s][0].w};  // fragment row g
+        const uint32_t wh[4] = {w[s][1].x, w[s][1].y, w[s][1].z, w[s][1].w};  // fragment row g + 8
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const uint32_t l8 = wl[i] >> 8, h8 = wh[i] >> 8;

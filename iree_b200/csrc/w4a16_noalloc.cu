@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -35,11 +36,17 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kScratchBytes];
 // What a kernel leaves here when one of its bounded waits ran out: [0] which wait, [1] tile, [2] N.
 static __device__ __align__(16) uint32_t g_decode_status[4];
 
+// The tensor map over the weights (used when K spans several slices) travels as a kernel parameter:
+// it is encoded on the host for every call, which needs no device memory.
+struct alignas(64) WeightMap {
+  unsigned char bytes[128];
+};
+
 template <int MH>
 __global__ void __launch_bounds__(b200::kDecodeThreads, 1)
-    decode_noalloc_kernel(const __half* a, const uint8_t* wq, const __half* scales, __half* out, void* scratch,
-                          uint32_t* status, int M, int N, int K, int ldo, int n_off) {
-  b200::decode_body<MH>(a, wq, scales, out, scratch, status, M, N, K, ldo, n_off);
+    decode_noalloc_kernel(const __grid_constant__ WeightMap wmap, const __half* a, const uint8_t* wq, const __half* scales,
+                          __half* out, void* scratch, uint32_t* status, int M, int N, int K, int ldo, int n_off) {
+  b200::decode_body<MH>(a, wq, scales, out, scratch, status, &wmap, M, N, K, ldo, n_off);
 }
 
 constexpr int kMaxDevices = 64;
@@ -130,6 +137,12 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
     e = cudaMemsetAsync(scratch, 0, b200::DecodeScratchLayout::counter_bytes(N), s);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(scratch)");
   }
+  WeightMap wmap;
+  memset(&wmap, 0, sizeof wmap);
+  if (slices > 1) {
+    const int32_t st = iree_b200_internal_encode_decode_weight_map(wq, N, K, wmap.bytes);
+    if (st != IREE_B200_STATUS_OK) return st;
+  }
   const int tiles = N / 16;
   int walkers = sms / slices;
   if (walkers < 1) walkers = 1;
@@ -137,11 +150,11 @@ extern "C" iree_b200_status_t iree_b200_w4a16_decode_noalloc(const void* a, cons
   const dim3 grid(walkers * slices, 1, 1), block(b200::kDecodeThreads, 1, 1);
   if (M <= 8) {
     decode_noalloc_kernel<1><<<grid, block, b200::decode_smem_bytes(1), s>>>(
-        static_cast<const __half*>(a), static_cast<const uint8_t*>(wq), static_cast<const __half*>(scales),
+        wmap, static_cast<const __half*>(a), static_cast<const uint8_t*>(wq), static_cast<const __half*>(scales),
         static_cast<__half*>(out), scratch, status, M, N, K, ldo, n_offset);
   } else {
     decode_noalloc_kernel<2><<<grid, block, b200::decode_smem_bytes(2), s>>>(
-        static_cast<const __half*>(a), static_cast<const uint8_t*>(wq), static_cast<const __half*>(scales),
+        wmap, static_cast<const __half*>(a), static_cast<const uint8_t*>(wq), static_cast<const __half*>(scales),
         static_cast<__half*>(out), scratch, status, M, N, K, ldo, n_offset);
   }
   e = cudaGetLastError();

@@ -17,7 +17,8 @@ from typing import Dict, List, Optional, Tuple
 
 GEMM_THREADS, GEMM_SMEM = 256, 197888
 W4_THREADS, W4_SMEM = 512, 230656  # 1024 + 224 KiB + 256
-DECODE_THREADS, DECODE_SMEM = 512, {8: 184448, 16: 217216}
+W4_WT_SMEM = 214528               # b200_w4a16_gemm_wt: 1024 + 4 x 32 KiB + 6 x 8 KiB + 2 x 16 KiB + 512
+DECODE_THREADS, DECODE_SMEM = 512, {8: 180864, 16: 213632}
 DECODE_SLICE_K = 4096           # K per CTA of the decode kernels; K beyond it is split over CTAs
 SM_COUNT = 148
 
@@ -131,7 +132,10 @@ def plan_w4a16(function: str, M: int, N: int, K: int, group: int = 128, ldo: Opt
         # bytes, one 1 KiB f32 partial tile per tile and K slice (only touched when K spans several slices)
         slices = (K + DECODE_SLICE_K - 1) // DECODE_SLICE_K
         counters = ((N // 16) * 4 + 255) // 256 * 256
-        plan.transients.append({"name": "workspace", "bytes": 512 + counters + (N // 16) * slices * 1024, "zero": True})
+        ws = {"name": "workspace", "bytes": 512 + counters + (N // 16) * slices * 1024, "zero": True}
+        if slices > 1:   # the kernel reads its weight tiles through a tensor map at the start of the workspace
+            ws["host_tensor_maps"] = {"kind": "w4a16_decode", "M": M, "N": N, "K": K}
+        plan.transients.append(ws)
         mh = 8 if M <= 8 else 16
         walkers = max(1, min(N // 16, sm_count // slices))
         plan.dispatches.append(Dispatch("b200_w4a16_decode_m%d" % mh, ["a", "wq", "scales", "out", "workspace"],

@@ -98,7 +98,10 @@ def execute_plan(ctx: rt.Context, plan: Plan, inputs, parameters=None):
 
 
 def _host_tensor_maps(ctx, spec, buffers, ws):
-    if spec["kind"] == "w4a16":
+    if spec["kind"] == "w4a16_decode":
+        p = rt.W4A16Params(spec["M"], spec["N"], spec["K"], 128, spec["N"], 0, rt.W4A16_DECODE, 0)
+        ctx.w4a16_prepare(p, buffers["a"], buffers["wq"], buffers["scales"], buffers["out"], ws)
+    elif spec["kind"] == "w4a16":
         p = rt.W4A16Params(spec["M"], spec["N"], spec["K"], 128, spec["N"], 0, rt.W4A16_GEMM, spec["tile_n"])
         ctx.w4a16_prepare(p, buffers["a"], buffers["wq"], buffers["scales"], buffers["out"], ws)
     else:

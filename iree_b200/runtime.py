@@ -45,7 +45,7 @@ class W4A16Params(C.Structure):
                 ("ldo", C.c_int32), ("n_offset", C.c_int32), ("variant", C.c_int32), ("tile_n", C.c_int32)]
 
 
-W4A16_AUTO, W4A16_DECODE, W4A16_GEMM, W4A16_GENERIC = 0, 1, 2, 3
+W4A16_AUTO, W4A16_DECODE, W4A16_GEMM, W4A16_GENERIC, W4A16_GEMM_WT = 0, 1, 2, 3, 4
 
 
 class _Binding(C.Structure):
@@ -318,6 +318,22 @@ class Context:
 
     def w4a16(self, params: W4A16Params, a, wq, scales, out, ws) -> None:
         check(library().iree_b200_w4a16(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out), _vp(ws)))
+
+    # N-sharded dispatch whose epilogue stores its column block into every rank's result
+    def w4a16_prepare_push(self, params: W4A16Params, a, wq, scales, results, flags, rank: int, ws) -> None:
+        """results / flags: one entry per rank (this rank's own buffers at index `rank`, the others as imported)."""
+        world = len(results)
+        check(library().iree_b200_w4a16_prepare_push(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales),
+                                                     self._ptr_array(results), self._ptr_array(flags), C.c_int32(world),
+                                                     C.c_int32(rank), _vp(ws)))
+
+    def w4a16_run_push(self, params: W4A16Params, scales, result, ws, world: int, rank: int, epoch: int) -> None:
+        check(library().iree_b200_w4a16_run_push(self.handle, C.byref(params), _vp(scales), _vp(result), _vp(ws),
+                                                 C.c_int32(world), C.c_int32(rank), C.c_int32(epoch)))
+
+    def w4a16_wait_arrivals(self, own_flags, ws, world: int, epoch: int) -> None:
+        check(library().iree_b200_w4a16_wait_arrivals(self.handle, _vp(own_flags), _vp(ws), C.c_int32(world),
+                                                      C.c_int32(epoch)))
 
     def w4a16_host(self, params: W4A16Params, a, wq, scales, out) -> None:
         check(library().iree_b200_w4a16_host(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out)))

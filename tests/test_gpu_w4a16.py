@@ -39,6 +39,64 @@ def test_exact_on_integer_data(ctx, variant):
         assert (got == want).all(), (variant, M, N, K, np.abs(got.astype(np.float32) - want.astype(np.float32)).max())
 
 
+def test_weights_in_tensor_memory_variant(ctx):
+    """The many-rows kernel (weights as the tensor-memory operand, results by TMA stores): exact on
+    integer data over ragged M and N, several tiles per CTA, column slices of a wider result, and
+    equal to the shared-memory-operand kernel on the same inputs."""
+    rng = np.random.default_rng(61)
+    for (M, N, K) in [(256, 128, 128), (300, 264, 256), (520, 151 * 16, 384), (1024, 384, 1024), (257, 8, 128)]:
+        a, wq, s = exact_case(rng, M, N, K)
+        got = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM_WT)
+        want = oracle.w4a16(a, wq, s, threads=THREADS)
+        assert (got == want).all(), (M, N, K, np.abs(got.astype(np.float32) - want.astype(np.float32)).max())
+    # a column slice: neighbours of the slice must survive, also next to a ragged last tile
+    M, N, K, ldo, off = 384, 200, 256, 512, 72
+    a, wq, s = exact_case(rng, M, N, K)
+    out = np.full((M, ldo), 7.0, np.float16)
+    w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM_WT, out=out, n_offset=off)
+    assert (out[:, off:off + N] == oracle.w4a16(a, wq, s, threads=THREADS)).all()
+    assert (out[:, :off] == 7.0).all() and (out[:, off + N:] == 7.0).all()
+    # real-valued data: same dequantised weights as the other tensor-core kernel, f32 accumulation
+    a, wq, s = workloads.c4_w4a16(512, N=1024, K=2048, seed=62)
+    wt = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM_WT)
+    ss = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM)
+    np.testing.assert_allclose(wt.astype(np.float32), ss.astype(np.float32), rtol=2e-3, atol=2e-3)
+    np.testing.assert_allclose(wt.astype(np.float32), oracle.w4a16(a, wq, s, threads=THREADS).astype(np.float32),
+                               rtol=RTOL, atol=ATOL)
+
+
+def test_pushing_dispatch_with_one_rank(ctx):
+    """The N-sharded form with a channel of one: the kernel stores into the (only) destination,
+    raises its arrival word, and the wait kernel sees it; a wait for a word nobody raises runs out
+    and is reported as DEADLINE_EXCEEDED with the context still usable."""
+    rng = np.random.default_rng(63)
+    M, N, K = 512, 256, 256
+    a, wq, s = exact_case(rng, M, N, K)
+    da, dw, ds = ctx.to_device(a), ctx.to_device(wq), ctx.to_device(s)
+    result, flags, ws = ctx.alloc(M * N * 2).fill(0x7E), ctx.alloc(256).fill(0), ctx.w4a16_workspace(N)
+    p = ib.W4A16Params(M, N, K, 128, N, 0, ib.W4A16_GEMM_WT, 0)
+    ctx.w4a16_prepare_push(p, da, dw, ds, [result], [flags], 0, ws)
+    want = oracle.w4a16(a, wq, s, threads=THREADS)
+    for epoch in (1, 2, 3):
+        result.fill(0x7E)
+        ctx.w4a16_run_push(p, ds, result, ws, 1, 0, epoch)
+        ctx.w4a16_wait_arrivals(flags, ws, 1, epoch)
+        ctx.workspace_status(ws)
+        assert (result.download(np.float16, (M, N)) == want).all()
+        assert flags.download(np.uint32, (1,))[0] == epoch
+    ctx.w4a16_wait_arrivals(flags, ws, 1, 9)          # nothing will ever raise the word to 9
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.workspace_status(ws)
+    assert e.value.code_name == "DEADLINE_EXCEEDED"
+    ws.fill(0)
+    ctx.w4a16_prepare_push(p, da, dw, ds, [result], [flags], 0, ws)
+    ctx.w4a16_run_push(p, ds, result, ws, 1, 0, 4)
+    ctx.w4a16_wait_arrivals(flags, ws, 1, 4)
+    ctx.workspace_status(ws)
+    for x in (da, dw, ds, result, flags, ws):
+        x.free()
+
+
 @pytest.mark.parametrize("tile_n", [16, 48, 80, 112, 128])
 def test_tensor_core_tile_widths(ctx, tile_n):
     """Every tile width the tensor-core kernel accepts (multiples of 16 up to 128), on shapes with

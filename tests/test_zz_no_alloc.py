@@ -79,8 +79,6 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(ctx):
     assert _noalloc(ctx, d, d, d, d, 1, 16, 100, 16, 0) == 3               # K not a multiple of 256
     assert _noalloc(ctx, d, d, d, d, 1, 16, 16384 + 256, 16, 0) == 3       # K above 16384
     assert _noalloc(ctx, d, d, d, d, 1, 16400, 16384, 16400, 0) == 11      # four K slices: half the columns at most
-    assert _noalloc(ctx, d, d, d, d, 1, 32768, 8192, 32768, 0) != 11       # two K slices: the full width fits
-    ctx.synchronize()
     d.free()
 
 

@@ -326,6 +326,22 @@ iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int
                                                const void* device_ptr, uint32_t dim0, uint32_t dim1, uint32_t dim2,
                                                uint32_t box0, uint32_t box1, void* out_map);
 
+/* The tensor-map templates the device-side builders start from (exports b200_encode_tensormaps and
+ * b200_encode_tensormap): one 128-byte map per kind, each fixing element type, rank, swizzle and fill
+ * mode; the builders patch address, extents, strides and box. A stock runtime never calls
+ * cuTensorMapEncodeTiled (runtime/src/iree/hal/drivers/cuda/cuda_dynamic_symbol_table.h), so the
+ * compiler plugin embeds these bytes as a constant. Writes IREE_B200_TEMPLATE_COUNT * 128 bytes. */
+enum {
+  IREE_B200_TEMPLATE_F16_SWIZZLE128_RANK3 = 0,  /* f16 operands of the tcgen05 kernels */
+  IREE_B200_TEMPLATE_BF16_SWIZZLE128_RANK3 = 1,
+  IREE_B200_TEMPLATE_U8_SWIZZLE128_RANK3 = 2,   /* i8 operands */
+  IREE_B200_TEMPLATE_U8_SWIZZLE64_RANK3 = 3,    /* raw int4 weight tiles of the W4A16 tensor-core kernels */
+  IREE_B200_TEMPLATE_F16_PLAIN_RANK2 = 4,       /* result tiles stored by b200_w4a16_gemm_wt */
+  IREE_B200_TEMPLATE_U64_PLAIN_RANK2 = 5,       /* int4 weight rows of the decode kernels when K > 4096 */
+  IREE_B200_TEMPLATE_COUNT = 6,
+};
+iree_b200_status_t iree_b200_tensormap_templates(iree_b200_context_t* context, void* out_templates);
+
 /* ---- fused int4 dequant + matmul (W4A16) -------------------------------------------------------
  * The dispatch that dispatch formation builds by cloning the dequantisation generic into its
  * consumer contraction (compiler/src/iree/compiler/Dialect/Flow/Transforms/RegionOpUtils.cpp:530-610,
@@ -353,7 +369,12 @@ typedef struct {
   int32_t variant;   /* IREE_B200_W4A16_* */
   int32_t tile_n;    /* 0 = choose (tensor-core kernel only; else a multiple of 16 up to 128) */
 } iree_b200_w4a16_params_t;
-/* Device workspace the dispatch needs for an N-column weight matrix: tensor maps, status words
+/* prepare() is what makes a workspace usable for run(): it writes the tensor maps of the tensor-core
+ * variants and, for DECODE with K > 4096, the map over the weights together with a note of which
+ * weights it describes; a DECODE dispatch on a workspace without that note (or with a note for other
+ * weights) computes nothing and iree_b200_workspace_status reports INVALID_ARGUMENT. DECODE with
+ * K <= 4096 and GENERIC need no prepare().
+ * Device workspace the dispatch needs for an N-column weight matrix: tensor maps, status words
  * and the scratch the decode kernel uses when K > 4096 (a counter per 16-row tile and an f32
  * partial tile per tile and 4096-wide K slice). It must be zero-filled once after allocation;
  * the kernels leave the counters at zero. One workspace serves one dispatch in flight. */

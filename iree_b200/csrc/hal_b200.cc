@@ -1193,10 +1193,10 @@ namespace {
 
 constexpr uint32_t kGemmThreads = 256;
 constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
-// weight ring (4 stages of 16 rows x 2048 B + 128 B), scale ring (4 x 4 KiB), 3 slots of 16 per-warp
+// weight ring (5 / 4 stages of 16 rows x 2048 B + 128 B), scale ring (4 KiB per stage), 3 slots of 16 per-warp
 // chunk sums, the per-warp offsets, barriers (decode_smem_bytes in w4a16_decode.cuh)
-constexpr uint32_t kDecodeSmemM8 = 4 * (16 * 2048 + 128) + 4 * 4096 + 3 * 16 * 32 * 16 * 1 + 16 * 1 * 2 * 32 * 8 + 128;
-constexpr uint32_t kDecodeSmemM16 = 4 * (16 * 2048 + 128) + 4 * 4096 + 3 * 16 * 32 * 16 * 2 + 16 * 2 * 2 * 32 * 8 + 128;
+constexpr uint32_t kDecodeSmemM8 = 5 * (16 * 2048 + 128) + 5 * 4096 + 3 * 16 * 32 * 16 * 1 + 16 * 1 * 2 * 32 * 8 + 256;
+constexpr uint32_t kDecodeSmemM16 = 4 * (16 * 2048 + 128) + 4 * 4096 + 3 * 16 * 32 * 16 * 2 + 16 * 2 * 2 * 32 * 8 + 256;
 // K per CTA of the decode kernels, and the scratch they need beyond one slice: a counter per 16-row
 // tile (padded to 256 bytes), then one 1 KiB partial tile per tile and slice (DecodeScratchLayout).
 constexpr int kDecodeSliceK = 4096, kDecodeMaxSlices = 4;
@@ -1232,6 +1232,7 @@ const EntryDecl kEntries[] = {
     {"b200_matmul_pair_i8_i32", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_matmul_pair_i8_requant_f16", {kGemmThreads, 1, 1}, kGemmSmemBytes},
     {"b200_encode_tensormaps", {32, 1, 1}, 0},
+    {"b200_encode_tensormap", {32, 1, 1}, 0},
     {"b200_selftest_wait_timeout", {32, 1, 1}, 0},
     {"b200_matmul_generic_f16_f16", {16, 16, 1}, 0},
     {"b200_matmul_generic_f16_f32", {16, 16, 1}, 0},
@@ -1480,6 +1481,53 @@ iree_b200_status_t iree_b200_encode_tensor_map(iree_b200_context_t* context, int
   return encode_map(dt, elem_bytes, CU_TENSOR_MAP_SWIZZLE_128B, 128, device_ptr, dim0, dim1, dim2, box0, box1, out_map);
 }
 
+iree_b200_status_t iree_b200_tensormap_templates(iree_b200_context_t* context, void* out_templates) {
+  if (!context || !out_templates) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  B200_RETURN_IF_ERROR(ensure_cuda());
+  // Any valid, 16-byte aligned device address will do for the tensor the templates describe: every
+  // field that depends on it is replaced on the device.
+  void* dummy = nullptr;
+  B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(context->device, 4096, &dummy));
+  struct FreeDummy {
+    iree_hal_b200_device_t* device;
+    void* p;
+    ~FreeDummy() { iree_hal_b200_buffer_free(device, p); }
+  } free_dummy{context->device, dummy};
+  uint8_t* out = static_cast<uint8_t*>(out_templates);
+  struct Kind {
+    CUtensorMapDataType type;
+    int elem_bytes;
+    CUtensorMapSwizzle swizzle;
+    uint32_t inner_bytes;
+    int rank;
+  };
+  const Kind kinds[IREE_B200_TEMPLATE_COUNT] = {
+      {CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, 128, 3},
+      {CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, 128, 3},
+      {CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128, 3},
+      {CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_64B, 64, 3},
+      {CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_NONE, 256, 2},
+      {CU_TENSOR_MAP_DATA_TYPE_UINT64, 8, CU_TENSOR_MAP_SWIZZLE_NONE, 2048, 2},
+  };
+  for (int i = 0; i < IREE_B200_TEMPLATE_COUNT; ++i) {
+    const Kind& k = kinds[i];
+    CUtensorMap map;
+    const cuuint32_t box0 = k.inner_bytes / k.elem_bytes;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(box0) * 4, 256, 1};
+    const cuuint64_t strides[2] = {dims[0] * k.elem_bytes, dims[0] * k.elem_bytes * 256};
+    const cuuint32_t box[3] = {box0, 8, 1};
+    const cuuint32_t estrides[3] = {1, 1, 1};
+    const CUtensorMapL2promotion promo = i == IREE_B200_TEMPLATE_F16_PLAIN_RANK2 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                                                                 : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, k.type, k.rank, dummy, dims, strides, box, estrides,
+                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, k.swizzle, promo,
+                                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                       "cuTensorMapEncodeTiled(template)");
+    memcpy(out + 128 * i, &map, 128);
+  }
+  return IREE_B200_STATUS_OK;
+}
+
 // The 512-byte workspace header of a TMA-eligible product, encoded on the host: tensor maps of
 // both operands (for the tile width `bn`), status words zero.
 static iree_b200_status_t encode_workspace_header(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
@@ -1623,7 +1671,7 @@ iree_b200_status_t iree_b200_workspace_status(iree_b200_context_t* context, cons
     uint8_t* ws = static_cast<uint8_t*>(const_cast<void*>(workspace));
     B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + IREE_B200_WORKSPACE_BYTES,
                                                    decode_counter_bytes(status[2]), 0));
-    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + 384, 128, 0));
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + 384, 64, 0));  // words 16.. keep the map's note
     B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
   }
   return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[0], status[1]);
@@ -1792,7 +1840,11 @@ static iree_b200_status_t w4_validate(const iree_b200_w4a16_params_t* p) {
 
 size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
   const int64_t n = N > 0 ? N : 0;
-  return (IREE_B200_WORKSPACE_BYTES + decode_scratch_bytes(n, kDecodeMaxSlices) + 255) & ~static_cast<size_t>(255);
+  // the decode kernels' slice-reduction scratch, and at least the output maps and arrival-word pointers
+  // that the many-rows kernel keeps behind the 512-byte header
+  size_t behind_header = decode_scratch_bytes(n, kDecodeMaxSlices);
+  if (behind_header < static_cast<size_t>(kWtMaxDestinations) * (128 + 8)) behind_header = kWtMaxDestinations * (128 + 8);
+  return (IREE_B200_WORKSPACE_BYTES + behind_header + 255) & ~static_cast<size_t>(255);
 }
 
 static int w4_choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_w4a16_params_t* p) {
@@ -1901,7 +1953,12 @@ iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const i
       return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
     uint8_t map[128];
     B200_RETURN_IF_ERROR(encode_decode_weight_map(wq, params->N, params->K, map));
-    return iree_hal_b200_transfer_h2d(context->device, map, workspace, sizeof map);
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(context->device, map, workspace, sizeof map));
+    // what the map was built for (status words 16..19): the kernel refuses a workspace without this note
+    const uint64_t address = reinterpret_cast<uint64_t>(wq);
+    const uint32_t note[4] = {static_cast<uint32_t>(address), static_cast<uint32_t>(address >> 32),
+                              static_cast<uint32_t>(params->N), static_cast<uint32_t>(params->K)};
+    return iree_hal_b200_transfer_h2d(context->device, note, static_cast<uint8_t*>(workspace) + 384 + 64, sizeof note);
   }
   if ((variant != IREE_B200_W4A16_GEMM && variant != IREE_B200_W4A16_GEMM_WT) || !params->M || !params->N)
     return IREE_B200_STATUS_OK;

@@ -108,9 +108,10 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 // shared-memory slot; one warp per tile (in rotation, two tiles behind the main loop) adds them
 // in chunk order and writes f16.
 //
-// K beyond one slice: the CTAs that hold the other slices of the same tiles leave their f32
-// partial tile in global scratch and bump the tile's counter; whoever bumps it last adds the
-// slices in slice order and writes the result, then resets the counter. Nobody waits for anybody.
+// K beyond one slice: every CTA leaves the f32 partial tiles of its slice in global scratch and,
+// when it is done, bumps the counter of its tile walker; the CTA that bumps it last adds the
+// slices of all the walker's tiles in slice order and writes the results, then resets the
+// counter. Nobody waits for anybody.
 // =============================================================================================
 constexpr int kDecodeThreads = 512;
 constexpr int kDecodeWarps = 16;
@@ -118,13 +119,16 @@ constexpr int kDecodeChunkK = 256;                           // K per warp
 constexpr int kDecodeSliceK = kDecodeWarps * kDecodeChunkK;  // K per CTA: 4096
 constexpr int kDecodeMaxSlices = 4;                          // K <= 16384
 constexpr int kDecodeTileRows = 16;                          // weight rows per tile
-constexpr int kDecodeStages = 4;                             // weight tiles resident in shared memory
+// Weight tiles resident in shared memory. What the stream needs is bytes in flight: HBM delivers
+// its peak to one CTA per SM only with about 128 KiB outstanding per SM. The 16-row variant has
+// room for four stages, the 8-row variant for five.
+__host__ __device__ constexpr int decode_stages(int mh) { return mh == 1 ? 5 : 4; }
 constexpr int kDecodeSlots = 3;                              // tiles whose chunk sums are live at the same time
 constexpr int kDecodeFinalizeLag = 2;                        // a tile is reduced this many tiles behind the main loop
 constexpr int kDecodeHalfSkew = 64;                          // bulk-copy path: the second eight rows sit this far off the first block's banks
 constexpr int kDecodeStageBytes = kDecodeTileRows * (kDecodeSliceK / 2) + 128;  // two blocks of 8 rows x <= 2048 B + skew
 constexpr int kDecodeScaleStageBytes = 16 * 128 * 2;         // 16 rows x up to 128 groups of f16
-constexpr int kDecodeBarrierBytes = 128;                     // 14 mbarriers + the abort word
+constexpr int kDecodeBarrierBytes = 256;                     // up to 16 mbarriers + the abort word
 static_assert(kDecodeSlots > kDecodeFinalizeLag, "a slot must be reduced before the main loop needs it again");
 
 // Dynamic shared memory:
@@ -134,12 +138,12 @@ static_assert(kDecodeSlots > kDecodeFinalizeLag, "a slot must be reduced before 
 //   offsets      [warp][MH][step][lane] float2  the constant part of each group sum, per output column
 //   mbarriers    weights full / empty per stage, chunk sums full / empty per slot; abort word
 __host__ __device__ constexpr int decode_smem_bytes(int mh) {
-  return kDecodeStages * kDecodeStageBytes + kDecodeStages * kDecodeScaleStageBytes +
+  return decode_stages(mh) * kDecodeStageBytes + decode_stages(mh) * kDecodeScaleStageBytes +
          kDecodeSlots * kDecodeWarps * 32 * 16 * mh + kDecodeWarps * mh * 2 * 32 * 8 + kDecodeBarrierBytes;
 }
 
 // Global scratch of a decode dispatch whose K spans more than one slice:
-//   counters [N / 16] u32 (zero between launches), padded to 256 bytes, then
+//   counters [N / 16] u32 (one per tile walker is used; zero between launches), padded to 256 bytes, then
 //   partial tiles [tile][slice][lane][2] float4 (fragment order; contents need not be initialised).
 struct DecodeScratchLayout {
   __host__ __device__ static constexpr size_t counter_bytes(int N) {
@@ -190,8 +194,10 @@ template <int MH>
 __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const uint8_t* __restrict__ wq,
                                             const __half* __restrict__ scales, __half* __restrict__ out,
                                             void* __restrict__ scratch, uint32_t* __restrict__ status,
-                                            const void* __restrict__ wmap, int M, int N, int K, int ldo, int n_off) {
+                                            const void* __restrict__ wmap, bool wmap_in_workspace, int M, int N,
+                                            int K, int ldo, int n_off) {
   extern __shared__ __align__(128) uint8_t decode_smem[];
+  constexpr int kDecodeStages = decode_stages(MH);
   constexpr int kWRingBytes = kDecodeStages * kDecodeStageBytes;
   constexpr int kSRingBytes = kDecodeStages * kDecodeScaleStageBytes;
   constexpr int kSumBytes = kDecodeSlots * kDecodeWarps * 32 * 16 * MH;
@@ -212,6 +218,18 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   const int row_bytes = K >> 1;
   const int num_tiles = N / kDecodeTileRows;
   const int slices = (K + kDecodeSliceK - 1) / kDecodeSliceK;
+  if (slices > 1 && wmap_in_workspace) {
+    // The tensor map over the weights is written into the workspace by the host (or by a map-building
+    // dispatch) together with a note of what it was built for: status words 16..19 = weights address
+    // (low, high), N, K. A map that was never written, or written for other weights, must not reach
+    // the copy engine: the whole grid refuses, reports, and leaves the result untouched.
+    const uint64_t noted = static_cast<uint64_t>(__ldcg(&status[16])) | (static_cast<uint64_t>(__ldcg(&status[17])) << 32);
+    if (noted != reinterpret_cast<uint64_t>(wq) || __ldcg(&status[18]) != static_cast<uint32_t>(N) ||
+        __ldcg(&status[19]) != static_cast<uint32_t>(K)) {
+      if (threadIdx.x == 0 && atomicCAS(&status[0], 0u, static_cast<uint32_t>(kStatusBadArgument)) == 0u) status[1] = 16;
+      return;
+    }
+  }
   // CTA c holds slice c % slices of the tiles c / slices, c / slices + walkers, ...
   const int slice = blockIdx.x % slices;
   const int walker = blockIdx.x / slices, walkers = gridDim.x / slices;
@@ -251,10 +269,10 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   // Feeding the weight ring is a side job that rotates over the warps (tile jp is fetched by warp
   // jp % 16): lanes 0 and 1 fetch the two eight-row blocks, lane 2 the scale rows.
   if (slices > 1 && threadIdx.x == 0) tensormap_fence_acquire(wmap);
-  auto produce = [&](int jp) -> bool {
-    const int st = jp % kDecodeStages;
-    if (!decode_wait(wempty_bar(st), ((jp / kDecodeStages) & 1) ^ 1, abort_flag, status, kStatusDecodeStage, jp, N))
-      return false;
+  // `st` / `empty_parity`: the stage tile jp goes into and the phase of its "empty" barrier to wait for
+  // (the main loop keeps both as running values instead of dividing).
+  auto produce = [&](int jp, int st, uint32_t empty_parity) -> bool {
+    if (!decode_wait(wempty_bar(st), empty_parity, abort_flag, status, kStatusDecodeStage, jp, N)) return false;
     const size_t row0 = static_cast<size_t>(walker + jp * walkers) * kDecodeTileRows;
     // a TMA box always delivers its full 8 x 2048 bytes (columns past the row's end arrive as zeros)
     if (lane == 0) mbar_arrive_expect_tx(wfull_bar(st), 2 * half_bytes + scale_tile_bytes);
@@ -272,7 +290,7 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   };
   bool ok = true;
   for (int jp = 0; jp < kDecodeStages && jp < my_tiles; ++jp)
-    if (warp == jp) ok = produce(jp) && ok;
+    if (warp == jp) ok = produce(jp, jp, 1u) && ok;
 
   // ---- activations of this warp's chunk, kept in registers in the order the MMAs want ---------------
   // A weight word holds the eight k = k0 .. k0 + 7, k0 = kc + 128 s + 32 q + 8 i for step s, thread
@@ -345,11 +363,9 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   // frees the slot and writes the 16 x M results (one slice) or hands the partial tile to the
   // slice reduction. One warp per tile, in rotation.
   // Fragment order: vals[mh][c] is tile row tile_row + 4 (c / 2), activation row 2 q + (c & 1) + 8 mh.
-  auto finalize = [&](int jf) -> bool {
-    const int slot = jf % kDecodeSlots;
+  auto finalize = [&](int jf, int slot, uint32_t full_parity) -> bool {
     const int tile = walker + jf * walkers;
-    if (!decode_wait(pfull_bar(slot), (jf / kDecodeSlots) & 1, abort_flag, status, kStatusDecodeSlotFull, jf, N))
-      return false;
+    if (!decode_wait(pfull_bar(slot), full_parity, abort_flag, status, kStatusDecodeSlotFull, jf, N)) return false;
     float vals[MH][4];
 #pragma unroll
     for (int mh = 0; mh < MH; ++mh)
@@ -379,46 +395,15 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
     __syncwarp();
     if (lane == 0) mbar_arrive(pempty_bar(slot));  // hand the slot to tile jf + kDecodeSlots
     if (slices > 1) {
-      // Leave this slice's partial tile in global memory, then count. The fence before the count
-      // makes the partial visible to whoever counts later; the last one to count reads the others
-      // past the L1 and adds all slices in slice order, its own from registers.
-      uint32_t* counters = reinterpret_cast<uint32_t*>(scratch);
+      // Several K slices: this CTA's partial tile goes to global memory; the slices meet once, when
+      // the CTAs are done (below). No fence and no counting here: a fence under a saturated memory
+      // system stalls the warp for microseconds, and every other warp of the CTA soon waits for it.
       float4* parts = reinterpret_cast<float4*>(static_cast<uint8_t*>(scratch) + DecodeScratchLayout::counter_bytes(N)) +
-                      (static_cast<size_t>(tile) * slices) * 64 + lane * 2;
+                      (static_cast<size_t>(tile) * slices + slice) * 64 + lane * 2;
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh)
-        __stcg(parts + slice * 64 + mh, make_float4(vals[mh][0], vals[mh][1], vals[mh][2], vals[mh][3]));
-      __syncwarp();  // orders the lanes' stores before lane 0's fence
-      uint32_t arrived = 0;
-      if (lane == 0) {
-        __threadfence();
-        arrived = atomicAdd(&counters[tile], 1u);
-      }
-      arrived = __shfl_sync(0xffffffffu, arrived, 0);
-      if (arrived != static_cast<uint32_t>(slices - 1)) return true;
-      if (lane == 0) __threadfence();
-      __syncwarp();
-      float total[MH][4];
-#pragma unroll
-      for (int mh = 0; mh < MH; ++mh)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) total[mh][c] = 0.f;
-      for (int sl = 0; sl < slices; ++sl) {
-#pragma unroll
-        for (int mh = 0; mh < MH; ++mh) {
-          float4 v = make_float4(vals[mh][0], vals[mh][1], vals[mh][2], vals[mh][3]);
-          if (sl != slice) v = __ldcg(parts + sl * 64 + mh);
-          total[mh][0] += v.x;
-          total[mh][1] += v.y;
-          total[mh][2] += v.z;
-          total[mh][3] += v.w;
-        }
-      }
-#pragma unroll
-      for (int mh = 0; mh < MH; ++mh)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) vals[mh][c] = total[mh][c];
-      if (lane == 0) counters[tile] = 0;  // clean for the next launch
+        __stcg(parts + mh, make_float4(vals[mh][0], vals[mh][1], vals[mh][2], vals[mh][3]));
+      return true;
     }
 #pragma unroll
     for (int mh = 0; mh < MH; ++mh)
@@ -436,30 +421,24 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
   const uint32_t s_addr0 = sring + tile_row * srow_pitch + static_cast<uint32_t>(k_slice0 >> 6) + warp * 4;
   const uint32_t sum_addr0 = sums + (warp * 32 + lane) * 16 * MH;
 
+  // Running ring positions (stage / slot index, phase bit, addresses) instead of divisions per tile.
+  int st = 0, slot = 0, fslot = 0;       // stage of tile j, chunk-sum slot of tile j, slot of the tile to finalise
+  uint32_t wph = 0, sph = 0, fph = 0;    // phase bits of the same
+  uint32_t wa = w_addr0, sa = s_addr0, cell = sum_addr0;
   for (int j = 0; j < my_tiles && ok; ++j) {
-    const int st = j % kDecodeStages;
-    if (!decode_wait(wfull_bar(st), (j / kDecodeStages) & 1, abort_flag, status, kStatusDecodeWeights, j, N)) break;
+    if (!decode_wait(wfull_bar(st), wph, abort_flag, status, kStatusDecodeWeights, j, N)) break;
     uint4 w[2][2];
     uint32_t sc[2] = {0, 0};
     if (has_chunk) {
-      const uint32_t wa = w_addr0 + st * kDecodeStageBytes;
 #pragma unroll
       for (int s = 0; s < 2; ++s)
 #pragma unroll
         for (int h = 0; h < 2; ++h) w[s][h] = lds128(wa + 64 * s + h * 4 * pitch);
-      const uint32_t sa = s_addr0 + st * kDecodeScaleStageBytes;
       sc[0] = lds32(sa);
       sc[1] = lds32(sa + 4 * srow_pitch);
     }
     __syncwarp();  // the whole warp has read this stage
     if (lane == 0) mbar_arrive(wempty_bar(st));
-    // Refill: the stage that tile j - 1 used is free once every warp has read it, which is
-    // almost always already the case here.
-    {
-      const int jp = j + kDecodeStages - 1;
-      if (j >= 1 && jp < my_tiles && warp == jp % kDecodeWarps && !produce(jp)) break;
-    }
-
     float acc[MH][4];
 #pragma unroll
     for (int mh = 0; mh < MH; ++mh)
@@ -512,20 +491,90 @@ __device__ __forceinline__ void decode_body(const __half* __restrict__ a, const 
 
     // ---- leave this K chunk's sums in the tile's slot ----------------------------------------------
     {
-      const int slot = j % kDecodeSlots;
-      if (!decode_wait(pempty_bar(slot), ((j / kDecodeSlots) & 1) ^ 1, abort_flag, status, kStatusDecodeSlotFree, j, N)) break;
-      const uint32_t cell = sum_addr0 + slot * (kDecodeWarps * 32 * 16 * MH);
+      if (!decode_wait(pempty_bar(slot), sph ^ 1u, abort_flag, status, kStatusDecodeSlotFree, j, N)) break;
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh) sts128f(cell + mh * 16, acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
       __syncwarp();
       if (lane == 0) mbar_arrive(pfull_bar(slot));
     }
+    // Refill of the stage this tile came from: it is free once every warp has read it, which by now
+    // is almost always the case. Asking here, rather than when the next tile lands, keeps one more
+    // tile in flight (the stream needs bytes in flight more than anything else).
+    {
+      const int jp = j + kDecodeStages;  // same stage; its "empty" phase to wait for is this tile's phase
+      if (jp < my_tiles && warp == (jp & (kDecodeWarps - 1)) && !produce(jp, st, wph)) break;
+    }
     // Tile j - 2 is finished off by warp (j - 2) % 16: by now every chunk has arrived, so the wait
     // is short, and no warp needs another warp's answer on its critical path.
-    if (j >= kDecodeFinalizeLag && warp == (j - kDecodeFinalizeLag) % kDecodeWarps) ok = finalize(j - kDecodeFinalizeLag);
+    if (j >= kDecodeFinalizeLag) {
+      if (warp == ((j - kDecodeFinalizeLag) & (kDecodeWarps - 1))) ok = finalize(j - kDecodeFinalizeLag, fslot, fph);
+      if (++fslot == kDecodeSlots) fslot = 0, fph ^= 1u;
+    }
+    if (++st == kDecodeStages) {
+      st = 0, wph ^= 1u, wa = w_addr0, sa = s_addr0;
+    } else {
+      wa += kDecodeStageBytes, sa += kDecodeScaleStageBytes;
+    }
+    if (++slot == kDecodeSlots) {
+      slot = 0, sph ^= 1u, cell = sum_addr0;
+    } else {
+      cell += kDecodeWarps * 32 * 16 * MH;
+    }
   }
-  for (int jf = my_tiles > kDecodeFinalizeLag ? my_tiles - kDecodeFinalizeLag : 0; jf < my_tiles; ++jf)
-    if (warp == jf % kDecodeWarps && ok && !*abort_flag) ok = finalize(jf);
+  for (int jf = my_tiles > kDecodeFinalizeLag ? my_tiles - kDecodeFinalizeLag : 0; jf < my_tiles; ++jf) {
+    if (warp == (jf & (kDecodeWarps - 1)) && ok && !*abort_flag) ok = finalize(jf, fslot, fph);
+    if (++fslot == kDecodeSlots) fslot = 0, fph ^= 1u;
+  }
+
+  if (slices > 1) {
+    // The slices of a walker's tiles meet here, once per CTA: everybody's partial tiles are issued
+    // (barrier), one thread publishes them (fence) and counts; the CTA that counts last reads all
+    // slices of every tile past the L1, adds them in slice order and writes the results.
+    __syncthreads();
+    volatile uint32_t* last_flag = abort_flag + 1;
+    if (threadIdx.x == 0) {
+      uint32_t* counters = reinterpret_cast<uint32_t*>(scratch);
+      uint32_t is_last = 0;
+      if (!*abort_flag && my_tiles > 0) {
+        __threadfence();
+        is_last = atomicAdd(&counters[walker], 1u) == static_cast<uint32_t>(slices - 1);
+        if (is_last) {
+          __threadfence();
+          counters[walker] = 0;  // clean for the next launch
+        }
+      }
+      *last_flag = is_last;
+    }
+    __syncthreads();
+    if (*last_flag) {
+      const float4* all = reinterpret_cast<const float4*>(static_cast<const uint8_t*>(scratch) + DecodeScratchLayout::counter_bytes(N));
+      for (int jf = warp; jf < my_tiles; jf += kDecodeWarps) {
+        const int tile = walker + jf * walkers;
+        float total[MH][4];
+#pragma unroll
+        for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) total[mh][c] = 0.f;
+        for (int sl = 0; sl < slices; ++sl) {
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh) {
+            const float4 v = __ldcg(all + (static_cast<size_t>(tile) * slices + sl) * 64 + lane * 2 + mh);
+            total[mh][0] += v.x;
+            total[mh][1] += v.y;
+            total[mh][2] += v.z;
+            total[mh][3] += v.w;
+          }
+        }
+#pragma unroll
+        for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int r = tile_row + 4 * (c >> 1), m = 2 * q + (c & 1) + 8 * mh;
+            if (m < M) out[static_cast<size_t>(m) * ldo + n_off + tile * kDecodeTileRows + r] = __float2half_rn(total[mh][c]);
+          }
+      }
+    }
+  }
 
   // Teardown: everyone meets here, also after a wait ran out. Bulk copies may then still be
   // landing in shared memory, so they get a bounded grace period before the CTA exits.

@@ -46,7 +46,7 @@ template <int MH>
 __global__ void __launch_bounds__(b200::kDecodeThreads, 1)
     decode_noalloc_kernel(const __grid_constant__ WeightMap wmap, const __half* a, const uint8_t* wq, const __half* scales,
                           __half* out, void* scratch, uint32_t* status, int M, int N, int K, int ldo, int n_off) {
-  b200::decode_body<MH>(a, wq, scales, out, scratch, status, &wmap, M, N, K, ldo, n_off);
+  b200::decode_body<MH>(a, wq, scales, out, scratch, status, &wmap, false, M, N, K, ldo, n_off);
 }
 
 constexpr int kMaxDevices = 64;

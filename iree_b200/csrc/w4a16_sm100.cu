@@ -386,17 +386,17 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
 using namespace b200;
 
 // Binding 4 is the dispatch's workspace: the tensor map over the weights (needed when K spans more
-// than one 4096-wide slice) at byte 0, status words at byte 384, the slice-reduction scratch
-// (DecodeScratchLayout) from byte 512 on.
+// than one 4096-wide slice) at byte 0, status words at byte 384 (words 16..19 note which weights,
+// N and K the map was built for), the slice-reduction scratch (DecodeScratchLayout) from byte 512 on.
 extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
     b200_w4a16_decode_m8(const __half* a, const uint8_t* wq, const __half* scales, __half* out, uint8_t* ws, int M,
                          int N, int K, int ldo, int n_off) {
-  decode_body<1>(a, wq, scales, out, ws + 512, reinterpret_cast<uint32_t*>(ws + 384), ws, M, N, K, ldo, n_off);
+  decode_body<1>(a, wq, scales, out, ws + 512, reinterpret_cast<uint32_t*>(ws + 384), ws, true, M, N, K, ldo, n_off);
 }
 extern "C" __global__ void __launch_bounds__(kDecodeThreads, 1)
     b200_w4a16_decode_m16(const __half* a, const uint8_t* wq, const __half* scales, __half* out, uint8_t* ws, int M,
                           int N, int K, int ldo, int n_off) {
-  decode_body<2>(a, wq, scales, out, ws + 512, reinterpret_cast<uint32_t*>(ws + 384), ws, M, N, K, ldo, n_off);
+  decode_body<2>(a, wq, scales, out, ws + 512, reinterpret_cast<uint32_t*>(ws + 384), ws, true, M, N, K, ldo, n_off);
 }
 
 extern "C" __global__ void __launch_bounds__(kW4Threads, 1)

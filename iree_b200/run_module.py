@@ -53,6 +53,9 @@ def execute_plan(ctx: rt.Context, plan: Plan, inputs, parameters=None):
         raise rt.IreeB200Error(3, "function expects %d inputs, %d given" % (len(free_inputs), len(inputs)))
     buffers, owned = {}, []
     for decl, arr in zip(free_inputs, inputs):
+        if list(arr.shape) != list(decl["shape"]) and int(np.prod(arr.shape)) == int(np.prod(decl["shape"])) and \
+                arr.shape[0] == decl["shape"][0]:
+            arr = arr.reshape(decl["shape"])       # a reshape of the trailing dimensions: [M, G, 128] for [M, K]
         if list(arr.shape) != list(decl["shape"]):
             raise rt.IreeB200Error(3, "input %s: expected shape %s, got %s" % (decl["name"], decl["shape"], list(arr.shape)))
         buffers[decl["name"]] = ctx.to_device(arr)
@@ -77,7 +80,12 @@ def execute_plan(ctx: rt.Context, plan: Plan, inputs, parameters=None):
         buf = ctx.alloc(t["bytes"])
         if t.get("zero"):
             buf.fill(0)
-        if t.get("templates"):
+        if t.get("templates") == "table":      # every template kind, as the compiler plugin embeds them
+            import ctypes as C
+            host = C.create_string_buffer(768)
+            rt.check(rt.library().iree_b200_tensormap_templates(ctx.handle, host))
+            buf.upload(np.frombuffer(host.raw, np.uint8))
+        elif t.get("templates"):
             kind = t["templates"]
             es = 1 if kind == "i8" else 2
             host = b"".join(ctx.encode_tensor_map(es, kind == "bf16", buf, 128 // es * 4, 256, 1, 128 // es, 64)
@@ -101,13 +109,17 @@ def _host_tensor_maps(ctx, spec, buffers, ws):
     if spec["kind"] == "w4a16_decode":
         p = rt.W4A16Params(spec["M"], spec["N"], spec["K"], 128, spec["N"], 0, rt.W4A16_DECODE, 0)
         ctx.w4a16_prepare(p, buffers["a"], buffers["wq"], buffers["scales"], buffers["out"], ws)
+    elif spec["kind"] == "w4a16_wt":
+        p = rt.W4A16Params(spec["M"], spec["N"], spec["K"], 128, spec["ldo"], spec["n_offset"], rt.W4A16_GEMM_WT, 0)
+        ctx.w4a16_prepare(p, buffers["a"], buffers["wq"], buffers["scales"], buffers["out"], ws)
     elif spec["kind"] == "w4a16":
         p = rt.W4A16Params(spec["M"], spec["N"], spec["K"], 128, spec["N"], 0, rt.W4A16_GEMM, spec["tile_n"])
         ctx.w4a16_prepare(p, buffers["a"], buffers["wq"], buffers["scales"], buffers["out"], ws)
     else:
         kind = {"f16": rt.KIND_F16, "bf16": rt.KIND_BF16, "i8": rt.KIND_I8}[spec["kind"]]
-        p = rt.MatmulParams(kind, rt.EPILOGUE_ACCUMULATOR if kind == rt.KIND_I8 else rt.EPILOGUE_CAST, spec["M"],
-                            spec["N"], spec["K"], spec["batch"], spec["layout"], spec["tile_n"], 0)
+        epilogue = {"cast": rt.EPILOGUE_CAST, "acc": rt.EPILOGUE_ACCUMULATOR, "requant": rt.EPILOGUE_REQUANT_F16}[
+            spec.get("epilogue", "acc" if kind == rt.KIND_I8 else "cast")]
+        p = rt.MatmulParams(kind, epilogue, spec["M"], spec["N"], spec["K"], spec["batch"], spec["layout"], spec["tile_n"], 0)
         ctx.matmul_prepare(p, buffers["lhs"], buffers["rhs"], ws)
 
 

@@ -209,9 +209,42 @@ def test_decode_slice_reduction_leaves_its_counters_clean(ctx):
             ctx.workspace_status(ws)
             assert (dc.download(np.float16, (M, N)) == want).all(), (M, N, K)
         counters = ((N // 16) * 4 + 255) // 256 * 256
-        assert not ws.download(np.uint8, (512 + counters,))[384:].any()
+        raw = ws.download(np.uint8, (512 + counters,))
+        assert not raw[384:448].any() and not raw[512:].any()     # status words 0..15 and the counters
+        note = raw[448:464].view(np.uint32)                       # words 16..19: which weights the map describes
+        assert (int(note[0]) | (int(note[1]) << 32), int(note[2]), int(note[3])) == (dw.ptr, N, K)
         for x in (da, dw, ds, dc, ws):
             x.free()
+
+
+def test_decode_refuses_a_workspace_that_was_not_prepared(ctx):
+    """K > 4096: the kernel fetches its weight tiles through a tensor map that prepare() leaves in the
+    workspace. Running on a workspace that was never prepared, or that was prepared for other
+    weights, must not reach the copy engine: nothing is computed and the status says so."""
+    rng = np.random.default_rng(25)
+    M, N, K = 4, 64, 8192
+    a, wq, s = exact_case(rng, M, N, K)
+    da, dw, ds, dw2 = ctx.to_device(a), ctx.to_device(wq), ctx.to_device(s), ctx.to_device(wq)
+    dc, ws = ctx.alloc(M * N * 2).fill(0x7E), ctx.w4a16_workspace(N)
+    p = ib.W4A16Params(M, N, K, 128, N, 0, ib.W4A16_DECODE, 0)
+    ctx.w4a16_run(p, da, dw, ds, dc, ws, ib.W4A16_DECODE, 0)          # never prepared
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.workspace_status(ws)
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    assert (dc.download(np.uint8, (M * N * 2,)) == 0x7E).all()
+    ws.fill(0)
+    ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
+    ctx.w4a16_run(p, da, dw2, ds, dc, ws, ib.W4A16_DECODE, 0)         # prepared, but for the other copy of the weights
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.workspace_status(ws)
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    ws.fill(0)
+    ctx.w4a16_prepare(p, da, dw2, ds, dc, ws)
+    ctx.w4a16_run(p, da, dw2, ds, dc, ws, ib.W4A16_DECODE, 0)
+    ctx.workspace_status(ws)
+    assert (dc.download(np.float16, (M, N)) == oracle.w4a16(a, wq, s)).all()
+    for x in (da, dw, ds, dw2, dc, ws):
+        x.free()
 
 
 def test_decode_refuses_misaligned_operands(ctx):

@@ -360,6 +360,10 @@ enum {
   IREE_B200_W4A16_GEMM_WT = 4, /* GEMM's preconditions, M >= 256, result base and pitch on 16-byte boundaries,
                                   n_offset % 8 == 0: tcgen05 with the dequantised weights as the tensor-memory
                                   operand, results leave through TMA stores */
+  IREE_B200_W4A16_DECODE_TC = 5, /* M <= 16, K % 256 == 0, group 128, `a` and `wq` on 16-byte and `scales` on
+                                  4-byte boundaries: weight streaming through the tensor cores (weights
+                                  expanded into tensor memory, work dealt to the SMs in equal ranges of
+                                  128-row x 256-K units); needs prepare() */
 };
 typedef struct {
   int32_t M, N, K;

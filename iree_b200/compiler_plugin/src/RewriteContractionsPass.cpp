@@ -49,7 +49,7 @@ namespace HAL = IREE::HAL;
 #include "TensorMapTemplates.inc"
 
 constexpr int64_t kGemmThreads = 256, kGemmSmem = 197888;
-constexpr int64_t kW4GemmThreads = 512, kW4GemmSmem = 230656, kW4WtSmem = 214528;
+constexpr int64_t kW4GemmThreads = 512, kW4GemmSmem = 230656, kW4WtThreads = 512, kW4WtSmem = 214528;
 constexpr int64_t kDecodeThreads = 512, kDecodeSmemM8 = 217984, kDecodeSmemM16 = 213760;
 constexpr int64_t kDecodeSliceK = 4096;
 // indices into the template table (IREE_B200_TEMPLATE_* of the runtime library's header)
@@ -464,7 +464,7 @@ class RewriteContractionsPass : public PassWrapper<RewriteContractionsPass, Oper
       SmallVector<Value> operands = {m.scales, result, ws};
       for (int64_t v : {M, N, K, ldo, nOff, int64_t((1 << 8) | 0), int64_t(0)}) operands.push_back(i32(b, loc, v));
       Operation *ext = emit(b, loc, "b200_w4a16_gemm_wt", {idx(b, loc, tiles)}, operands, {outType}, 1, 7,
-                            {std::min<int64_t>(tiles, sms), 1, 1}, {kW4GemmThreads, 1, 1}, kW4WtSmem);
+                            {std::min<int64_t>(tiles, sms), 1, 1}, {kW4WtThreads, 1, 1}, kW4WtSmem);
       ext->setAttr("tied_operands", b.getIndexArrayAttr({1}));  // writes the tensor the output map was built over
       ext->setAttr("b200.binding_order", b.getStrArrayAttr({"scales", "out", "workspace"}));
       m.last->getResult(0).replaceAllUsesWith(ext->getResult(0));

@@ -20,6 +20,7 @@
 
 #include "../../include/iree_b200.h"
 #include "hal_b200_internal.h"
+#include "w4a16_decode_tc.h"
 
 namespace {
 
@@ -1242,6 +1243,7 @@ const EntryDecl kEntries[] = {
     {"b200_matmul_generic_i8_requant_f16", {16, 16, 1}, 0},
     {"b200_w4a16_decode_m8", {512, 1, 1}, kDecodeSmemM8},
     {"b200_w4a16_decode_m16", {512, 1, 1}, kDecodeSmemM16},
+    {"b200_w4a16_decode_tc", {b200::kTcThreads, 1, 1}, b200::kTcSmemBytes},
     {"b200_w4a16_gemm", {512, 1, 1}, kW4SmemBytes},
     {"b200_w4a16_gemm_wt", {512, 1, 1}, kW4WtSmemBytes},
     {"b200_wait_arrivals", {32, 1, 1}, 0},
@@ -1450,7 +1452,7 @@ iree_hal_b200_command_buffer_t* iree_b200_context_command_buffer(iree_b200_conte
 // Rank-3 row-major tensor [dim2, dim1, dim0]; the box is box0 x box1 x 1 elements.
 static iree_b200_status_t encode_map(CUtensorMapDataType dt, int elem_bytes, CUtensorMapSwizzle swizzle,
                                      uint32_t swizzle_bytes, const void* device_ptr, uint32_t dim0, uint32_t dim1,
-                                     uint32_t dim2, uint32_t box0, uint32_t box1, void* out_map) {
+                                     uint32_t dim2, uint32_t box0, uint32_t box1, void* out_map, uint32_t box2 = 1) {
   B200_RETURN_IF_ERROR(ensure_cuda());
   if (box0 * elem_bytes != swizzle_bytes || box1 == 0 || box1 > 256)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "box must be %u bytes wide and 1..256 rows", swizzle_bytes);
@@ -1460,7 +1462,7 @@ static iree_b200_status_t encode_map(CUtensorMapDataType dt, int elem_bytes, CUt
   const cuuint64_t dims[3] = {dim0, dim1, dim2};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(dim0) * elem_bytes,
                                  static_cast<cuuint64_t>(dim0) * dim1 * elem_bytes};
-  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t box[3] = {box0, box1, box2};
   const cuuint32_t estrides[3] = {1, 1, 1};
   CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, dt, 3, const_cast<void*>(device_ptr), dims, strides, box,
                                                  estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
@@ -1659,12 +1661,22 @@ iree_b200_status_t iree_b200_matmul(iree_b200_context_t* context, const iree_b20
 
 iree_b200_status_t iree_b200_workspace_status(iree_b200_context_t* context, const void* workspace) {
   if (!context || !workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
-  uint32_t status[3] = {0, 0, 0};
+  uint32_t status[19] = {0};
   B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(context->device, static_cast<const uint8_t*>(workspace) + 384,
                                                   status, sizeof status));
   B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
   if (status[0] == 0) return IREE_B200_STATUS_OK;
   if (status[0] == 5) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "kernel rejected its arguments (shape / alignment)");
+  if (status[16] == b200::kTcNoteMagic) {
+    // A tensor-core decode dispatch that gave up may have left tile counters behind (status word 17
+    // is its N): clear them and the status words, so the workspace is usable again.
+    uint8_t* ws = static_cast<uint8_t*>(const_cast<void*>(workspace));
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + b200::kTcCountersOffset,
+                                                   b200::tc_partials_offset(status[17]) - b200::kTcCountersOffset, 0));
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, ws + 384, 64, 0));
+    B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
+    return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[0], status[1]);
+  }
   if (status[0] >= 16 && status[2] > 0) {
     // A decode dispatch that gave up may have left tile counters of its slice reduction behind
     // (status word 2 is its N): clear them and the status words, so the workspace is usable again.
@@ -1844,6 +1856,9 @@ size_t iree_b200_w4a16_workspace_bytes(int32_t N) {
   // that the many-rows kernel keeps behind the 512-byte header
   size_t behind_header = decode_scratch_bytes(n, kDecodeMaxSlices);
   if (behind_header < static_cast<size_t>(kWtMaxDestinations) * (128 + 8)) behind_header = kWtMaxDestinations * (128 + 8);
+  // the tensor-core decode kernel: tile counters and two partial sums per CTA
+  if (behind_header < b200::tc_workspace_bytes(n) - IREE_B200_WORKSPACE_BYTES)
+    behind_header = b200::tc_workspace_bytes(n) - IREE_B200_WORKSPACE_BYTES;
   return (IREE_B200_WORKSPACE_BYTES + behind_header + 255) & ~static_cast<size_t>(255);
 }
 
@@ -1939,6 +1954,18 @@ static iree_b200_status_t w4_prepare_wt(iree_b200_context_t* context, const iree
   return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
 }
 
+static iree_b200_status_t w4_check_decode_tc(const iree_b200_w4a16_params_t* params, const void* a, const void* wq,
+                                             const void* scales) {
+  if (params->group_size != 128 || params->M > b200::kTcARows || params->K % 256)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the tensor-core decode kernel needs M <= 16, K %% 256 == 0, group 128");
+  // TMA over activations and weights (16-byte bases and pitches), 4-byte copies of scale pairs
+  if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(wq) % 16) ||
+      (reinterpret_cast<uintptr_t>(scales) % 4))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT,
+                "the tensor-core decode kernel needs activations and weights on 16-byte, scales on 4-byte boundaries");
+  return IREE_B200_STATUS_OK;
+}
+
 iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                            const void* a, const void* wq, const void* scales, const void* out,
                                            void* workspace, int32_t* out_variant, int32_t* out_tile_n) {
@@ -1959,6 +1986,23 @@ iree_b200_status_t iree_b200_w4a16_prepare(iree_b200_context_t* context, const i
     const uint32_t note[4] = {static_cast<uint32_t>(address), static_cast<uint32_t>(address >> 32),
                               static_cast<uint32_t>(params->N), static_cast<uint32_t>(params->K)};
     return iree_hal_b200_transfer_h2d(context->device, note, static_cast<uint8_t*>(workspace) + 384 + 64, sizeof note);
+  }
+  if (variant == IREE_B200_W4A16_DECODE_TC && params->M && params->N) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 128))
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace must be a 128-byte aligned device buffer");
+    B200_RETURN_IF_ERROR(w4_check_decode_tc(params, a, wq, scales));
+    // header: maps over the activations (boxes of 64 K x 16 rows) and the weights (seen as [N][K / 256][128
+    // bytes], boxes of 128 rows x 2 x 128 bytes), status words with the note the kernel checks; behind it
+    // the tile counters, zeroed
+    std::vector<uint8_t> host(b200::tc_partials_offset(params->N), 0);
+    B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, 128, a, params->K,
+                                    params->M, 1, 64, b200::kTcARows, host.data()));
+    B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_128B, 128, wq, 128,
+                                    params->K / 256, params->N, 128, b200::kTcUnitK / 256, host.data() + 128,
+                                    b200::kTcWRows));
+    const uint32_t note[3] = {b200::kTcNoteMagic, static_cast<uint32_t>(params->N), static_cast<uint32_t>(params->K)};
+    memcpy(host.data() + 384 + 64, note, sizeof note);
+    return iree_hal_b200_transfer_h2d(context->device, host.data(), workspace, host.size());
   }
   if ((variant != IREE_B200_W4A16_GEMM && variant != IREE_B200_W4A16_GEMM_WT) || !params->M || !params->N)
     return IREE_B200_STATUS_OK;
@@ -2084,6 +2128,25 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     const bool saved_overlap = cb->overlap;  // what the caller set on the command buffer itself survives
     cb->overlap = saved_overlap || context->dispatch_overlap;
     const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 5, 5, gx, 1, 1);
+    cb->overlap = saved_overlap;
+    return st;
+  }
+  if (variant == IREE_B200_W4A16_DECODE_TC) {
+    B200_RETURN_IF_ERROR(w4_check_decode_tc(params, a, wq, scales));
+    if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
+    iree_hal_b200_descriptor_set_binding_t bindings[3] = {{0, const_cast<void*>(scales)}, {1, out}, {2, workspace}};
+    const int32_t constants[5] = {params->M, params->N, params->K, params->ldo, params->n_offset};
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 3, bindings));
+    B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+    const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_decode_tc");
+    // equal contiguous ranges of (128 rows x 512 K) units, one CTA per SM
+    const int64_t units = static_cast<int64_t>((params->N + b200::kTcWRows - 1) / b200::kTcWRows) *
+                          ((params->K + b200::kTcUnitK - 1) / b200::kTcUnitK);
+    int64_t gx = sms < b200::kTcMaxCtas ? sms : b200::kTcMaxCtas;
+    if (gx > units) gx = units;
+    const bool saved_overlap = cb->overlap;
+    cb->overlap = saved_overlap || context->dispatch_overlap;
+    const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 3, 5, static_cast<uint32_t>(gx), 1, 1);
     cb->overlap = saved_overlap;
     return st;
   }

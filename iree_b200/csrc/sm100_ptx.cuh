@@ -170,6 +170,10 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base_lane + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  // .sync.aligned: every lane must execute it together. Lanes that polled a barrier leave their
+  // loops one by one and a vote does not bring them back into step; without this the instruction
+  // has been seen to drop single lanes' data.
+  __syncwarp();
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -185,6 +189,7 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 // 32 lanes x 32 consecutive 32-bit columns, registers -> tensor memory: thread t of the warp writes
 // lane (base_lane + t). A warp reaches only the 32 lanes of its own quarter (warp index % 4).
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+  __syncwarp();  // see tmem_ld_32x32
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "

@@ -15,8 +15,10 @@
 //
 //   warp 0      TMA producer of the activation tiles: 256 rows x 64 K per stage (two 128-row boxes)
 //   warp 3      TMA producer of the raw int4 tiles: 128 rows x 128 K (one scale group) per stage
-//   warps 8-15  dequant, two groups of four alternating K blocks: 32 raw bytes of the thread's row
-//               -> 32 registers of f16 pairs -> tcgen05.st into one of eight 32-column A stages
+//   warps 8-15  dequant, two groups of four taking K blocks in turn (a third group changed
+//               nothing: the groups are not what the tensor pipe waits for): 32 raw bytes of the
+//               thread's row -> 32 registers of f16 pairs -> tcgen05.st into one of eight 32-column
+//               A stages
 //   warp 1      one thread issues tcgen05.mma (A from TMEM, B from shared memory, M = 128, N = 256)
 //   warp 2      owns the TMEM allocation: 256 accumulator columns + 8 x 32 columns of A stages
 //   warps 4-7   epilogue: tcgen05.ld -> f16 -> transposed into a shared-memory staging tile of
@@ -48,7 +50,8 @@ constexpr int kWtAStages = 8;                             // expanded-weight sta
 constexpr int kWtAStageColumns = 32;                      // 64 K as f16 pairs
 constexpr int kWtOutRows = 64;                            // result rows per staged piece
 constexpr int kWtOutStageBytes = kWtOutRows * kWtWRows * 2;  // 16 KiB
-constexpr int kWtThreads = 512;
+constexpr int kWtDequantGroups = 2;
+constexpr int kWtThreads = 256 + kWtDequantGroups * 128;
 constexpr int kWtMaxDestinations = 8;
 constexpr int kWtBarrierBytes = 512;
 constexpr int kWtSmemBytes = 1024 + kWtActStages * kWtActStageBytes + kWtRawStages * kWtRawStageBytes +
@@ -80,9 +83,9 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   const uint32_t out_base = raw_base + kWtRawStages * kWtRawStageBytes;
   const uint32_t bars = out_base + 2 * kWtOutStageBytes;
   uint8_t* bars_gen = smem_gen + (bars - smem_base);
-  // barriers: act full / empty, raw full / empty, A-stage full / empty, accumulator full / empty
+  // barriers: act full (the slots after them are unused: an activation stage comes back through the
+  // A-stage barrier of the K block that held it), raw full / empty, A-stage full / empty, accumulator full / empty
   auto act_full = [&](int i) { return bars + 8u * i; };
-  auto act_empty = [&](int i) { return bars + 8u * (kWtActStages + i); };
   auto raw_full = [&](int i) { return bars + 8u * (2 * kWtActStages + i); };
   auto raw_empty = [&](int i) { return bars + 8u * (2 * kWtActStages + kWtRawStages + i); };
   auto a_full = [&](int i) { return bars + 8u * (2 * kWtActStages + 2 * kWtRawStages + i); };
@@ -108,11 +111,10 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   if (threadIdx.x == 0) {
     for (int i = 0; i < kWtActStages; ++i) {
       mbar_init(act_full(i), 1);
-      mbar_init(act_empty(i), 1);
     }
     for (int i = 0; i < kWtRawStages; ++i) {
       mbar_init(raw_full(i), 1);
-      mbar_init(raw_empty(i), 8);  // both dequant groups read every raw stage
+      mbar_init(raw_empty(i), 8);  // a raw stage holds two K blocks: the four warps of each block's group
     }
     for (int i = 0; i < kWtAStages; ++i) {
       mbar_init(a_full(i), 4);     // the four warps of the group that expanded the K block
@@ -150,7 +152,11 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         tile_coords(t, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int st = it % kWtActStages;
-          if (!mbar_wait(act_empty(st), ((it / kWtActStages) & 1) ^ 1, abort_flag)) {
+          // The stage's previous tenant was K block it - 4; its MMAs' completion is reported once, on
+          // the barrier that also hands the block's A stage back to the dequant warps (a commit
+          // costs the tensor pipe about as long as a small MMA, so there is one per block, not two).
+          const uint32_t prev = it - kWtActStages;
+          if (it >= kWtActStages && !mbar_wait(a_empty(prev % kWtAStages), (prev / kWtAStages) & 1, abort_flag)) {
             wt_report(ws, kStatusTimeoutEmpty, it);
             *abort_flag = 1;
             ok = false;
@@ -218,7 +224,6 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
           for (int k = 0; k < 4; ++k)
             mma_f16_ts(tmem_base, tmem_a + as * kWtAStageColumns + k * 8, make_smem_desc(b_src + k * 32, 16, 1024), idesc,
                        (kb > 0 || k > 0) ? 1u : 0u);
-          tc_commit(act_empty(st));
           tc_commit(a_empty(as));
         }
         if (ok) tc_commit(d_full);
@@ -299,7 +304,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
     // -------- dequant: raw int4 (64-byte swizzled rows) -> 32 columns of this thread's TMEM lane ------
     const int td = threadIdx.x - 256;
     const int r = td & 127;   // weight row of the tile = TMEM lane; td / 32 % 4 == warp % 4
-    const int grp = td >> 7;  // K blocks of this parity
+    const int grp = td >> 7;  // K blocks grp, grp + kWtDequantGroups, ...
     const int groups = K >> 7;
     // Scales of eight consecutive groups arrive as one 16-byte load, one load ahead of their use.
     const bool vec_scales = (groups & 7) == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0;
@@ -315,11 +320,12 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
       __half2 s2 = __half2half2(__float2half_rn(0.f));
       uint4 sc_cur = make_uint4(0, 0, 0, 0), sc_next = make_uint4(0, 0, 0, 0);
       __half next_scale = __float2half_rn(0.f);
+      int cur_octet = -1;  // which eight groups sc_cur holds; sc_next holds the eight after them
       if (has_scales) {
         if (vec_scales) sc_next = *reinterpret_cast<const uint4*>(srow);
-        else next_scale = srow[0];
+        else if ((grp >> 1) < groups) next_scale = srow[grp >> 1];
       }
-      for (int kb = grp; kb < num_kb; kb += 2) {
+      for (int kb = grp; kb < num_kb; kb += kWtDequantGroups) {
         const uint32_t it = it_base + kb;
         const uint32_t raw_it = raw_it_base + (kb >> 1);
         const int rs = raw_it % kWtRawStages;
@@ -334,15 +340,18 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         {
           const int g = kb >> 1;
           if (vec_scales) {
-            if ((g & 7) == 0) {
+            if ((g >> 3) != cur_octet) {  // a group's blocks advance g by one or two: never past a whole octet
               sc_cur = sc_next;
-              if (has_scales && g + 8 < groups) sc_next = *reinterpret_cast<const uint4*>(srow + g + 8);
+              cur_octet = g >> 3;
+              if (has_scales && (cur_octet + 1) * 8 < groups)
+                sc_next = *reinterpret_cast<const uint4*>(srow + (cur_octet + 1) * 8);
             }
             const uint32_t word = (g & 4) ? ((g & 2) ? sc_cur.w : sc_cur.z) : ((g & 2) ? sc_cur.y : sc_cur.x);
             s2 = as_half2(__byte_perm(word, 0u, (g & 1) ? 0x3232u : 0x1010u));
           } else {
             s2 = __half2half2(next_scale);
-            if (has_scales && g + 1 < groups) next_scale = srow[g + 1];
+            const int g_next = (kb + kWtDequantGroups) >> 1;  // this group's next block
+            if (has_scales && g_next < groups) next_scale = srow[g_next];
           }
         }
         const int as = it % kWtAStages;

@@ -17,6 +17,7 @@ from typing import Dict, List, Optional, Tuple
 
 GEMM_THREADS, GEMM_SMEM = 256, 197888
 W4_THREADS, W4_SMEM = 512, 230656  # 1024 + 224 KiB + 256
+W4_WT_THREADS = 512
 W4_WT_SMEM = 214528               # b200_w4a16_gemm_wt: 1024 + 4 x 32 KiB + 6 x 8 KiB + 2 x 16 KiB + 512
 DECODE_THREADS, DECODE_SMEM = 512, {8: 217984, 16: 213760}
 DECODE_SLICE_K = 4096           # K per CTA of the decode kernels; K beyond it is split over CTAs
@@ -197,7 +198,7 @@ def plan_w4a16(function: str, M: int, N: int, K: int, group: int = 128, ldo: Opt
             ws["host_tensor_maps"] = {"kind": "w4a16_wt", "M": M, "N": N, "K": K, "ldo": ldo, "n_offset": n_offset}
         plan.dispatches.append(Dispatch("b200_w4a16_gemm_wt", ["scales", "out", "workspace"],
                                         [M, N, K, ldo, n_offset, (1 << 8) | 0, 0], (min(tiles, sm_count), 1, 1),
-                                        (W4_THREADS, 1, 1), W4_WT_SMEM))
+                                        (W4_WT_THREADS, 1, 1), W4_WT_SMEM))
     elif group == 128 and K % 128 == 0:
         # tiles: a multiple of 16, at most 128 columns; M >= 256 runs the kernel's 256-row variant
         tall = M >= 256

@@ -45,7 +45,7 @@ class W4A16Params(C.Structure):
                 ("ldo", C.c_int32), ("n_offset", C.c_int32), ("variant", C.c_int32), ("tile_n", C.c_int32)]
 
 
-W4A16_AUTO, W4A16_DECODE, W4A16_GEMM, W4A16_GENERIC, W4A16_GEMM_WT = 0, 1, 2, 3, 4
+W4A16_AUTO, W4A16_DECODE, W4A16_GEMM, W4A16_GENERIC, W4A16_GEMM_WT, W4A16_DECODE_TC = 0, 1, 2, 3, 4, 5
 
 
 class _Binding(C.Structure):

@@ -70,7 +70,8 @@ def test_plugin_constants_match_the_runtime_export_table():
             consts[name] = int(value)
     expected = {"kGemmThreads": threads["b200_matmul_f16_f16"], "kGemmSmem": smem["b200_matmul_f16_f16"],
                 "kW4GemmThreads": threads["b200_w4a16_gemm"], "kW4GemmSmem": smem["b200_w4a16_gemm"],
-                "kW4WtSmem": smem["b200_w4a16_gemm_wt"], "kDecodeThreads": threads["b200_w4a16_decode_m8"],
+                "kW4WtSmem": smem["b200_w4a16_gemm_wt"], "kW4WtThreads": threads["b200_w4a16_gemm_wt"],
+                "kDecodeThreads": threads["b200_w4a16_decode_m8"],
                 "kDecodeSmemM8": smem["b200_w4a16_decode_m8"], "kDecodeSmemM16": smem["b200_w4a16_decode_m16"]}
     for name, value in expected.items():
         assert consts.get(name) == value, (name, consts.get(name), value)
@@ -78,6 +79,7 @@ def test_plugin_constants_match_the_runtime_export_table():
     # and the Python restatement of the same table
     assert (dg.GEMM_SMEM, dg.W4_SMEM, dg.W4_WT_SMEM) == (consts["kGemmSmem"], consts["kW4GemmSmem"], consts["kW4WtSmem"])
     assert dg.DECODE_SMEM == {8: consts["kDecodeSmemM8"], 16: consts["kDecodeSmemM16"]}
+    assert (dg.W4_THREADS, dg.W4_WT_THREADS) == (consts["kW4GemmThreads"], consts["kW4WtThreads"])
 
 
 def test_unaligned_shapes_go_to_the_generic_exports():

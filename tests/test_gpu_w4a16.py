@@ -65,6 +65,55 @@ def test_weights_in_tensor_memory_variant(ctx):
                                rtol=RTOL, atol=ATOL)
 
 
+def test_tensor_core_decode_variant(ctx):
+    """The few-rows kernel on the tensor cores: exact on integer data over every M it takes, ragged
+    N (tiles of 128 weight rows), K from one unit to several tiles' worth, shapes whose units
+    divide evenly among the CTAs and shapes whose ranges start and end inside a tile (partial sums
+    met through the workspace), twice through the same workspace; then real-valued data."""
+    rng = np.random.default_rng(71)
+    shapes = [(1, 128, 256), (16, 128, 256), (8, 64, 512), (3, 200, 1024), (16, 1000, 768), (16, 19 * 128, 8192),
+              (5, 150 * 128, 512), (16, 149 * 128 + 8, 4096), (13, 8, 16384), (16, 2048, 2048)]
+    for (M, N, K) in shapes:
+        a, wq, s = exact_case(rng, M, N, K)
+        want = oracle.w4a16(a, wq, s, threads=THREADS)
+        da, dw, ds = ctx.to_device(a), ctx.to_device(wq), ctx.to_device(s)
+        dc, ws = ctx.alloc(M * N * 2), ctx.w4a16_workspace(N)
+        p = ib.W4A16Params(M, N, K, 128, N, 0, ib.W4A16_DECODE_TC, 0)
+        variant, tile_n = ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
+        assert variant == ib.W4A16_DECODE_TC
+        for round_ in range(2):
+            dc.upload(np.full((M, N), 9.0, np.float16))
+            ctx.w4a16_run(p, da, dw, ds, dc, ws, variant, tile_n)
+            ctx.workspace_status(ws)
+            got = dc.download(np.float16, (M, N))
+            assert (got == want).all(), (M, N, K, round_, np.abs(got.astype(np.float32) - want.astype(np.float32)).max())
+        for b in (da, dw, ds, dc, ws):
+            b.free()
+    # a column slice of a wider result
+    M, N, K, ldo, off = 7, 200, 512, 512, 72
+    a, wq, s = exact_case(rng, M, N, K)
+    out = np.full((M, ldo), 7.0, np.float16)
+    w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_DECODE_TC, out=out, n_offset=off)
+    assert (out[:, off:off + N] == oracle.w4a16(a, wq, s, threads=THREADS)).all()
+    assert (out[:, :off] == 7.0).all() and (out[:, off + N:] == 7.0).all()
+    # real-valued data: the dequantised weights are the reference's, the accumulation is f32
+    for M in (1, 16):
+        a, wq, s = workloads.c4_w4a16(M, N=1536, K=4096, seed=72)
+        got = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_DECODE_TC)
+        np.testing.assert_allclose(got.astype(np.float32), oracle.w4a16(a, wq, s, threads=THREADS).astype(np.float32),
+                                   rtol=RTOL, atol=ATOL)
+    # a workspace that was never prepared is refused by the kernel, not run through an empty tensor map
+    a, wq, s = exact_case(rng, 4, 256, 512)
+    da, dw, ds = ctx.to_device(a), ctx.to_device(wq), ctx.to_device(s)
+    dc, ws = ctx.alloc(4 * 256 * 2), ctx.w4a16_workspace(256)
+    ctx.w4a16_run(ib.W4A16Params(4, 256, 512, 128, 256, 0, ib.W4A16_DECODE_TC, 0), da, dw, ds, dc, ws, ib.W4A16_DECODE_TC, 0)
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.workspace_status(ws)
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    for b in (da, dw, ds, dc, ws):
+        b.free()
+
+
 def test_pushing_dispatch_with_one_rank(ctx):
     """The N-sharded form with a channel of one: the kernel stores into the (only) destination,
     raises its arrival word, and the wait kernel sees it; a wait for a word nobody raises runs out

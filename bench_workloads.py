@@ -55,6 +55,14 @@ def workloads():
                                          "C5: Llama-70B-shaped W4A16 M=%d N=28672 K=8192 sharded along N, seed 4" % m,
                                          "GB/s" if m <= 16 else "TFLOP/s", "hbm" if m <= 16 else "tensor", "f16",
                                          M=m, N=28672, K=8192, sharded=True)
+    # The same few-row products through the tensor-core decode variant (not what AUTO picks: it is
+    # the slower of the two decode kernels today; the rows keep its numbers beside the other's).
+    w["c4_w4a16_m16_tc"] = Workload("c4_w4a16_m16_tc", "w4a16", "C4: W4A16 group-128 M=16 N=11008 K=4096, seed 3, "
+                                    "tensor-core decode variant", "GB/s", "hbm", "f16", M=16, N=11008, K=4096,
+                                    variant="decode_tc")
+    w["c5_w4a16_m16_tc"] = Workload("c5_w4a16_m16_tc", "w4a16", "C5: Llama-70B-shaped W4A16 M=16 N=28672 K=8192, seed 4, "
+                                    "tensor-core decode variant", "GB/s", "hbm", "f16", M=16, N=28672, K=8192,
+                                    sharded=True, variant="decode_tc")
     # Data-tiled entry points (the micro kernels llvm-cpu's matmul is made of), on operands of the configurations above.
     w["f2_pack_rhs_c3"] = Workload("f2_pack_rhs_c3", "tiling", "pack of the C3 int8 weight matrix [4096, 11008] into RHS "
                                    "tiles [688, 2048, 16, 2] (transpose inner + outer)", "GB/s", "hbm", "u8", op="pack",
@@ -305,7 +313,8 @@ def w4a16_state(ctx, wl, rank, world, channel):
             variant, tile_n = rt.W4A16_GEMM_WT, 128
         else:
             dc = st.alloc(M * n_local * 2)
-            p = rt.W4A16Params(M, n_local, K, 128, n_local, 0, rt.W4A16_AUTO, 0)
+            wanted = rt.W4A16_DECODE_TC if getattr(wl, "variant", "") == "decode_tc" else rt.W4A16_AUTO
+            p = rt.W4A16Params(M, n_local, K, 128, n_local, 0, wanted, 0)
             variant, tile_n = ctx.w4a16_prepare(p, da, dw, ds, dc, ws)
         st.sets.append((p, da, dw, ds, dc, ws, variant, tile_n))
     if channel is not None and push is None:

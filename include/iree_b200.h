@@ -281,6 +281,10 @@ enum {
   IREE_B200_FLAG_DEVICE_TENSORMAPS = 2,  /* build the tensor maps with the b200_encode_tensormaps dispatch */
   IREE_B200_FLAG_PAIR_CTAS = 4,          /* force the CTA-pair kernels (256-row tiles, cta_group::2) */
   IREE_B200_FLAG_SINGLE_CTA = 8,         /* force the single-CTA kernels (128-row tiles) */
+  IREE_B200_FLAG_SPLIT_K = 16,           /* the workspace has iree_b200_matmul_workspace_bytes() bytes: products of
+                                            few rows (M <= 32) may cut every tile's K range into work items, so
+                                            that all SMs stream the right-hand side (bits 8..11: splits to use,
+                                            0 = choose) */
 };
 #define IREE_B200_WORKSPACE_BYTES 512
 
@@ -302,8 +306,14 @@ typedef struct {
 iree_b200_status_t iree_b200_matmul(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
                                     const void* lhs, const void* rhs, void* out, const float* row_scale,
                                     const float* col_scale, void* workspace);
-/* The same in two steps: prepare() writes the tensor maps and clears the status words;
- * run() only dispatches the kernel and may be repeated while operands stay in place. */
+/* Bytes of workspace a product needs: IREE_B200_WORKSPACE_BYTES, or more when
+ * IREE_B200_FLAG_SPLIT_K is set and the product qualifies (tile counters and one partial
+ * accumulator per tile and split behind the header). */
+size_t iree_b200_matmul_workspace_bytes(iree_b200_context_t* context, const iree_b200_matmul_params_t* params);
+/* The same in two steps: prepare() writes the tensor maps and clears the status words (and the
+ * tile counters of a split product); run() only dispatches the kernel and may be repeated while
+ * operands stay in place. With a split, out_tile_n carries the number of splits minus one in its
+ * upper 16 bits; run() wants it back as it is. */
 iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
                                             const void* lhs, const void* rhs, void* workspace, int32_t* out_tile_n);
 iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,

@@ -21,14 +21,17 @@ module attributes {hal.device.targets = [#cuda]} {
   }
 }
 
+// 4096^3 fills the SM pairs: the CTA-pair export; each CTA loads half of the 256-wide right-hand tile, so the
+// encode dispatch gets 128.
 // CHECK-LABEL: util.func public @matmul_f16
 //   CHECK-NOT:   linalg.matmul
 //       CHECK:   %[[WS:.+]] = hal.dispatch.extern "b200_encode_tensormaps"
+//  CHECK-SAME:       %c4096_i32, %c4096_i32, %c4096_i32, %c1_i32, %c0_i32, %c128_i32, %c2_i32
 //  CHECK-SAME:       -> tensor<512xi8>
 //       CHECK:     push_constants = 7
 //       CHECK:     #hal.executable.object<{path = "b200_contraction.cubin"}>
 //       CHECK:     workgroup_size = [32 : index, 1 : index, 1 : index]
-//       CHECK:   %[[OUT:.+]] = hal.dispatch.extern "b200_matmul_f16_f16"
+//       CHECK:   %[[OUT:.+]] = hal.dispatch.extern "b200_matmul_pair_f16_f16"
 //  CHECK-SAME:       (%[[WS]], %c4096_i32, %c4096_i32, %c4096_i32, %c1_i32, %c0_i32, %c256_i32)
 //       CHECK:     hal.return %c148, %c1, %c1
 //       CHECK:     push_constants = 6

@@ -1377,9 +1377,46 @@ int choose_tile_n(const iree_b200_context_t* ctx, const iree_b200_matmul_params_
   return best;
 }
 
+// Few-rows products (the kernels' deep-ring variant) leave most SMs idle when N / tile_n is small
+// against the SM count: cut every tile's K range into `splits` work items and deal those. A wave
+// of items costs its K blocks plus about two blocks' worth of fixed work per item.
+constexpr int kFewRows = 32, kMaxSplits = 16;
+constexpr size_t kSplitCountersOffset = 512;
+size_t split_partials_offset(int64_t tiles) { return kSplitCountersOffset + ((static_cast<size_t>(tiles) * 4 + 127) / 128) * 128; }
+int choose_splits(const iree_b200_context_t* ctx, const iree_b200_matmul_params_t* p, int bn) {
+  if (!(p->flags & IREE_B200_FLAG_SPLIT_K) || p->M > kFewRows || bn > 128 || use_pairs(ctx, p)) return 1;
+  const int es = elem_bytes_of(p->kind);
+  const int num_kb = (p->K + 128 / es - 1) / (128 / es);
+  const int64_t tiles = static_cast<int64_t>((p->N + bn - 1) / bn) * p->batch;
+  const int forced = (p->flags >> 8) & 0xf;
+  const int sms = usable_sms(ctx);
+  int best = 1;
+  double best_cost = 0;
+  for (int s = 1; s <= kMaxSplits && s <= num_kb; ++s) {
+    if (forced && s != forced) continue;
+    const int64_t waves = (tiles * s + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * (static_cast<double>(num_kb) / s + 2.0);
+    if (best_cost == 0 || cost < best_cost * 0.97) {  // more splits only for a clear gain: they cost scratch traffic
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
 }  // namespace
 
 extern "C" {
+
+size_t iree_b200_matmul_workspace_bytes(iree_b200_context_t* context, const iree_b200_matmul_params_t* params) {
+  if (!context || !params || validate(params) != IREE_B200_STATUS_OK || !params->M || !params->N || !params->K || !params->batch)
+    return IREE_B200_WORKSPACE_BYTES;
+  const int bn = choose_tile_n(context, params);
+  const int splits = bn ? choose_splits(context, params, bn) : 1;
+  if (splits <= 1) return IREE_B200_WORKSPACE_BYTES;
+  const int64_t tiles = static_cast<int64_t>((params->N + bn - 1) / bn) * params->batch;
+  return split_partials_offset(tiles) + static_cast<size_t>(tiles) * splits * kFewRows * bn * 4;
+}
 
 iree_b200_status_t iree_b200_context_create(int32_t device_ordinal, const char* cubin_path,
                                             iree_b200_context_t** out_context) {
@@ -1560,7 +1597,13 @@ iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const 
   const int es = elem_bytes_of(params->kind);
   const int bn = choose_tile_n(context, params);
   if (!bn) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tile_n %d is not usable for this layout", params->tile_n);
-  if (out_tile_n) *out_tile_n = bn;
+  const int splits = choose_splits(context, params, bn);
+  if (out_tile_n) *out_tile_n = bn | ((splits - 1) << 16);
+  if (splits > 1) {  // the tile counters behind the header start at zero
+    const int64_t tiles = static_cast<int64_t>((params->N + bn - 1) / bn) * params->batch;
+    B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, static_cast<uint8_t*>(workspace) + kSplitCountersOffset,
+                                                   split_partials_offset(tiles) - kSplitCountersOffset, 0));
+  }
   const uint32_t bk = 128 / es;
   const uint32_t M = params->M, N = params->N, K = params->K, B = params->batch;
   if (params->flags & IREE_B200_FLAG_DEVICE_TENSORMAPS) {
@@ -1628,15 +1671,18 @@ iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree
   if (!workspace) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "workspace is NULL");
   if (tile_n <= 0) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "run() needs the tile_n that prepare() returned");
   const int sms = usable_sms(context);
+  const int width = tile_n & 0xffff, splits = (tile_n >> 16) + 1;
+  if (splits > 1 && (pairs || params->M > kFewRows || width > 128 || splits > kMaxSplits))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "tile_n %#x asks for a K split this product cannot take", tile_n);
   uint32_t grid;
   if (pairs) {
     const int64_t tiles =
-        static_cast<int64_t>((params->M + 255) / 256) * ((params->N + tile_n - 1) / tile_n) * params->batch;
+        static_cast<int64_t>((params->M + 255) / 256) * ((params->N + width - 1) / width) * params->batch;
     grid = 2u * static_cast<uint32_t>(tiles < sms / 2 ? tiles : sms / 2);  // whole pairs only
   } else {
-    const int64_t tiles =
-        static_cast<int64_t>((params->M + 127) / 128) * ((params->N + tile_n - 1) / tile_n) * params->batch;
-    grid = static_cast<uint32_t>(tiles < sms ? tiles : sms);
+    const int64_t items =
+        static_cast<int64_t>((params->M + 127) / 128) * ((params->N + width - 1) / width) * params->batch * splits;
+    grid = static_cast<uint32_t>(items < sms ? items : sms);
   }
   const int32_t constants[6] = {params->M, params->N, params->K, params->batch, params->rhs_layout, tile_n};
   if (requant) {

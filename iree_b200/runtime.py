@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 KIND_F16, KIND_BF16, KIND_I8 = 0, 1, 2
 EPILOGUE_CAST, EPILOGUE_ACCUMULATOR, EPILOGUE_REQUANT_F16 = 0, 1, 2
 RHS_KN, RHS_NK = 0, 1
-FLAG_FORCE_GENERIC, FLAG_DEVICE_TENSORMAPS, FLAG_PAIR_CTAS, FLAG_SINGLE_CTA = 1, 2, 4, 8
+FLAG_FORCE_GENERIC, FLAG_DEVICE_TENSORMAPS, FLAG_PAIR_CTAS, FLAG_SINGLE_CTA, FLAG_SPLIT_K = 1, 2, 4, 8, 16
 WORKSPACE_BYTES = 512
 
 _STATUS_NAMES = {0: "OK", 1: "CANCELLED", 2: "UNKNOWN", 3: "INVALID_ARGUMENT", 4: "DEADLINE_EXCEEDED",
@@ -253,6 +253,12 @@ class Context:
 
     def workspace(self) -> DeviceBuffer:
         return DeviceBuffer(self, WORKSPACE_BYTES).fill(0)
+
+    def matmul_workspace(self, params: MatmulParams) -> DeviceBuffer:
+        """A workspace of the size this product asks for (more than the header when FLAG_SPLIT_K applies)."""
+        library().iree_b200_matmul_workspace_bytes.restype = C.c_size_t
+        nbytes = int(library().iree_b200_matmul_workspace_bytes(self.handle, C.byref(params)))
+        return DeviceBuffer(self, nbytes).fill(0)
 
     def workspace_status(self, ws) -> None:
         check(library().iree_b200_workspace_status(self.handle, _vp(ws)))

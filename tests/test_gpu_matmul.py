@@ -134,6 +134,52 @@ def test_c3_w8a8_requant(ctx, M):
     assert (got == want).all()                           # same operation order: identical in fact
 
 
+@pytest.mark.parametrize("splits", [0, 2, 3, 5, 16])
+def test_few_rows_products_with_their_k_range_split_over_ctas(ctx, splits):
+    """Few-rows products whose tiles' K ranges are cut into work items (partial accumulators met through
+    the workspace, last arriver applies the epilogue): i32 results bit-exact and the requant output
+    identical to the unsplit kernel's, f16 exact on small integers, ragged N and K, both right-hand
+    side layouts, a batch, and twice through the same workspace (the counters come back to zero)."""
+    from iree_b200 import runtime as rt
+    rng = np.random.default_rng(90 + splits)
+    flags = rt.FLAG_SPLIT_K | (splits << 8)
+    cases = [(ib.KIND_I8, ib.EPILOGUE_ACCUMULATOR, ib.RHS_KN, 16, 1280, 4096, 1),
+             (ib.KIND_I8, ib.EPILOGUE_REQUANT_F16, ib.RHS_KN, 1, 11008, 4096, 1),
+             (ib.KIND_I8, ib.EPILOGUE_ACCUMULATOR, ib.RHS_NK, 7, 200, 2064, 1),
+             (ib.KIND_F16, ib.EPILOGUE_CAST, ib.RHS_KN, 32, 264, 1096, 1),
+             (ib.KIND_F16, ib.EPILOGUE_ACCUMULATOR, ib.RHS_NK, 5, 96, 2048, 3)]
+    for kind, epi, layout, M, N, K, B in cases:
+        a = small_ints(rng, kind, (B, M, K))
+        b = small_ints(rng, kind, (B, K, N) if layout == ib.RHS_KN else (B, N, K))
+        if kind == ib.KIND_F16:
+            a, b = (a / 4).astype(np.float16), (b / 4).astype(np.float16)      # keeps |result| exact in f16
+        sa = rng.uniform(0.5, 1.5, M).astype(np.float32) / 64
+        sw = rng.uniform(0.5, 1.5, N).astype(np.float32) / 64
+        requant = epi == ib.EPILOGUE_REQUANT_F16
+        da, db = ctx.to_device(a), ctx.to_device(b)
+        odt = rt.out_dtype(kind, epi)
+        dc = ctx.alloc(B * M * N * np.dtype(odt).itemsize)
+        rs, cs = (ctx.to_device(sa), ctx.to_device(sw)) if requant else (None, None)
+        p = MatmulParams(kind, epi, M, N, K, B, layout, 0, flags)
+        ws = ctx.matmul_workspace(p)
+        tile_n = ctx.matmul_prepare(p, da, db, ws)
+        if splits:
+            assert (tile_n >> 16) + 1 == min(splits, -(-K // (128 if kind == ib.KIND_I8 else 64)))
+        t = {ib.KIND_I8: oracle.TYPE_S8S8S32, ib.KIND_F16: oracle.TYPE_F16F16F32}[kind]
+        for round_ in range(2):
+            dc.fill(0x55)
+            ctx.matmul_run(p, da, db, dc, ws, tile_n, rs, cs)
+            ctx.workspace_status(ws)
+            got = dc.download(odt, (B, M, N))
+            for i in range(B):
+                bi = b[i] if layout == ib.RHS_KN else np.ascontiguousarray(b[i].T)
+                acc = oracle_matmul(t, a[i], bi)
+                want = oracle.requant_f16(acc, sa, sw) if requant else (oracle.truncf(acc) if epi == ib.EPILOGUE_CAST else acc)
+                assert (got[i] == want).all(), (kind, epi, layout, M, N, K, i, round_, splits, tile_n >> 16)
+        for x in (da, db, dc, ws) + ((rs, cs) if requant else ()):
+            x.free()
+
+
 def test_int8_linearity_at_full_size(ctx):
     """Size-independent property on the largest i8 configuration: C(A, B1 + B2) = C(A,B1) + C(A,B2)."""
     rng = np.random.default_rng(5)

@@ -193,12 +193,12 @@ def test_c5_w4a16_70b_shape(ctx, M):
     np.testing.assert_allclose(got[np.ix_(rows, cols)].astype(np.float32), want.astype(np.float32), rtol=RTOL, atol=ATOL)
 
 
-@pytest.mark.parametrize("variant", [ib.W4A16_DECODE, ib.W4A16_GEMM])
+@pytest.mark.parametrize("variant", [ib.W4A16_DECODE, ib.W4A16_GEMM, ib.W4A16_DECODE_TC])
 def test_distance_from_the_restated_dequant_is_measured(ctx, variant):
     """Data on which the rounding of f16(w * s) matters: integer activations (so every product
     a * w and every group sum is exact) and scales that are not powers of two. The restated
-    dispatch rounds each dequantised weight to f16 before the contraction. The tensor-core kernel
-    does the same and may differ from the oracle only through f32 summation order: at most one
+    dispatch rounds each dequantised weight to f16 before the contraction. The tensor-core kernels
+    do the same and may differ from the oracle only through f32 summation order: at most one
     f16 unit in the last place of the result. The decode kernel multiplies the exact f32 group
     sum by the scale instead, so it differs from the oracle by the weights' rounding error, at
     most 2^-11 relative per weight: |got - oracle| <= 2^-11 * sum_k |a_k| |w_k s| plus the
@@ -216,7 +216,7 @@ def test_distance_from_the_restated_dequant_is_measured(ctx, variant):
     exact_scaled = a.astype(np.float64) @ (w.astype(np.float64) * s_full).T    # scale applied exactly
     magnitude = np.abs(a.astype(np.float64)) @ (np.abs(w.astype(np.float64)) * s_full).T
     ulp = np.spacing(np.abs(want).astype(np.float16)).astype(np.float64)
-    if variant == ib.W4A16_GEMM:
+    if variant in (ib.W4A16_GEMM, ib.W4A16_DECODE_TC):    # the tensor-core kernels: exact dequant
         assert (np.abs(got - want) <= ulp).all()
         return
     bound = 2.0 ** -11 * magnitude + ulp

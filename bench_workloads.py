@@ -240,7 +240,7 @@ def matmul_state(ctx, wl, rank, world, channel):
     for _ in range(n_sets):
         da, db = st.to_device(a), st.to_device(b)
         dc = st.alloc(out_bytes)
-        p = rt.MatmulParams(wl.kind, wl.epi, wl.M, wl.N, wl.K, wl.B, ib.RHS_KN, 0, rt.FLAG_SPLIT_K)
+        p = rt.MatmulParams(wl.kind, wl.epi, wl.M, wl.N, wl.K, wl.B, ib.RHS_KN, 0, 0)
         ws = st.track(ctx.matmul_workspace(p))
         bn = ctx.matmul_prepare(p, da, db, ws)
         rs = st.to_device(scales[0]) if scales else None

@@ -123,6 +123,12 @@ iree_b200_status_t iree_b200_executable_def_build(int32_t entry_count, const cha
                                                   size_t image_size, void* out_data, size_t out_capacity,
                                                   size_t* out_size);
 
+/* The ExecutableDef of the contraction cubin: every export of the file with the block size and
+ * dynamic shared-memory size its kernel needs (what the compiler plugin records per
+ * hal.executable.export). Needs no GPU. Call with out_data == NULL to query the size. */
+iree_b200_status_t iree_b200_contraction_executable_def(const char* cubin_path, void* out_data, size_t out_capacity,
+                                                        size_t* out_size);
+
 /* iree_hal_executable_cache_prepare_executable for format "PTXE"
  * (runtime/src/iree/hal/drivers/cuda/nop_executable_cache.c:76-93,
  * native_executable.c:55-272): verifies the flatbuffer (non-empty entry names, as many block
@@ -281,10 +287,10 @@ enum {
   IREE_B200_FLAG_DEVICE_TENSORMAPS = 2,  /* build the tensor maps with the b200_encode_tensormaps dispatch */
   IREE_B200_FLAG_PAIR_CTAS = 4,          /* force the CTA-pair kernels (256-row tiles, cta_group::2) */
   IREE_B200_FLAG_SINGLE_CTA = 8,         /* force the single-CTA kernels (128-row tiles) */
-  IREE_B200_FLAG_SPLIT_K = 16,           /* the workspace has iree_b200_matmul_workspace_bytes() bytes: products of
-                                            few rows (M <= 32) may cut every tile's K range into work items, so
-                                            that all SMs stream the right-hand side (bits 8..11: splits to use,
-                                            0 = choose) */
+  IREE_B200_FLAG_SPLIT_K = 16,           /* the workspace has iree_b200_matmul_workspace_bytes() bytes: a product of
+                                            few rows (M <= 32) cuts every tile's K range into the number of work
+                                            items given in bits 8..11 (1..15; 0 = no split, which is the faster
+                                            choice on every shape measured so far) */
 };
 #define IREE_B200_WORKSPACE_BYTES 512
 

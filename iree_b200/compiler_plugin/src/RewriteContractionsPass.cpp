@@ -249,25 +249,6 @@ static int64_t chooseTileN(int64_t M, int64_t N, int64_t batch, int64_t chunk, i
   return best;
 }
 
-// Few-rows products leave most SMs idle when N / tile_n is small against the SM count: every tile's
-// K range is cut into this many work items (the runtime library's rule: a wave of items costs its K
-// blocks plus about two blocks' worth of fixed work; more splits only for a clear gain).
-static int64_t chooseSplits(int64_t M, int64_t N, int64_t K, int64_t batch, int64_t elem, int64_t bn, bool pairs,
-                            int smCount) {
-  if (M > 32 || bn > 128 || pairs) return 1;
-  const int64_t blockK = 128 / elem, numKb = (K + blockK - 1) / blockK, tiles = ((N + bn - 1) / bn) * batch;
-  int64_t best = 1;
-  double bestCost = 0;
-  for (int64_t s = 1; s <= 16 && s <= numKb; ++s) {
-    const double cost = double((tiles * s + smCount - 1) / smCount) * (double(numKb) / double(s) + 2.0);
-    if (bestCost == 0 || cost < bestCost * 0.97) {
-      bestCost = cost;
-      best = s;
-    }
-  }
-  return best;
-}
-
 class RewriteContractionsPass : public PassWrapper<RewriteContractionsPass, OperationPass<ModuleOp>> {
  public:
   explicit RewriteContractionsPass(RewriteOptions options) : options(std::move(options)) {}
@@ -410,12 +391,8 @@ class RewriteContractionsPass : public PassWrapper<RewriteContractionsPass, Oper
     const int64_t bn = chooseTileN(M, N, batch, (pairs ? 2 : 1) * 128 / elem, options.smCount, pairs);
     const int64_t rows = pairs ? 256 : 128;
     const int64_t tiles = ((M + rows - 1) / rows) * ((N + bn - 1) / bn) * batch;
-    const int64_t splits = chooseSplits(M, N, K, batch, elem, bn, pairs, options.smCount);
-    const int64_t gridX = pairs ? 2 * std::min<int64_t>(tiles, (options.smCount & ~1) / 2)
-                                : std::min<int64_t>(tiles * splits, options.smCount);
-    // split products: a counter per tile (padded to 128 bytes) and a [32][bn] 32-bit partial per tile and split
-    const int64_t wsBytes = splits == 1 ? 512 : 512 + (tiles * 4 + 127) / 128 * 128 + tiles * splits * 32 * bn * 4;
-    auto wsType = RankedTensorType::get({wsBytes}, b.getI8Type());
+    const int64_t gridX = pairs ? 2 * std::min<int64_t>(tiles, (options.smCount & ~1) / 2) : std::min<int64_t>(tiles, options.smCount);
+    auto wsType = RankedTensorType::get({512}, b.getI8Type());
     // The A / B templates of the operand type: rows (2 kind) and (2 kind + 1) of the pair table this export reads.
     const Template tmpl = m.kind == ElemKind::I8 ? kU8Sw128R3 : m.kind == ElemKind::BF16 ? kBF16Sw128R3 : kF16Sw128R3;
     SmallVector<int8_t> pair(256);
@@ -426,15 +403,12 @@ class RewriteContractionsPass : public PassWrapper<RewriteContractionsPass, Oper
     // in pair mode each CTA loads half of the right-hand tile: the map's box is half as wide
     SmallVector<Value> encOperands = {m.lhs, m.rhs, pairTable};
     for (int64_t v : {M, N, K, batch, int64_t(0), pairs ? bn / 2 : bn, elem}) encOperands.push_back(i32(b, loc, v));
-    if (splits > 1) encOperands.insert(encOperands.begin() + 3, workspace(b, loc, wsBytes));  // counters start at zero
     Operation *enc = emit(b, loc, "b200_encode_tensormaps", {idx(b, loc, 1)}, encOperands, {wsType}, 3, 7, {1, 1, 1}, {32, 1, 1}, 0);
-    if (splits > 1) enc->setAttr("tied_operands", b.getIndexArrayAttr({3}));  // writes the maps into the zeroed tensor
     // GEMM: bindings (out[, a_scale, w_scale], workspace), constants (M, N, K, batch, rhs_layout, tile_n)
     SmallVector<Value> operands(scales.begin(), scales.end());
     operands.push_back(enc->getResult(0));
-    // tile width, and splits - 1 in the upper half of the same constant
-    for (int64_t v : {M, N, K, batch, int64_t(0), bn | ((splits - 1) << 16)}) operands.push_back(i32(b, loc, v));
-    Operation *gemm = emit(b, loc, exportName(m, /*generic=*/false, pairs), {idx(b, loc, tiles * splits)}, operands, {outType},
+    for (int64_t v : {M, N, K, batch, int64_t(0), bn}) operands.push_back(i32(b, loc, v));
+    Operation *gemm = emit(b, loc, exportName(m, /*generic=*/false, pairs), {idx(b, loc, tiles)}, operands, {outType},
                            /*numReadOnly=*/scales.size(), 6, {gridX, 1, 1}, {kGemmThreads, 1, 1}, kGemmSmem);
     // The workspace is read and written (status words): it is the last read-write binding.
     gemm->setAttr("b200.binding_order", b.getStrArrayAttr(requant ? ArrayRef<StringRef>{"out", "a_scale", "w_scale", "workspace"}

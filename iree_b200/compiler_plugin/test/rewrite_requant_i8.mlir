@@ -26,18 +26,16 @@ module attributes {hal.device.targets = [#cuda]} {
 }
 
 // Pattern C: i8 matmul + (sitofp, mulf a_scale[m], mulf w_scale[n], truncf) consumer. Sixteen rows: the
-// few-rows variant, every tile's K range cut into three work items (86 tiles x 3 on 148 SMs), so the
-// workspace carries tile counters and partial accumulators behind its header and starts zeroed.
+// few-rows variant of the 1-CTA export (tiles 128 wide, deep ring), 86 tiles.
 // CHECK-LABEL: util.func public @w8a8_m16
 //   CHECK-NOT:   linalg.matmul
 //   CHECK-NOT:   arith.sitofp
-//       CHECK:   %[[ZWS:.+]] = linalg.fill {{.*}} -> tensor<4227968xi8>
 //       CHECK:   %[[WS:.+]] = hal.dispatch.extern "b200_encode_tensormaps"
-//  CHECK-SAME:       %[[ZWS]], %c16_i32, %c11008_i32, %c4096_i32, %c1_i32, %c0_i32, %c128_i32, %c1_i32
-//  CHECK-SAME:       -> tensor<4227968xi8>
+//  CHECK-SAME:       %c16_i32, %c11008_i32, %c4096_i32, %c1_i32, %c0_i32, %c128_i32, %c1_i32
+//  CHECK-SAME:       -> tensor<512xi8>
 //       CHECK:   %[[OUT:.+]] = hal.dispatch.extern "b200_matmul_i8_requant_f16"
-//  CHECK-SAME:       (%a_scale, %w_scale, %[[WS]], %c16_i32, %c11008_i32, %c4096_i32, %c1_i32, %c0_i32, %c131200_i32)
-//       CHECK:     hal.return %c148, %c1, %c1
+//  CHECK-SAME:       (%a_scale, %w_scale, %[[WS]], %c16_i32, %c11008_i32, %c4096_i32, %c1_i32, %c0_i32, %c128_i32)
+//       CHECK:     hal.return %c86, %c1, %c1
 //       CHECK:     push_constants = 6
 //       CHECK:     workgroup_size = [256 : index, 1 : index, 1 : index], workgroup_local_memory = 197888 : index
 //       CHECK:   util.return %[[OUT]]

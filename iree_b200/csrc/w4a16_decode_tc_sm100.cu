@@ -13,10 +13,9 @@
 // tile's counter, and whoever arrives last adds the tile's partial sums in CTA order (the result
 // does not depend on who that is) and writes the f16 result.
 //
-// What bounds the kernel is bytes in flight and how long a stage stays occupied, so the weights
-// have a ring of their own that only the dequant warps read: a stage is handed back as soon as its
-// bytes are in registers. Each box takes 256 contiguous bytes per weight row (two 128-byte lines);
-// with 128-byte boxes the same loop streams a quarter slower.
+// The weights have a ring of their own that only the dequant warps read (the MMAs never touch it).
+// Each box takes 256 contiguous bytes per weight row (two 128-byte lines); with 128-byte boxes the
+// same loop streams a quarter slower.
 //
 //   warp 0      TMA producer of the raw weights: one box of 128 rows x 2 x 128 bytes per unit, five
 //               stages of 32 KiB
@@ -74,9 +73,20 @@ __device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+// Loads from a ring stage that is handed back to its producer right afterwards. They are
+// volatile at the PTX level: a weak load may be executed again later (to save registers across
+// the long waits that follow), and by then the stage holds the next lap's bytes.
+__device__ __forceinline__ uint2 lds64_once(uint32_t addr) {
   uint2 r;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr));
+  asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr) : "memory");
+  return r;
+}
+__device__ __forceinline__ uint4 lds128_once(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "r"(addr)
+               : "memory");
   return r;
 }
 
@@ -431,12 +441,14 @@ __device__ __forceinline__ void decode_tc_body(const __half* __restrict__ scales
         break;
       }
       const uint32_t raw = smem_base + st * kTcRawBytes;
-      const uint4 w00 = lds128(raw + off00), w01 = lds128(raw + off01);
-      const uint4 w10 = lds128(raw + off10), w11 = lds128(raw + off11);
-      const uint2 sc = lds64(scale_base + st * kTcScaleBytes + r * 8);
-      // the stage's bytes are in registers: hand it back
-      __syncwarp();
-      if (lane == 0) mbar_arrive(raw_empty(st));
+      const uint4 w00 = lds128_once(raw + off00), w01 = lds128_once(raw + off01);
+      const uint4 w10 = lds128_once(raw + off10), w11 = lds128_once(raw + off11);
+      const uint2 sc = lds64_once(scale_base + st * kTcScaleBytes + r * 8);
+      // The stage goes back to its producer after the unit's second expansion, not here: handing it
+      // back as soon as the bytes were in registers corrupted single lanes' weights about once in
+      // five launches at sixteen units per CTA (also with these volatile loads and with every loaded
+      // register consumed before the arrival); with the late hand-over no run has failed.
+      const int st_done = st;
       if (++st == kTcRawStages) {
         st = 0;
         parity ^= 1u;
@@ -461,6 +473,8 @@ __device__ __forceinline__ void decode_tc_body(const __half* __restrict__ scales
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(h));
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(raw_empty(st_done));
     }
   }
 

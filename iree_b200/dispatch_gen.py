@@ -87,33 +87,6 @@ def choose_tile_n(M: int, N: int, batch: int, chunk: int, sm_count: int = SM_COU
     return best
 
 
-FEW_ROWS, MAX_SPLITS = 32, 16
-
-
-def choose_splits(M: int, N: int, K: int, batch: int, elem_bytes: int, bn: int, pairs: bool,
-                  sm_count: int = SM_COUNT) -> int:
-    """Few-rows products leave most SMs idle when N / tile_n is small against the SM count: every
-    tile's K range is cut into this many work items (the runtime library's rule: a wave of items
-    costs its K blocks plus about two blocks' worth of fixed work; more splits only for a clear gain)."""
-    if M > FEW_ROWS or bn > 128 or pairs:
-        return 1
-    block_k = 128 // elem_bytes
-    num_kb = (K + block_k - 1) // block_k
-    tiles = ((N + bn - 1) // bn) * batch
-    best, best_cost = 1, 0.0
-    for s in range(1, min(MAX_SPLITS, num_kb) + 1):
-        cost = ((tiles * s + sm_count - 1) // sm_count) * (num_kb / s + 2.0)
-        if best_cost == 0.0 or cost < best_cost * 0.97:
-            best, best_cost = s, cost
-    return best
-
-
-def split_workspace_bytes(tiles: int, splits: int, bn: int) -> int:
-    """512-byte header, a counter per tile (padded to 128 bytes), a raw 32-bit partial accumulator
-    of [32 rows][bn columns] per tile and split."""
-    return 512 + (tiles * 4 + 127) // 128 * 128 + tiles * splits * FEW_ROWS * bn * 4
-
-
 def matmul_export(kind: str, epilogue: str, generic: bool, pairs: bool = False) -> str:
     table = {("f16", "cast"): "f16_f16", ("f16", "acc"): "f16_f32", ("bf16", "cast"): "bf16_bf16",
              ("bf16", "acc"): "bf16_f32", ("i8", "acc"): "i8_i32", ("i8", "requant"): "i8_requant_f16"}
@@ -147,10 +120,8 @@ def plan_matmul(function: str, kind: str, epilogue: str, M: int, N: int, K: int,
     bn = choose_tile_n(M, N, batch, chunk, sm_count, pairs)
     rows = 256 if pairs else 128
     tiles = ((M + rows - 1) // rows) * ((N + bn - 1) // bn) * batch
-    splits = choose_splits(M, N, K, batch, es, bn, pairs, sm_count)
-    grid = 2 * min(tiles, (sm_count & ~1) // 2) if pairs else min(tiles * splits, sm_count)   # whole pairs only
-    plan.transients.append({"name": "workspace", "bytes": 512 if splits == 1 else split_workspace_bytes(tiles, splits, bn),
-                            "zero": True})
+    grid = 2 * min(tiles, (sm_count & ~1) // 2) if pairs else min(tiles, sm_count)   # whole pairs only
+    plan.transients.append({"name": "workspace", "bytes": 512, "zero": True})
     if device_tensor_maps:
         plan.transients.append({"name": "templates", "bytes": 256, "zero": False, "templates": kind})
         # in pair mode each CTA loads half of the right-hand tile: the map's box is half as wide
@@ -160,8 +131,7 @@ def plan_matmul(function: str, kind: str, epilogue: str, M: int, N: int, K: int,
         plan.transients[0]["host_tensor_maps"] = {"kind": kind, "epilogue": epilogue, "M": M, "N": N, "K": K,
                                                   "batch": batch, "layout": layout, "tile_n": bn}
     plan.dispatches.append(Dispatch(matmul_export(kind, epilogue, False, pairs), ["out"] + scales + ["workspace"],
-                                    [M, N, K, batch, layout, bn | ((splits - 1) << 16)], (grid, 1, 1),
-                                    (GEMM_THREADS, 1, 1), GEMM_SMEM))     # tile width, and splits - 1 in the upper half
+                                    [M, N, K, batch, layout, bn], (grid, 1, 1), (GEMM_THREADS, 1, 1), GEMM_SMEM))
     return plan
 
 

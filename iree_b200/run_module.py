@@ -123,6 +123,37 @@ def _host_tensor_maps(ctx, spec, buffers, ws):
         ctx.matmul_prepare(p, buffers["lhs"], buffers["rhs"], ws)
 
 
+def _run_bytecode_module(args, contents: bytes) -> int:
+    """--module=x.vmfb: the bytecode-module subset (iree_b200/vm.py) instead of a JSON plan."""
+    from . import vm, vmfb
+    try:
+        module = vmfb.read_module(contents)
+    except vmfb.VmfbError as e:
+        print(str(e), file=sys.stderr)
+        return 1
+    exported = [f.name for f in module.functions if f.name]
+    function = args.function or (exported[0] if exported else "")
+    if function not in exported:
+        print("NOT_FOUND: no function @%s in the module (it exports %s)" % (function, ", ".join("@" + n for n in exported)),
+              file=sys.stderr)
+        return 1
+    inputs = [parse_tensor_flag(t) for t in args.input]
+    ordinal = int(args.device.split(":")[1]) if ":" in args.device else 0
+    ctx = rt.Context(ordinal)
+    try:
+        print("EXEC @%s" % function)
+        outs, _ = vm.run_vmfb(ctx, contents, function, inputs)
+        for i, o in enumerate(outs):
+            if i < len(args.output) and args.output[i].startswith("@"):
+                np.save(args.output[i][1:], o)
+            else:
+                print("result[%d]: hal.buffer_view\n%sx%s=%s ..." % (i, "x".join(map(str, o.shape)), o.dtype,
+                                                                   " ".join(str(v) for v in o.reshape(-1)[:8])))
+        return 0
+    finally:
+        ctx.close()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="iree_b200.run_module", allow_abbrev=False)
     ap.add_argument("--device", default="cuda")
@@ -138,7 +169,10 @@ def main(argv=None) -> int:
     if not args.device.startswith("cuda"):
         print("only --device=cuda is available (no CPU path)", file=sys.stderr)
         return 2
-    plan = Plan.from_json(open(args.module).read())
+    raw = open(args.module, "rb").read()
+    if not raw.lstrip()[:1] == b"{":
+        return _run_bytecode_module(args, raw)
+    plan = Plan.from_json(raw.decode())
     if args.function and args.function != plan.function:
         print("NOT_FOUND: no function @%s in the module (it holds @%s)" % (args.function, plan.function), file=sys.stderr)
         return 1

@@ -14,7 +14,7 @@
 //   D  generic(extsi i4 -> sitofp f16 -> mulf scale[n,g]) feeding the grouped contraction
 //      generic with two reduction dims (g, k) and a truncf (the IR of
 //      Dialect/Flow/Transforms/test/pipeline_tests.mlir:53-99, signed weights, no zero point)
-//        -> b200_w4a16_decode_m8 / _m16 (static M <= 16), b200_w4a16_gemm_wt (M >= 256),
+//        -> b200_w4a16_decode_m8 / _m16 (static M <= 16), b200_w4a16_gemm_wt (M > 16, aligned result),
 //           else b200_w4a16_gemm
 //
 // Operands whose row pitch is not a multiple of 16 bytes go to the *_generic exports.
@@ -450,9 +450,10 @@ class RewriteContractionsPass : public PassWrapper<RewriteContractionsPass, Oper
       m.last->getResult(0).replaceAllUsesWith(ext->getResult(0));
       return success();
     }
-    if (M >= 256) {
-      // many rows: weights as the tensor-memory operand; 128 weight rows x 256 activation rows per tile; results
-      // leave by TMA stores through the output map at byte 512 of the workspace (one destination)
+    if ((ldo * 2) % 16 == 0 && nOff % 8 == 0) {
+      // more than sixteen rows: weights as the tensor-memory operand; 128 weight rows x 128 (M <= 128) or 256
+      // activation rows per tile; results leave by TMA stores through the output map at byte 512 of the
+      // workspace (one destination), which needs the result's pitch and offset on 16-byte boundaries
       Value ws = workspace(b, loc, 512 + 8 * 128 + 8 * 8);
       ws = encodeMap(b, loc, m.activations, table, ws, 0, kF16Sw128R3, 3, {K, M, 1}, {K * 2, M * K * 2}, {64, 128, 1}, 2, 1);
       ws = encodeMap(b, loc, m.weights, table, ws, 128, kU8Sw64R3, 3, {K / 2, N, 1}, {K / 2, N * (K / 2)}, {64, 128, 1}, 1, 0);

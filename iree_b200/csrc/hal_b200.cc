@@ -1873,11 +1873,12 @@ static int w4_variant(const iree_b200_context_t* ctx, const iree_b200_w4a16_para
   if (p->group_size == 128 && aligned && scales16 && p->M <= 16 && p->N % 16 == 0 && p->K % 256 == 0 && p->K <= 16384)
     return IREE_B200_W4A16_DECODE;
   if (p->group_size == 128 && aligned && p->K % 128 == 0) {
-    // Many rows: the kernel with the weights as the tensor-memory operand; it leaves its results by
-    // TMA stores, which need the result on 16-byte boundaries.
+    // The kernel with the weights as the tensor-memory operand (activation tiles of 128 rows up to
+    // M = 128, of 256 above); it leaves its results by TMA stores, which need the result on 16-byte
+    // boundaries. Otherwise the kernel with the expanded weights as a shared-memory operand.
     const bool out16 = !(reinterpret_cast<uintptr_t>(out) % 16) && (static_cast<int64_t>(p->ldo) * 2) % 16 == 0 &&
                        p->n_offset % 8 == 0;
-    return (p->M >= 256 && out16) ? IREE_B200_W4A16_GEMM_WT : IREE_B200_W4A16_GEMM;
+    return out16 ? IREE_B200_W4A16_GEMM_WT : IREE_B200_W4A16_GEMM;
   }
   return IREE_B200_W4A16_GENERIC;
 }

@@ -1,6 +1,6 @@
-// Fused "dequantise int4 weights, then contract" for many activation rows (M >= 256), with the
+// Fused "dequantise int4 weights, then contract" for more than a few activation rows (M > 16), with the
 // operand roles swapped: the WEIGHTS are the 128-row operand of the tensor core and live in
-// tensor memory, the activations are the (up to) 256-row shared-memory operand, and the
+// tensor memory, the activations are the (128- or 256-row) shared-memory operand, and the
 // accumulator holds the transposed tile D[n, m].
 //
 //   w_f16[n,k] = f16( f16(sext(wq[n,k])) * scale[n, k/128] )      (exactly the dequant generic)
@@ -83,8 +83,8 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   const uint32_t out_base = raw_base + kWtRawStages * kWtRawStageBytes;
   const uint32_t bars = out_base + 2 * kWtOutStageBytes;
   uint8_t* bars_gen = smem_gen + (bars - smem_base);
-  // barriers: act full (the slots after them are unused: an activation stage comes back through the
-  // A-stage barrier of the K block that held it), raw full / empty, A-stage full / empty, accumulator full / empty
+  // barriers: act full (eight slots, four in use with 256-row tiles; an activation stage comes back through
+  // the A-stage barrier of the K block that held it), raw full / empty, A-stage full / empty, accumulator full / empty
   auto act_full = [&](int i) { return bars + 8u * i; };
   auto raw_full = [&](int i) { return bars + 8u * (2 * kWtActStages + i); };
   auto raw_empty = [&](int i) { return bars + 8u * (2 * kWtActStages + kWtRawStages + i); };
@@ -103,13 +103,20 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
     if (threadIdx.x == 0) wt_report(ws, kStatusBadArgument, 0);
     return;
   }
-  const int tiles_m = (M + kWtARows - 1) / kWtARows;
+  // Up to 128 activation rows: tiles of 128 (MMA N = 128, half the tensor-pipe time per K block and
+  // no zero rows to multiply); above that tiles of 256.
+  const int a_rows = M <= 128 ? 128 : kWtARows;
+  // The activation ring holds 128 KiB either way: four stages of 256 rows or eight of 128 (a tile of
+  // 128 rows finishes its MMAs in half the time, so it needs twice the stages in flight).
+  const int act_stages = a_rows == 128 ? 2 * kWtActStages : kWtActStages;
+  const uint32_t act_pitch = static_cast<uint32_t>(a_rows) * 128u;
+  const int tiles_m = (M + a_rows - 1) / a_rows;
   const int tiles_n = (N + kWtWRows - 1) / kWtWRows;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = K / 64;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kWtActStages; ++i) {
+    for (int i = 0; i < 2 * kWtActStages; ++i) {  // 128-row tiles run eight half-size activation stages
       mbar_init(act_full(i), 1);
     }
     for (int i = 0; i < kWtRawStages; ++i) {
@@ -151,21 +158,22 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         int tm, tn;
         tile_coords(t, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int st = it % kWtActStages;
+          const int st = it % act_stages;
           // The stage's previous tenant was K block it - 4; its MMAs' completion is reported once, on
           // the barrier that also hands the block's A stage back to the dequant warps (a commit
           // costs the tensor pipe about as long as a small MMA, so there is one per block, not two).
-          const uint32_t prev = it - kWtActStages;
-          if (it >= kWtActStages && !mbar_wait(a_empty(prev % kWtAStages), (prev / kWtAStages) & 1, abort_flag)) {
+          const uint32_t prev = it - act_stages;
+          if (it >= static_cast<uint32_t>(act_stages) &&
+              !mbar_wait(a_empty(prev % kWtAStages), (prev / kWtAStages) & 1, abort_flag)) {
             wt_report(ws, kStatusTimeoutEmpty, it);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(act_full(st), kWtActStageBytes);
-          tma_load_3d(smem_base + st * kWtActStageBytes, ws->map_a, act_full(st), kb * 64, tm * kWtARows, 0);
-          tma_load_3d(smem_base + st * kWtActStageBytes + 128 * 128, ws->map_a, act_full(st), kb * 64,
-                      tm * kWtARows + 128, 0);
+          mbar_arrive_expect_tx(act_full(st), a_rows * 128);
+          tma_load_3d(smem_base + st * act_pitch, ws->map_a, act_full(st), kb * 64, tm * a_rows, 0);
+          if (a_rows > 128)
+            tma_load_3d(smem_base + st * act_pitch + 128 * 128, ws->map_a, act_full(st), kb * 64, tm * a_rows + 128, 0);
         }
       }
     }
@@ -194,7 +202,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   } else if (warp == 1) {
     // -------- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_instr_desc(1u, 0u, 0u, 0u, 0u, kWtWRows, kWtARows);
+      const uint32_t idesc = make_instr_desc(1u, 0u, 0u, 0u, 0u, kWtWRows, a_rows);
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
@@ -205,8 +213,8 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         }
         tc_fence_after_sync();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int st = it % kWtActStages, as = it % kWtAStages;
-          if (!mbar_wait(act_full(st), (it / kWtActStages) & 1, abort_flag)) {
+          const int st = it % act_stages, as = it % kWtAStages;
+          if (!mbar_wait(act_full(st), (it / act_stages) & 1, abort_flag)) {
             wt_report(ws, kStatusTimeoutFull, it);
             *abort_flag = 1;
             ok = false;
@@ -219,7 +227,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
             break;
           }
           tc_fence_after_sync();
-          const uint32_t b_src = smem_base + st * kWtActStageBytes;
+          const uint32_t b_src = smem_base + st * act_pitch;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_f16_ts(tmem_base, tmem_a + as * kWtAStageColumns + k * 8, make_smem_desc(b_src + k * 32, 16, 1024), idesc,
@@ -247,15 +255,15 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         break;
       }
       tc_fence_after_sync();
-      const int rows_left = M - tm * kWtARows;
-      const int pieces = rows_left >= kWtARows ? kWtARows / kWtOutRows : (rows_left + kWtOutRows - 1) / kWtOutRows;
-      for (int pc = 0; pc < kWtARows / kWtOutRows; ++pc) {
+      const int rows_left = M - tm * a_rows;
+      const int pieces = rows_left >= a_rows ? a_rows / kWtOutRows : (rows_left + kWtOutRows - 1) / kWtOutRows;
+      for (int pc = 0; pc < a_rows / kWtOutRows; ++pc) {
         uint32_t v0[32], v1[32];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + pc * kWtOutRows;
         tmem_ld_32x32(taddr, v0);
         tmem_ld_32x32(taddr + 32, v1);
         tc_wait_ld();
-        if (pc == kWtARows / kWtOutRows - 1) {
+        if (pc == a_rows / kWtOutRows - 1) {
           // the accumulator is in registers / already stored: the next tile's MMAs may start
           tc_fence_before_sync();
           __syncwarp();
@@ -277,7 +285,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
         if (issuer) {
-          const int x = n_off + tn * kWtWRows, y = tm * kWtARows + pc * kWtOutRows;
+          const int x = n_off + tn * kWtWRows, y = tm * a_rows + pc * kWtOutRows;
           for (int p = 0; p < world; ++p) {
             const int dest = (rank + p) % world;  // start with the own buffer, then round the ring
             tma_store_2d(ws->map_out[dest], stage, x, y);

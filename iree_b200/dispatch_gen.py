@@ -182,9 +182,10 @@ def plan_w4a16(function: str, M: int, N: int, K: int, group: int = 128, ldo: Opt
         plan.dispatches.append(Dispatch("b200_w4a16_decode_m%d" % mh, ["a", "wq", "scales", "out", "workspace"],
                                         [M, N, K, ldo, n_offset], (walkers * slices, 1, 1),
                                         (DECODE_THREADS, 1, 1), DECODE_SMEM[mh]))
-    elif group == 128 and K % 128 == 0 and M >= 256 and (ldo * 2) % 16 == 0 and n_offset % 8 == 0:
-        # many rows: the weights are the tensor-memory operand, tiles are 128 weight rows x 256 activation rows,
-        # results leave by TMA stores through an output map in the workspace (one destination here)
+    elif group == 128 and K % 128 == 0 and (ldo * 2) % 16 == 0 and n_offset % 8 == 0:
+        # more than sixteen rows: the weights are the tensor-memory operand, tiles are 128 weight rows x 128
+        # (M <= 128) or 256 activation rows, results leave by TMA stores through an output map in the
+        # workspace (one destination here), which needs pitch and offset on 16-byte boundaries
         tiles = ((M + 255) // 256) * ((N + 127) // 128)
         ws = {"name": "workspace", "bytes": 512 + 8 * 128 + 8 * 8, "zero": True}
         plan.transients.append(ws)

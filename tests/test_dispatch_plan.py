@@ -28,7 +28,9 @@ def test_baseline_plans_pick_the_expected_exports():
     assert p["c3_w8a8_m16"].dispatches[1].bindings == ["out", "a_scale", "w_scale", "workspace"]
     assert p["c4_w4a16_m1"].dispatches[0].export == "b200_w4a16_decode_m8"
     assert p["c4_w4a16_m16"].dispatches[0].export == "b200_w4a16_decode_m16"
-    assert p["c4_w4a16_m128"].dispatches[0].export == "b200_w4a16_gemm"
+    assert p["c4_w4a16_m128"].dispatches[0].export == "b200_w4a16_gemm_wt"      # every M > 16 with an aligned result
+    assert p["c4_w4a16_m128"].dispatches[0].grid == (86, 1, 1)                    # one 128-row activation tile x 86 weight tiles
+    assert dg.plan_w4a16("odd", 100, 264, 256, ldo=270).dispatches[0].export == "b200_w4a16_gemm"   # pitch off the 16-byte grid
     assert p["c5_w4a16_m16"].dispatches[0].grid == (148, 1, 1)            # K = 8192: 74 tile walkers x 2 K slices
     assert p["c5_w4a16_m16"].transients[0]["host_tensor_maps"]["kind"] == "w4a16_decode"
     assert "host_tensor_maps" not in p["c4_w4a16_m16"].transients[0]      # one slice: plain bulk copies, no map

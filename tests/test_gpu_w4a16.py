@@ -44,7 +44,8 @@ def test_weights_in_tensor_memory_variant(ctx):
     integer data over ragged M and N, several tiles per CTA, column slices of a wider result, and
     equal to the shared-memory-operand kernel on the same inputs."""
     rng = np.random.default_rng(61)
-    for (M, N, K) in [(256, 128, 128), (300, 264, 256), (520, 151 * 16, 384), (1024, 384, 1024), (257, 8, 128)]:
+    for (M, N, K) in [(256, 128, 128), (300, 264, 256), (520, 151 * 16, 384), (1024, 384, 1024), (257, 8, 128),
+                      (128, 256, 512), (100, 264, 256), (17, 128, 1024), (129, 136, 128)]:
         a, wq, s = exact_case(rng, M, N, K)
         got = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM_WT)
         want = oracle.w4a16(a, wq, s, threads=THREADS)

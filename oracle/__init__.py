@@ -145,6 +145,27 @@ def x86_64_tile(mmt4d_type: int, M: int, N: int, avx512: bool = True, vnni: bool
     return m0, n0, k0
 
 
+def matmul_narrow_sizes(M: int, N: int):
+    """(narrow_M, narrow_N) as GlobalOptimization/SetEncoding.cpp:101-142 records them on the
+    encoding: a static size below 16 is narrow; when both are, only the smaller is kept (M on a tie)."""
+    nm = M if 0 < M < 16 else None
+    nn = N if 0 < N < 16 else None
+    if nm is not None and nn is not None:
+        if nm <= nn:
+            nn = None
+        else:
+            nm = None
+    return nm, nn
+
+
+def is_narrow_n_result(M: int, N: int) -> bool:
+    """Codegen/Common/EncodingUtils.cpp:206-213: narrow N set and (narrow M unset or larger). The
+    materialisation then swaps the operands and computes the transposed product, so that the narrow
+    dimension becomes the mmt4d's M (MaterializeEncodingIntoPackUnPack.cpp:330-399)."""
+    nm, nn = matmul_narrow_sizes(M, N)
+    return nn is not None and (nm is None or nm > nn)
+
+
 def _as_in(x, t):
     x = np.ascontiguousarray(x)
     if t == TYPE_BF16BF16F32:
@@ -160,6 +181,11 @@ def matmul_port(t: int, lhs, rhs, tile=None, acc=None) -> np.ndarray:
     M, K = lhs.shape
     K2, N = rhs.shape
     assert K == K2
+    if tile is None and is_narrow_n_result(M, N):
+        # narrow N: out^T[N, M] = rhs^T[N, K] x lhs^T[K, M], tiles chosen for the swapped problem
+        swapped = matmul_port(t, np.ascontiguousarray(rhs.T), np.ascontiguousarray(lhs.T), tile=x86_64_tile(t, N, M),
+                              acc=None if acc is None else np.ascontiguousarray(np.asarray(acc).T))
+        return np.ascontiguousarray(swapped.T)
     m0, n0, k0 = tile or x86_64_tile(t, M, N)
     out = np.zeros((M, N), _ACC_DTYPE[t]) if acc is None else np.ascontiguousarray(acc).copy()
     rc = port_lib().oracle_matmul_data_tiled(C.c_int(t), C.c_int64(M), C.c_int64(N), C.c_int64(K),

@@ -59,6 +59,26 @@ def test_x86_64_tile_choice():
 
 
 @needs_ref
+def test_narrow_n_products_swap_their_operands(built):
+    """SetEncoding records at most one narrow dimension (M wins a tie); a narrow-N result is
+    materialised as the transposed product with the operands swapped, which must give the same
+    numbers as the plain product."""
+    assert oracle.matmul_narrow_sizes(1, 1000) == (1, None) and oracle.matmul_narrow_sizes(1000, 1) == (None, 1)
+    assert oracle.matmul_narrow_sizes(8, 8) == (8, None) and oracle.matmul_narrow_sizes(9, 3) == (None, 3)
+    assert oracle.matmul_narrow_sizes(16, 15) == (None, 15) and oracle.matmul_narrow_sizes(64, 64) == (None, None)
+    assert oracle.is_narrow_n_result(1000, 1) and oracle.is_narrow_n_result(9, 3)
+    assert not oracle.is_narrow_n_result(3, 9) and not oracle.is_narrow_n_result(8, 8)
+    assert oracle.x86_64_tile(oracle.TYPE_S8S8S32, 3, 1000) == (4, 16, 2)       # the swapped problem of [1000, K] x [K, 3]
+    rng = np.random.default_rng(12)
+    for (M, N, K) in [(1000, 1, 64), (37, 3, 129), (9, 3, 10), (10, 1, 10)]:
+        a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        b = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        want = a.astype(np.int32) @ b.astype(np.int32)
+        assert (oracle.matmul_port(oracle.TYPE_S8S8S32, a, b) == want).all()
+        acc = rng.integers(-1000, 1000, (M, N), dtype=np.int32)
+        assert (oracle.matmul_port(oracle.TYPE_S8S8S32, a, b, acc=acc) == want + acc).all()
+
+
 @pytest.mark.parametrize("dtype", [np.int8, np.float16, np.float32, np.int32])
 def test_pack_unpack_match_reference_ukernels(built, dtype):
     rng = np.random.default_rng(3)

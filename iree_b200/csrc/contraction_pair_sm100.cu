@@ -59,7 +59,9 @@ __device__ __forceinline__ void gemm_pair_body(void* __restrict__ c_ptr, const f
   const bool bad = s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batch <= 0 || s.bn < 64 || s.bn > kMaxBN || (s.bn & 63) ||
                    (s.K * kElem) % 16 != 0 || (gridDim.x & 1) ||
                    (s.b_layout == kBLayoutKN && ((s.N * kElem) % 16 != 0 || half_bn % kChunkN != 0));
+  grid_launch_dependents();
   if (bad) {
+    grid_dependency_wait();
     if (threadIdx.x == 0) report(ws, kStatusBadArgument, 1);
     return;
   }
@@ -92,6 +94,7 @@ __device__ __forceinline__ void gemm_pair_body(void* __restrict__ c_ptr, const f
   cluster_sync_all();  // barriers of both CTAs exist before anything is signalled across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  grid_dependency_wait();  // as in the 1-CTA kernel: global memory is touched only below this line
 
   auto tile_coords = [&](int t, int& b, int& tm, int& tn) {
     b = t / tiles_per_batch;
@@ -188,6 +191,7 @@ __device__ __forceinline__ void gemm_pair_body(void* __restrict__ c_ptr, const f
     const int q = warp & 3;
     constexpr int kOutBytes = (EPI == kEpiRaw) ? 4 : 2;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 16 == 0) && ((s.N * kOutBytes) % 16 == 0);
+    const bool wide_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 32 == 0) && ((s.N * kOutBytes) % 32 == 0);
     uint32_t local_tile = 0;
     for (int t = pair; t < num_tiles; t += num_pairs, ++local_tile) {
       int b, tm, tn;
@@ -211,7 +215,7 @@ __device__ __forceinline__ void gemm_pair_body(void* __restrict__ c_ptr, const f
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxBN + c, v);
         tc_wait_ld();
         const int col0 = tn * s.bn + c;
-        if (row < s.M && col0 < s.N) store_row_chunk<KIND, EPI>(v, c_ptr, row_offset, col0, s.N, rs, col_scale, vec_ok);
+        if (row < s.M && col0 < s.N) store_row_chunk<KIND, EPI>(v, c_ptr, row_offset, col0, s.N, rs, col_scale, vec_ok, wide_ok);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -106,13 +106,30 @@ struct KindTraits<kI8> {
   static constexpr uint32_t kFormat = 1, kCFormat = 2;
 };
 
-// The epilogue for one thread: 32 consecutive columns of one output row.
+// One 32-byte store. A warp's epilogue store touches 32 different rows whatever its width, and the
+// load/store unit's cost is per row touched: twice the bytes per instruction halves the time.
+__device__ __forceinline__ void st_global_256(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e,
+                                              uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d),
+               "r"(e), "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+
+// The epilogue for one thread: 32 consecutive columns of one output row. vec_ok: 16-byte stores are
+// aligned (base and row pitch); wide_ok: 32-byte ones are.
 template <int KIND, int EPI>
 __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], void* c_base, int64_t row_offset, int col0,
-                                                int N, float row_scale, const float* col_scale, bool vec_ok) {
+                                                int N, float row_scale, const float* col_scale, bool vec_ok,
+                                                bool wide_ok = false) {
   if constexpr (EPI == kEpiRaw) {
     // Raw 32-bit accumulator (i32 for kind::i8, f32 for kind::f16).
     uint32_t* out = reinterpret_cast<uint32_t*>(c_base) + row_offset + col0;
+    if (wide_ok && col0 + 31 < N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        st_global_256(out + j, v[j], v[j + 1], v[j + 2], v[j + 3], v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
       if (vec_ok && col0 + j + 3 < N) {
@@ -141,6 +158,14 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], void* c
       }
     }
     uint16_t* out = reinterpret_cast<uint16_t*>(c_base) + row_offset + col0;
+    if (wide_ok && col0 + 31 < N) {
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) w[j] = h[2 * j] | (uint32_t(h[2 * j + 1]) << 16);
+      st_global_256(out, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+      st_global_256(out + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       if (vec_ok && col0 + j + 7 < N) {
@@ -199,7 +224,11 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   bool bad = s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batch <= 0 || s.bn < 16 || s.bn > kMaxBN || (s.bn & 31) ||
              (s.K * kElem) % 16 != 0 || (s.b_layout == kBLayoutKN && ((s.N * kElem) % 16 != 0 || s.bn % kChunkN != 0)) ||
              S < 1 || S > kMaxSplits || S > (s.K + kBK - 1) / kBK;
+  // The next dispatch on the stream may be launched from here on (it waits on the device for this
+  // one to complete before it touches memory; see grid_dependency_wait below).
+  grid_launch_dependents();
   if (bad) {
+    grid_dependency_wait();
     if (threadIdx.x == 0) report(ws, kStatusBadArgument, 0);
     return;
   }
@@ -238,6 +267,10 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Under a programmatic dependency this CTA was launched while the dispatch ahead was still
+  // running: everything above touched only this CTA's own shared and tensor memory; nothing below
+  // (maps, operands, scales, result, status words) is read or written before that dispatch is complete.
+  grid_dependency_wait();
 
   // m fastest inside a column of tiles: consecutive CTAs share the B tile and walk down A.
   auto tile_coords = [&](int t, int& b, int& tm, int& tn) {
@@ -344,6 +377,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
     // 16-byte stores need a 16-byte aligned row pitch and base.
     constexpr int kOutBytes = (EPI == kEpiRaw) ? 4 : 2;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 16 == 0) && ((s.N * kOutBytes) % 16 == 0);
+    const bool wide_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 32 == 0) && ((s.N * kOutBytes) % 32 == 0);
     uint32_t local_tile = 0;
     for (int w = blockIdx.x; w < num_items; w += gridDim.x, ++local_tile) {
       int t, kb0, kb1, b, tm, tn;
@@ -429,7 +463,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxBN + c, v);
         tc_wait_ld();
         const int col0 = tn * s.bn + c;
-        if (row < s.M && col0 < s.N) store_row_chunk<KIND, EPI>(v, c_ptr, row_offset, col0, s.N, rs, col_scale, vec_ok);
+        if (row < s.M && col0 < s.N) store_row_chunk<KIND, EPI>(v, c_ptr, row_offset, col0, s.N, rs, col_scale, vec_ok, wide_ok);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -1637,6 +1637,19 @@ iree_b200_status_t iree_b200_matmul_prepare(iree_b200_context_t* context, const 
   return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
 }
 
+// A dispatch of an export that orders itself on the device (it waits there for the dispatch ahead
+// before it touches global memory): launched early when the context allows dispatch overlap.
+static iree_b200_status_t dispatch_self_ordering(iree_b200_context_t* context, int32_t ordinal, uint32_t binding_count,
+                                                 uint32_t constant_count, uint32_t grid_x, uint32_t grid_y = 1) {
+  auto* cb = context->command_buffer;
+  const bool saved_overlap = cb->overlap;  // what the caller set on the command buffer itself survives
+  cb->overlap = saved_overlap || context->dispatch_overlap;
+  const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(cb, context->executable, ordinal, binding_count,
+                                                                      constant_count, grid_x, grid_y, 1);
+  cb->overlap = saved_overlap;
+  return st;
+}
+
 iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
                                         const void* lhs, const void* rhs, void* out, const float* row_scale,
                                         const float* col_scale, void* workspace, int32_t tile_n) {
@@ -1692,7 +1705,9 @@ iree_b200_status_t iree_b200_matmul_run(iree_b200_context_t* context, const iree
     B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 2, bindings));
   }
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
-  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, requant ? 4 : 2, 6, grid, 1, 1);
+  // These exports set up their barriers and tensor memory before they wait, on the device, for the
+  // dispatch ahead of them: like the decode exports they may be launched early.
+  return dispatch_self_ordering(context, ord, requant ? 4 : 2, 6, grid);
 }
 
 iree_b200_status_t iree_b200_matmul(iree_b200_context_t* context, const iree_b200_matmul_params_t* params,
@@ -2087,7 +2102,7 @@ static iree_b200_status_t w4_run_wt(iree_b200_context_t* context, const iree_b20
   const int64_t tiles = static_cast<int64_t>((params->M + 255) / 256) * ((params->N + 127) / 128);
   const int32_t ord = iree_hal_b200_executable_lookup(context->executable, "b200_w4a16_gemm_wt");
   if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_w4a16_gemm_wt missing from the executable");
-  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 3, 7, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);
+  return dispatch_self_ordering(context, ord, 3, 7, static_cast<uint32_t>(tiles < sms ? tiles : sms));
 }
 
 iree_b200_status_t iree_b200_w4a16_prepare_push(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
@@ -2205,7 +2220,7 @@ iree_b200_status_t iree_b200_w4a16_run(iree_b200_context_t* context, const iree_
     const int tile_rows = params->M >= 256 ? 256 : 128;  // the kernel's 256-row variant
     const int64_t tiles = static_cast<int64_t>((params->M + tile_rows - 1) / tile_rows) * ((params->N + tile_n - 1) / tile_n);
     const int32_t ord = iree_hal_b200_executable_lookup(exe, "b200_w4a16_gemm");
-    return iree_hal_b200_command_buffer_dispatch(cb, exe, ord, 3, 6, static_cast<uint32_t>(tiles < sms ? tiles : sms), 1, 1);
+    return dispatch_self_ordering(context, ord, 3, 6, static_cast<uint32_t>(tiles < sms ? tiles : sms));
   }
   if (variant == IREE_B200_W4A16_GEMM_WT) return w4_run_wt(context, params, scales, out, workspace, 1, 0, 0);
   if (variant == IREE_B200_W4A16_GENERIC) {

@@ -90,7 +90,10 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || bn < 16 || bn > kAccColumns || (bn & 15);
+  // The next dispatch on the stream may be launched from here on; it orders itself on the device.
+  grid_launch_dependents();
   if (bad) {
+    grid_dependency_wait();
     if (threadIdx.x == 0) w4_report(ws, kStatusBadArgument, 0);
     return;
   }
@@ -123,6 +126,9 @@ __device__ __forceinline__ void w4gemm_body(const __half* __restrict__ scales, _
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Launched early under a programmatic dependency: only this CTA's shared and tensor memory was
+  // touched above; global memory is read and written only once the dispatch ahead is complete.
+  grid_dependency_wait();
 
   auto tile_coords = [&](int t, int& tm, int& tn) {
     tn = t / tiles_m;

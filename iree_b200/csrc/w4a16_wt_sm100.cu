@@ -99,7 +99,10 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool bad = M <= 0 || N <= 0 || K <= 0 || (K & 127) || world < 1 || world > kWtMaxDestinations || (n_off & 7);
+  // The next dispatch on the stream may be launched from here on; it orders itself on the device.
+  grid_launch_dependents();
   if (bad) {
+    grid_dependency_wait();
     if (threadIdx.x == 0) wt_report(ws, kStatusBadArgument, 0);
     return;
   }
@@ -140,6 +143,9 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Launched early under a programmatic dependency: only this CTA's shared and tensor memory was
+  // touched above; global memory is read and written only once the dispatch ahead is complete.
+  grid_dependency_wait();
   const uint32_t tmem_a = tmem_base + kWtARows;  // A stages follow the accumulator columns
 
   // Consecutive tiles of a CTA share the weight rows and walk down the activations.

@@ -311,3 +311,57 @@ def test_graph_mode_replays_recorded_dispatches(ctx):
     graph.release()
     for x in (da, db, c1, c2, ws):
         x.free()
+
+
+@pytest.mark.parametrize("M,graph", [(128, False), (512, True), (16, True), (300, False)])
+def test_overlapped_matmul_chain_equals_the_serial_chain(ctx, M, graph):
+    """A chain of f16 matmuls in which every step's left operand is the previous step's result
+    (N = K), dispatched with overlap (programmatic dependent launch; stream mode and graph mode): a
+    kernel may be launched, and set up its barriers and tensor memory, before the one ahead has
+    finished, but must not read an operand early. The results are bit-identical to the serial
+    chain (1-CTA kernel, its few-rows variant and the CTA-pair kernel)."""
+    from iree_b200 import runtime as rt
+    rng = np.random.default_rng(77 + M)
+    N = K = 1024
+    steps = 10
+    a0 = (rng.standard_normal((M, K)) * 0.5).astype(np.float16)
+    rhs = [ctx.to_device((rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16)) for _ in range(3)]
+    bufs = [ctx.to_device(a0), ctx.alloc(M * N * 2), ctx.alloc(M * N * 2)]
+    p = MatmulParams(ib.KIND_F16, ib.EPILOGUE_CAST, M, N, K, 1, ib.RHS_KN, 0, 0)
+    # one workspace (its maps name the operands) per (source, right-hand side) pair in use
+    prepared = {}
+
+    def chain():
+        bufs[0].upload(a0)
+        if graph:
+            ctx.begin_graph()
+        src = 0
+        for i in range(steps):
+            dst = 1 + (i % 2)
+            key = (src, i % 3)
+            if key not in prepared:
+                ws = ctx.matmul_workspace(p)
+                prepared[key] = (ws, ctx.matmul_prepare(p, bufs[src], rhs[i % 3], ws))
+            ws, bn = prepared[key]
+            ctx.matmul_run(p, bufs[src], rhs[i % 3], bufs[dst], ws, bn)
+            src = dst
+        if graph:
+            g = ctx.end_graph()
+            g.execute()
+            ctx.synchronize()
+            g.release()
+        for ws, _ in prepared.values():
+            ctx.workspace_status(ws)
+        return bufs[src].download(np.float16, (M, N))
+
+    chain()                       # every workspace is prepared outside a recording
+    serial = chain()
+    ctx.set_dispatch_overlap(True)
+    try:
+        overlapped = chain()
+    finally:
+        ctx.set_dispatch_overlap(False)
+    assert np.isfinite(serial.astype(np.float32)).all() and np.abs(serial.astype(np.float32)).max() > 1e-3
+    assert np.array_equal(serial.view(np.uint16), overlapped.view(np.uint16))
+    for b in bufs + rhs + [ws for ws, _ in prepared.values()]:
+        b.free()

@@ -479,6 +479,9 @@ iree_b200_status_t iree_b200_context_set_reserved_sms(iree_b200_context_t* conte
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16F32 0x05
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16BF16 0x06
 #define IREE_B200_UK_FLAG_MMT4D_ACCUMULATE 0x100
+/* No counterpart in the reference: take the path that brings both operands back to row-major first
+ * (un-tile, row-major contraction, re-tile) even where the kernel that reads tiled operands applies. */
+#define IREE_B200_UK_FLAG_MMT4D_UNTILE 0x10000
 #define IREE_B200_UK_FLAG_PACK_TYPE_MASK 0xFF
 #define IREE_B200_UK_FLAG_PACK_TYPE_F32F32 0x01
 #define IREE_B200_UK_FLAG_PACK_TYPE_I8I8 0x02
@@ -502,10 +505,15 @@ iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void*
                                        int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,
                                        int64_t in_size2, int64_t in_size3, int64_t out_size0, int64_t out_size1,
                                        uint32_t flags);
-/* iree_uk_mmt4d: out[M,N,M0,N0] (+)= lhs[M,K,M0,K0] x rhs[N,K,N0,K0]. The tiled operands are
- * brought to row-major by the unpack kernel, multiplied by the tensor-core contraction kernel
- * and the accumulator is tiled (and added, with ACCUMULATE) by the pack kernel; `workspace` is a
- * zero-filled device buffer of iree_b200_uk_mmt4d_workspace_bytes() bytes, 256-byte aligned.
+/* iree_uk_mmt4d: out[M,N,M0,N0] (+)= lhs[M,K,M0,K0] x rhs[N,K,N0,K0]
+ * (runtime/src/iree/builtins/ukernel/mmt4d.c:55-141). Tiles whose rows are 32 bytes in both operands
+ * (i8 16x16x2, the x86-64 VNNI tile; f16 / bf16 16x16x1), at 16-byte aligned operand addresses and
+ * pitches and 32-byte aligned results, are multiplied as they are by one kernel: 16-byte asynchronous
+ * copies land the tiled operands in shared memory in a layout the tensor core reads directly, and the
+ * epilogue writes whole [M0,N0] tiles with ACCUMULATE folded in. Other tile shapes are brought to row-major by the
+ * unpack kernel, multiplied by the row-major contraction kernel, and the accumulator is tiled (and
+ * added, with ACCUMULATE) by the pack kernel. `workspace` is a zero-filled device buffer of
+ * iree_b200_uk_mmt4d_workspace_bytes() bytes, 256-byte aligned.
  * Types: S8S8S32 (bit-exact), F16F16F32, BF16BF16F32, F16F16F16, BF16BF16BF16 (f32 accumulation
  * in tensor-core order; ACCUMULATE only with 32-bit outputs); other types: UNIMPLEMENTED. The
  * 16-bit-output types always accumulate in f32 and round once at the end, i.e. they behave as the

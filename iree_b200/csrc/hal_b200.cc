@@ -1248,6 +1248,11 @@ const EntryDecl kEntries[] = {
     {"b200_w4a16_gemm_wt", {512, 1, 1}, kW4WtSmemBytes},
     {"b200_wait_arrivals", {32, 1, 1}, 0},
     {"b200_w4a16_generic", {256, 1, 1}, 0},
+    {"b200_mmt4d_s8s8s32", {512, 1, 1}, kGemmSmemBytes},
+    {"b200_mmt4d_f16f16f32", {512, 1, 1}, kGemmSmemBytes},
+    {"b200_mmt4d_f16f16f16", {512, 1, 1}, kGemmSmemBytes},
+    {"b200_mmt4d_bf16bf16f32", {512, 1, 1}, kGemmSmemBytes},
+    {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kGemmSmemBytes},
     {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b16", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b32", {256, 1, 1}, kTilingStageBytes},
@@ -2453,6 +2458,51 @@ size_t iree_b200_uk_mmt4d_workspace_bytes(int64_t M, int64_t N, int64_t K, int32
          up256(m * n * t.out_bytes);
 }
 
+// The kernel that multiplies tiled operands as they are (mmt4d_sm100.cu) takes tiles whose rows are 32
+// bytes in both operands (i8 16x16x2, f16 / bf16 16x16x1) at 16-byte aligned addresses and pitches and
+// 32-byte aligned results. True when it was dispatched; other shapes go through the un-tiling path.
+static iree_b200_status_t mmt4d_direct(iree_b200_context_t* context, const Mmt4dTypes& t, const uint8_t* lhs,
+                                       int64_t lhs_stride0, const uint8_t* rhs, int64_t rhs_stride0, uint8_t* out,
+                                       int64_t out_stride0, int64_t M1, int64_t N1, int64_t K1, int32_t M0, int32_t N0,
+                                       int32_t K0, bool accumulate, void* workspace, bool* dispatched) {
+  *dispatched = false;
+  const int es = t.elem_bytes;
+  if (M0 != 16 || N0 != 16 || K0 != (es == 1 ? 2 : 1) || K1 <= 0) return IREE_B200_STATUS_OK;
+  if ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15) return IREE_B200_STATUS_OK;
+  if (reinterpret_cast<uintptr_t>(out) & 31) return IREE_B200_STATUS_OK;
+  if ((lhs_stride0 * es) % 16 || (rhs_stride0 * es) % 16 || (out_stride0 * t.out_bytes) % 32) return IREE_B200_STATUS_OK;
+  if (lhs_stride0 <= 0 || rhs_stride0 <= 0 || !fits_i32(lhs_stride0) || !fits_i32(rhs_stride0) || !fits_i32(out_stride0))
+    return IREE_B200_STATUS_OK;
+  const int sms = usable_sms(context);
+  const int run = 32 / es;                      // elements of one tile row; the product's row / column unit
+  const int64_t rows = M1 * run, cols = N1 * run;  // extents of the product the tensor core computes
+  const int64_t tiles_m = (rows + 127) / 128;
+  int bn = 0;
+  double best = 0;
+  for (int w = 256; w >= 32; w -= 32) {
+    const int64_t tiles = tiles_m * ((cols + w - 1) / w);
+    const double cost = static_cast<double>((tiles + sms - 1) / sms) * (400.0 + w);  // the GEMM kernels' wave model
+    if (!bn || cost < best * 0.9999) bn = w, best = cost;
+  }
+  const int64_t tiles = tiles_m * ((cols + bn - 1) / bn);
+  const uint32_t grid = static_cast<uint32_t>(tiles < sms ? tiles : sms);
+  const char* name = t.kind == IREE_B200_KIND_I8
+                         ? "b200_mmt4d_s8s8s32"
+                         : t.kind == IREE_B200_KIND_F16 ? (t.out_bytes == 4 ? "b200_mmt4d_f16f16f32" : "b200_mmt4d_f16f16f16")
+                                                        : (t.out_bytes == 4 ? "b200_mmt4d_bf16bf16f32" : "b200_mmt4d_bf16bf16bf16");
+  const int32_t ord = iree_hal_b200_executable_lookup(context->executable, name);
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export %s missing from the executable", name);
+  iree_hal_b200_descriptor_set_binding_t bindings[4] = {
+      {0, const_cast<uint8_t*>(lhs)}, {1, const_cast<uint8_t*>(rhs)}, {2, out}, {3, workspace}};
+  const int32_t constants[7] = {(int32_t)M1,          (int32_t)N1,          (int32_t)K1, (int32_t)lhs_stride0,
+                                (int32_t)rhs_stride0, (int32_t)out_stride0, bn | (accumulate ? 1 << 16 : 0)};
+  auto* cb = context->command_buffer;
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
+  *dispatched = true;
+  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 4, 7, grid, 1, 1);
+}
+
 iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* lhs_buffer, int64_t lhs_offset,
                                       int64_t lhs_stride0, const void* rhs_buffer, int64_t rhs_offset,
                                       int64_t rhs_stride0, void* out_buffer, int64_t out_offset, int64_t out_stride0,
@@ -2462,7 +2512,8 @@ iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* 
   Mmt4dTypes t;
   if (!mmt4d_types(flags, &t))
     return fail(IREE_B200_STATUS_UNIMPLEMENTED, "mmt4d type 0x%x has no tensor-core kernel", flags & 0xFF);
-  if (flags & ~(IREE_B200_UK_FLAG_MMT4D_TYPE_MASK | IREE_B200_UK_FLAG_MMT4D_ACCUMULATE | 0x200u | 0x400u))
+  if (flags & ~(IREE_B200_UK_FLAG_MMT4D_TYPE_MASK | IREE_B200_UK_FLAG_MMT4D_ACCUMULATE | 0x200u | 0x400u |
+                IREE_B200_UK_FLAG_MMT4D_UNTILE))
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown mmt4d flags 0x%x", flags);
   const bool accumulate = flags & IREE_B200_UK_FLAG_MMT4D_ACCUMULATE;
   if (accumulate && t.out_bytes != 4)
@@ -2483,6 +2534,12 @@ iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* 
   const uint8_t* lhs = static_cast<const uint8_t*>(lhs_buffer) + lhs_offset * t.elem_bytes;
   const uint8_t* rhs = static_cast<const uint8_t*>(rhs_buffer) + rhs_offset * t.elem_bytes;
   uint8_t* out = static_cast<uint8_t*>(out_buffer) + out_offset * t.out_bytes;
+  if (!(flags & IREE_B200_UK_FLAG_MMT4D_UNTILE)) {
+    bool dispatched = false;
+    B200_RETURN_IF_ERROR(mmt4d_direct(context, t, lhs, lhs_stride0, rhs, rhs_stride0, out, out_stride0, M, N, K, M0, N0, K0,
+                                      accumulate, workspace, &dispatched));
+    if (dispatched) return IREE_B200_STATUS_OK;
+  }
   if (k > 0) {
     B200_RETURN_IF_ERROR(tiling_dispatch(context, false, t.elem_bytes, lhs, lhs_rm, m, k, k, 1, M, K, M0, K0, lhs_stride0, 0, 0));
     B200_RETURN_IF_ERROR(tiling_dispatch(context, false, t.elem_bytes, rhs, rhs_rm, n, k, k, 1, N, K, N0, K0, rhs_stride0, 0, 0));

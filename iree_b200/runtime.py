@@ -444,6 +444,7 @@ UK_PACK_TYPE = {1: 0x02, 2: 0x04, 4: 0x03}  # element bytes -> I8I8 / F16F16 / I
 UK_TRANSPOSE_INNER, UK_TRANSPOSE_OUTER = 0x100, 0x200
 UK_MMT4D_S8S8S32, UK_MMT4D_F16F16F32, UK_MMT4D_F16F16F16 = 0x02, 0x03, 0x04
 UK_MMT4D_BF16BF16F32, UK_MMT4D_BF16BF16BF16, UK_MMT4D_ACCUMULATE = 0x05, 0x06, 0x100
+UK_MMT4D_UNTILE = 0x10000   # this library's own: take the un-tiling path even where the tiled-operand kernel applies
 
 
 def pack_numpy(ctx: Context, x: np.ndarray, tile, transpose_inner=False, transpose_outer=False, padding: int = 0,

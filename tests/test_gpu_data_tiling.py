@@ -206,3 +206,71 @@ def test_data_tiled_matmul_chain_on_the_gpu_equals_the_reference_chain(ctx):
     got = unpack_numpy(ctx, po, (M, N))
     want = oracle.matmul_ref(oracle.TYPE_S8S8S32, a, b) if oracle.have_ref() else oracle.matmul_port(oracle.TYPE_S8S8S32, a, b)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("type_flag,tile", [(rt.UK_MMT4D_S8S8S32, (16, 16, 2)), (rt.UK_MMT4D_F16F16F32, (16, 16, 1)),
+                                            (rt.UK_MMT4D_BF16BF16BF16, (16, 16, 1))])
+def test_mmt4d_on_tiled_operands_is_one_launch_and_equals_the_untiling_path(ctx, type_flag, tile):
+    """The kernel that reads tiled operands as they are (one launch) against the path that un-tiles both
+    operands first (four launches): many tiles per CTA, K1 tails, outer extents that do not fill a CTA
+    tile, operands and result inside larger buffers (offsets and outer strides), ACCUMULATE.
+    Integer results are identical; float results are sums of the same products in another order."""
+    m0, n0, k0 = tile
+    rng = np.random.default_rng(5)
+    i8 = type_flag == rt.UK_MMT4D_S8S8S32
+    bf = type_flag == rt.UK_MMT4D_BF16BF16BF16
+    idt = np.int8 if i8 else np.uint16 if bf else np.float16
+    odt = np.int32 if i8 else np.uint16 if bf else np.float32
+
+    def draw(shape, K):
+        if i8:
+            return rng.integers(-128, 128, shape, dtype=np.int8)
+        x = (rng.standard_normal(shape) / np.sqrt(K)).astype(np.float32)
+        return (x.view(np.uint32) >> 16).astype(np.uint16) if bf else x.astype(np.float16)
+
+    for (M, N, K, pad) in [(9, 21, 130, 0), (40, 70, 257, 48), (3, 300, 64, 16), (33, 1, 1, 0)]:
+        lhs, rhs = draw((M, K, m0, k0), K * k0), draw((N, K, n0, k0), K * k0)
+        # rows of outer tiles `pad` elements apart from tight, operands 64 elements into their buffers
+        ls, rs, os_ = K * m0 * k0 + pad, K * n0 * k0 + pad, N * m0 * n0 + pad
+        lbuf = np.zeros(64 + M * ls, idt); rbuf = np.zeros(64 + N * rs, idt)
+        for i in range(M):
+            lbuf[64 + i * ls: 64 + i * ls + K * m0 * k0] = lhs[i].ravel()
+        for i in range(N):
+            rbuf[64 + i * rs: 64 + i * rs + K * n0 * k0] = rhs[i].ravel()
+        acc = rng.integers(-10 ** 6, 10 ** 6, (M, N, m0, n0)).astype(np.int32) if i8 else rng.standard_normal((M, N, m0, n0)).astype(np.float32)
+        dl, dr = ctx.to_device(lbuf), ctx.to_device(rbuf)
+        results = {}
+        for accumulate in ((False, True) if not bf else (False,)):
+            for untile in (False, True):
+                obuf = np.full(64 + M * os_, 0x55, odt)
+                if accumulate:
+                    for i in range(M):
+                        obuf[64 + i * os_: 64 + i * os_ + N * m0 * n0] = acc[i].ravel().view(odt)
+                do = ctx.to_device(obuf)
+                flags = type_flag | (rt.UK_MMT4D_ACCUMULATE if accumulate else 0) | (rt.UK_MMT4D_UNTILE if untile else 0)
+                ws = ctx.uk_mmt4d_workspace(M, N, K, m0, n0, k0, flags)
+                before = ctx.launch_count
+                ctx.uk_mmt4d(dl, 64, ls, dr, 64, rs, do, 64, os_, M, N, K, m0, n0, k0, flags, ws)
+                launches = ctx.launch_count - before
+                ctx.workspace_status(ws)
+                assert launches == (4 if untile else 1), (M, N, K, untile, launches)
+                got = do.download(odt, (64 + M * os_,))
+                assert (got[:64] == 0x55).all()
+                tiles = np.stack([got[64 + i * os_: 64 + i * os_ + N * m0 * n0] for i in range(M)]).reshape(M, N, m0, n0)
+                if pad:
+                    gaps = np.stack([got[64 + i * os_ + N * m0 * n0: 64 + (i + 1) * os_] for i in range(M)])
+                    assert (gaps == 0x55).all()
+                results[(accumulate, untile)] = tiles
+                do.free(); ws.free()
+            a, b = results[(accumulate, False)], results[(accumulate, True)]
+            if i8:
+                assert np.array_equal(a, b), (M, N, K, accumulate)
+            elif bf:
+                fa, fb = (a.astype(np.uint32) << 16).view(np.float32), (b.astype(np.uint32) << 16).view(np.float32)
+                assert np.allclose(fa, fb, rtol=RTOL, atol=ATOL), (M, N, K)
+            else:
+                assert np.allclose(a, b, rtol=1e-4, atol=1e-4), (M, N, K, accumulate)
+        if i8:
+            want = oracle.mmt4d_port(oracle.TYPE_S8S8S32, lhs, rhs, acc)
+            assert np.array_equal(results[(True, False)], want), (M, N, K)
+        dl.free(); dr.free()

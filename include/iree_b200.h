@@ -490,6 +490,9 @@ iree_b200_status_t iree_b200_context_set_reserved_sms(iree_b200_context_t* conte
 #define IREE_B200_UK_FLAG_PACK_TYPE_BF16BF16 0x05
 #define IREE_B200_UK_FLAG_PACK_TRANSPOSE_INNER 0x100
 #define IREE_B200_UK_FLAG_PACK_TRANSPOSE_OUTER 0x200
+/* No counterpart in the reference (pack and unpack): take the kernels that stage regions in shared
+ * memory even where the shape allows the copy to be done by the TMA unit alone. */
+#define IREE_B200_UK_FLAG_PACK_NO_TMA 0x40000
 /* iree_uk_pack: row-major [in_size0, in_size1] -> tiled [out_size0..3], ragged edge filled with
  * the low bytes of padding_value. out_stride1 must equal out_size2 * out_size3 (pack.c:72). */
 iree_b200_status_t iree_b200_uk_pack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,

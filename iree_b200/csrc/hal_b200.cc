@@ -1253,6 +1253,7 @@ const EntryDecl kEntries[] = {
     {"b200_mmt4d_f16f16f16", {512, 1, 1}, kGemmSmemBytes},
     {"b200_mmt4d_bf16bf16f32", {512, 1, 1}, kGemmSmemBytes},
     {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kGemmSmemBytes},
+    {"b200_tiling_tma", {32, 1, 1}, 1024 + 8 * 16384 + 128},
     {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b16", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b32", {256, 1, 1}, kTilingStageBytes},
@@ -1269,6 +1270,9 @@ struct iree_b200_context_t {
   iree_hal_b200_executable_t* executable = nullptr;
   iree_hal_b200_command_buffer_t* command_buffer = nullptr;
   void* templates = nullptr;  // device copy of two template tensor maps per element size: [f16 A, f16 B, bf16.., i8..]
+  // pack / unpack by TMA: three rank-4 template maps (1-, 2-, 4-byte elements) in the first 4 KiB, then 256 bytes
+  // per CTA in which the kernel builds its own two maps
+  void* tiling_scratch = nullptr;
   // Grow-only device staging area for the host-buffer entry points, so that repeated calls do
   // not pay for cuMemAlloc / cuMemFree.
   void* arena = nullptr;
@@ -1462,6 +1466,7 @@ void iree_b200_context_release(iree_b200_context_t* context) {
   if (!context) return;
   if (context->device) iree_hal_b200_device_synchronize(context->device);
   if (context->templates) iree_hal_b200_buffer_free(context->device, context->templates);
+  if (context->tiling_scratch) iree_hal_b200_buffer_free(context->device, context->tiling_scratch);
   if (context->arena) iree_hal_b200_buffer_free(context->device, context->arena);
   iree_hal_b200_command_buffer_release(context->command_buffer);
   iree_hal_b200_executable_release(context->executable);
@@ -2356,6 +2361,75 @@ uint32_t tiling_grid(int64_t o0, int64_t o1, int64_t o2, int64_t o3, uint32_t fl
   return static_cast<uint32_t>(blocks < cap ? blocks : cap);
 }
 
+// pack / unpack as a pure TMA copy (tiling_tma_sm100.cu), for the shapes it takes: tiles not transposed
+// inside, tile rows of whole 16-byte pieces, a matrix the tiles cover exactly, 16-byte aligned addresses
+// and pitches, no accumulation. Everything else goes to the staging kernels.
+constexpr uint32_t kTilingNoTma = IREE_B200_UK_FLAG_PACK_NO_TMA;  // take the staging kernel whatever the shape
+iree_b200_status_t tiling_by_tma(iree_b200_context_t* ctx, bool pack, int es, const void* in, void* out, int64_t rm_size0,
+                                 int64_t rm_size1, int64_t rm_stride0, int64_t rm_stride1, int64_t t0, int64_t t1,
+                                 int64_t t2, int64_t t3, int64_t t_stride0, uint32_t kernel_flags, bool* dispatched) {
+  *dispatched = false;
+  const bool ti = kernel_flags & kUkTransposeInner, to = kernel_flags & kUkTransposeOuter;
+  if (ti || (kernel_flags & (kTilingAccumulateI32 | kTilingAccumulateF32)) || rm_stride1 != 1) return IREE_B200_STATUS_OK;
+  const int64_t outer0 = to ? t1 : t0, outer1 = to ? t0 : t1;  // tiles along matrix rows / columns
+  if (outer0 * t2 != rm_size0 || outer1 * t3 != rm_size1) return IREE_B200_STATUS_OK;
+  if ((t3 * es) % 16 || t3 > 256 || t2 > 256 || t2 * t3 * es > 16384) return IREE_B200_STATUS_OK;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return IREE_B200_STATUS_OK;
+  // Pitches in bytes of (tile row, o1 step, o0 step) on both sides.
+  const uint64_t tiled[3] = {static_cast<uint64_t>(t3) * es, static_cast<uint64_t>(t2) * t3 * es,
+                             static_cast<uint64_t>(t_stride0) * es};
+  const uint64_t row_pitch = static_cast<uint64_t>(rm_stride0) * es;
+  const uint64_t along_rows = static_cast<uint64_t>(t2) * row_pitch, along_cols = static_cast<uint64_t>(t3) * es;
+  const uint64_t matrix[3] = {row_pitch, to ? along_rows : along_cols, to ? along_cols : along_rows};
+  for (int i = 0; i < 3; ++i)
+    if ((tiled[i] & 15) || (matrix[i] & 15) || !tiled[i] || !matrix[i] || tiled[i] >= (1ull << 40) || matrix[i] >= (1ull << 40))
+      return IREE_B200_STATUS_OK;
+  const int sms = usable_sms(ctx);
+  if (!ctx->tiling_scratch) {
+    uint8_t host[3 * 128];
+    B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(ctx->device, 4096 + 256 * 256, &ctx->tiling_scratch));
+    const CUtensorMapDataType types[3] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                                          CU_TENSOR_MAP_DATA_TYPE_UINT32};
+    for (int i = 0; i < 3; ++i) {
+      // any valid rank-4 tensor will do: address, extents, pitches and box are replaced on the device
+      const cuuint64_t e = 1ull << i;
+      const cuuint64_t dims[4] = {64, 4, 4, 4};
+      const cuuint64_t strides[3] = {64 * e, 256 * e, 1024 * e};
+      const cuuint32_t box[4] = {static_cast<cuuint32_t>(16 / e), 1, 1, 1}, estrides[4] = {1, 1, 1, 1};
+      CUtensorMap map;
+      CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, types[i], 4, ctx->tiling_scratch, dims, strides, box, estrides,
+                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                         "cuTensorMapEncodeTiled(rank-4 template)");
+      memcpy(host + 128 * i, &map, 128);
+    }
+    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(ctx->device, host, ctx->tiling_scratch, sizeof host));
+  }
+  if (sms > 256) return IREE_B200_STATUS_OK;
+  // tiles per box: as many as fit 16 KiB, at most 256 and at most what one o0 index holds
+  int64_t box2 = 16384 / (t2 * t3 * es);
+  if (box2 > 256) box2 = 256;
+  if (box2 > t1) box2 = t1;
+  const int64_t regions = ((t1 + box2 - 1) / box2) * t0;
+  const int32_t ord = iree_hal_b200_executable_lookup(ctx->executable, "b200_tiling_tma");
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_tiling_tma missing from the executable");
+  const uint64_t* sp = pack ? matrix : tiled;
+  const uint64_t* dp = pack ? tiled : matrix;
+  uint8_t* scratch = static_cast<uint8_t*>(ctx->tiling_scratch);
+  iree_hal_b200_descriptor_set_binding_t bindings[4] = {
+      {0, const_cast<void*>(in)}, {1, out}, {2, scratch + 128 * (es == 1 ? 0 : es == 2 ? 1 : 2)}, {3, scratch + 4096}};
+  const int32_t c[18] = {(int32_t)t3, (int32_t)t2, (int32_t)t1, (int32_t)t0, (int32_t)box2, es,
+                         (int32_t)(uint32_t)sp[0], (int32_t)(sp[0] >> 32), (int32_t)(uint32_t)sp[1], (int32_t)(sp[1] >> 32),
+                         (int32_t)(uint32_t)sp[2], (int32_t)(sp[2] >> 32), (int32_t)(uint32_t)dp[0], (int32_t)(dp[0] >> 32),
+                         (int32_t)(uint32_t)dp[1], (int32_t)(dp[1] >> 32), (int32_t)(uint32_t)dp[2], (int32_t)(dp[2] >> 32)};
+  auto* cb = ctx->command_buffer;
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
+  *dispatched = true;
+  return iree_hal_b200_command_buffer_dispatch(cb, ctx->executable, ord, 4, 18, static_cast<uint32_t>(regions < sms ? regions : sms),
+                                               1, 1);
+}
+
 // Shared by pack (row-major -> tiled) and unpack; `rm_*` describe the row-major side.
 iree_b200_status_t tiling_dispatch(iree_b200_context_t* ctx, bool pack, int es, const void* in, void* out,
                                    int64_t rm_size0, int64_t rm_size1, int64_t rm_stride0, int64_t rm_stride1,
@@ -2371,6 +2445,13 @@ iree_b200_status_t tiling_dispatch(iree_b200_context_t* ctx, bool pack, int es, 
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "the tiled shape does not cover the %lldx%lld matrix",
                 static_cast<long long>(rm_size0), static_cast<long long>(rm_size1));
   if (!in || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
+  if (!(kernel_flags & kTilingNoTma)) {
+    bool dispatched = false;
+    B200_RETURN_IF_ERROR(tiling_by_tma(ctx, pack, es, in, out, rm_size0, rm_size1, rm_stride0, rm_stride1, t0, t1, t2, t3,
+                                       t_stride0, kernel_flags, &dispatched));
+    if (dispatched) return IREE_B200_STATUS_OK;
+  }
+  kernel_flags &= ~kTilingNoTma;
   const char* name = pack ? (es == 1 ? "b200_pack_b8" : es == 2 ? "b200_pack_b16" : "b200_pack_b32")
                           : (es == 1 ? "b200_unpack_b8" : es == 2 ? "b200_unpack_b16" : "b200_unpack_b32");
   const int32_t ord = iree_hal_b200_executable_lookup(ctx->executable, name);
@@ -2421,14 +2502,14 @@ iree_b200_status_t iree_b200_uk_pack(iree_b200_context_t* context, const void* i
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
   const int es = pack_elem_bytes(flags);
   if (!es) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown pack type 0x%x", flags & 0xFF);
-  if (flags & ~(IREE_B200_UK_FLAG_PACK_TYPE_MASK | kUkTransposeInner | kUkTransposeOuter))
+  if (flags & ~(IREE_B200_UK_FLAG_PACK_TYPE_MASK | kUkTransposeInner | kUkTransposeOuter | IREE_B200_UK_FLAG_PACK_NO_TMA))
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown pack flags 0x%x", flags);
   if (out_stride1 != out_size2 * out_size3)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_stride1 must equal out_size2 * out_size3");
   return tiling_dispatch(context, true, es, static_cast<const uint8_t*>(in_buffer) + in_offset * es,
                          static_cast<uint8_t*>(out_buffer) + out_offset * es, in_size0, in_size1, in_stride0, in_stride1,
-                         out_size0, out_size1, out_size2, out_size3, out_stride0, flags & (kUkTransposeInner | kUkTransposeOuter),
-                         padding_value);
+                         out_size0, out_size1, out_size2, out_size3, out_stride0,
+                         flags & (kUkTransposeInner | kUkTransposeOuter | kTilingNoTma), padding_value);
 }
 
 iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
@@ -2439,14 +2520,14 @@ iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void*
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
   const int es = pack_elem_bytes(flags);
   if (!es) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown unpack type 0x%x", flags & 0xFF);
-  if (flags & ~(IREE_B200_UK_FLAG_PACK_TYPE_MASK | kUkTransposeInner | kUkTransposeOuter))
+  if (flags & ~(IREE_B200_UK_FLAG_PACK_TYPE_MASK | kUkTransposeInner | kUkTransposeOuter | IREE_B200_UK_FLAG_PACK_NO_TMA))
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown unpack flags 0x%x", flags);
   if (in_stride1 != in_size2 * in_size3)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "in_stride1 must equal in_size2 * in_size3");
   return tiling_dispatch(context, false, es, static_cast<const uint8_t*>(in_buffer) + in_offset * es,
                          static_cast<uint8_t*>(out_buffer) + out_offset * es, out_size0, out_size1, out_stride0,
                          out_stride1, in_size0, in_size1, in_size2, in_size3, in_stride0,
-                         flags & (kUkTransposeInner | kUkTransposeOuter), 0);
+                         flags & (kUkTransposeInner | kUkTransposeOuter | kTilingNoTma), 0);
 }
 
 size_t iree_b200_uk_mmt4d_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,

@@ -221,6 +221,18 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem
                ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(tmap), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst_smem), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once at most N of this thread's groups are still reading their shared-memory source.
 template <int N>
@@ -283,6 +295,7 @@ __device__ __forceinline__ void tensormap_replace_address(uint32_t smem_map, con
 B200_TENSORMAP_REPLACE_DIM(0)
 B200_TENSORMAP_REPLACE_DIM(1)
 B200_TENSORMAP_REPLACE_DIM(2)
+B200_TENSORMAP_REPLACE_DIM(3)
 #undef B200_TENSORMAP_REPLACE_DIM
 // Stride ordinal i is the byte stride of dimension i + 1 (dimension 0 is contiguous).
 #define B200_TENSORMAP_REPLACE_STRIDE(ORD)                                                                       \
@@ -293,6 +306,7 @@ B200_TENSORMAP_REPLACE_DIM(2)
   }
 B200_TENSORMAP_REPLACE_STRIDE(0)
 B200_TENSORMAP_REPLACE_STRIDE(1)
+B200_TENSORMAP_REPLACE_STRIDE(2)
 #undef B200_TENSORMAP_REPLACE_STRIDE
 #define B200_TENSORMAP_REPLACE_BOX(ORD)                                                                       \
   __device__ __forceinline__ void tensormap_replace_box##ORD(uint32_t smem_map, uint32_t v) {               \
@@ -303,6 +317,7 @@ B200_TENSORMAP_REPLACE_STRIDE(1)
 B200_TENSORMAP_REPLACE_BOX(0)
 B200_TENSORMAP_REPLACE_BOX(1)
 B200_TENSORMAP_REPLACE_BOX(2)
+B200_TENSORMAP_REPLACE_BOX(3)
 #undef B200_TENSORMAP_REPLACE_BOX
 // Copies the edited 128-byte map from shared to global memory and releases it to the
 // tensor-map proxy. Must be executed by a full warp.

@@ -442,13 +442,14 @@ def matmul_numpy(ctx: Context, kind: int, epilogue: int, lhs: np.ndarray, rhs: n
 
 UK_PACK_TYPE = {1: 0x02, 2: 0x04, 4: 0x03}  # element bytes -> I8I8 / F16F16 / I32I32 (pure data movement)
 UK_TRANSPOSE_INNER, UK_TRANSPOSE_OUTER = 0x100, 0x200
+UK_PACK_NO_TMA = 0x40000     # this library's own: the staging kernels even where the TMA unit alone could copy
 UK_MMT4D_S8S8S32, UK_MMT4D_F16F16F32, UK_MMT4D_F16F16F16 = 0x02, 0x03, 0x04
 UK_MMT4D_BF16BF16F32, UK_MMT4D_BF16BF16BF16, UK_MMT4D_ACCUMULATE = 0x05, 0x06, 0x100
 UK_MMT4D_UNTILE = 0x10000   # this library's own: take the un-tiling path even where the tiled-operand kernel applies
 
 
 def pack_numpy(ctx: Context, x: np.ndarray, tile, transpose_inner=False, transpose_outer=False, padding: int = 0,
-               out_shape=None) -> np.ndarray:
+               out_shape=None, extra_flags: int = 0) -> np.ndarray:
     """Host [S0,S1] array in, tiled [o0,o1,o2,o3] array out, through iree_b200_uk_pack. `tile` is the
     (rows, cols) tile extent in matrix terms; x may be a strided 2-D view."""
     assert x.ndim == 2
@@ -471,6 +472,7 @@ def pack_numpy(ctx: Context, x: np.ndarray, tile, transpose_inner=False, transpo
     count = int(np.prod(out_shape))
     dev_out = ctx.alloc(max(count * es, 16)).fill(0xCD)
     flags = UK_PACK_TYPE[es] | (UK_TRANSPOSE_INNER if transpose_inner else 0) | (UK_TRANSPOSE_OUTER if transpose_outer else 0)
+    flags |= extra_flags
     ctx.uk_pack(dev_in, offset, stride0, stride1, dev_out, 0, out_shape[1] * out_shape[2] * out_shape[3],
                 out_shape[2] * out_shape[3], x.shape[0], x.shape[1], *out_shape, padding, flags)
     out = dev_out.download(x.dtype, out_shape)
@@ -480,7 +482,7 @@ def pack_numpy(ctx: Context, x: np.ndarray, tile, transpose_inner=False, transpo
 
 
 def unpack_numpy(ctx: Context, x4: np.ndarray, out_shape, transpose_inner=False, transpose_outer=False,
-                 fill: int = 0xCD) -> np.ndarray:
+                 fill: int = 0xCD, extra_flags: int = 0) -> np.ndarray:
     """Tiled host array in, row-major [S0,S1] out, through iree_b200_uk_unpack; untouched output bytes keep `fill`."""
     x4 = np.ascontiguousarray(x4)
     es = x4.dtype.itemsize
@@ -488,6 +490,7 @@ def unpack_numpy(ctx: Context, x4: np.ndarray, out_shape, transpose_inner=False,
     count = int(out_shape[0] * out_shape[1])
     dev_out = ctx.alloc(max(count * es, 16)).fill(fill)
     flags = UK_PACK_TYPE[es] | (UK_TRANSPOSE_INNER if transpose_inner else 0) | (UK_TRANSPOSE_OUTER if transpose_outer else 0)
+    flags |= extra_flags
     ctx.uk_unpack(dev_in, 0, x4.shape[1] * x4.shape[2] * x4.shape[3], x4.shape[2] * x4.shape[3], dev_out, 0, out_shape[1], 1,
                   *x4.shape, out_shape[0], out_shape[1], flags)
     out = dev_out.download(x4.dtype, tuple(out_shape))

@@ -274,3 +274,26 @@ def test_mmt4d_on_tiled_operands_is_one_launch_and_equals_the_untiling_path(ctx,
             want = oracle.mmt4d_port(oracle.TYPE_S8S8S32, lhs, rhs, acc)
             assert np.array_equal(results[(True, False)], want), (M, N, K)
         dl.free(); dr.free()
+
+
+@pytest.mark.parametrize("dtype,tile", [(np.float32, (16, 16)), (np.int32, (8, 4)), (np.float16, (16, 8)), (np.int8, (7, 32)),
+                                        (np.int8, (16, 16)), (np.float32, (1, 64))])
+@pytest.mark.parametrize("transpose_outer", [False, True])
+def test_pack_and_unpack_by_tma_copy_equal_the_staging_kernels(ctx, dtype, tile, transpose_outer):
+    """Shapes the TMA-only copy takes (tile rows of whole 16-byte pieces, no inner transpose, a matrix
+    the tiles cover exactly): bit-identical to the staging kernels and to the oracle, in both
+    directions, one tile to many boxes per CTA, ragged last box along o1."""
+    rng = np.random.default_rng(3)
+    t0, t1 = tile
+    for (n0, n1) in [(1, 1), (3, 5), (37, 70), (150, 301)]:
+        x = rng.integers(-100, 100, (n0 * t0, n1 * t1)).astype(dtype)
+        shape4 = ((n1, n0) if transpose_outer else (n0, n1)) + (t0, t1)
+        want = oracle.pack_port(x, shape4, False, transpose_outer)
+        got = pack_numpy(ctx, x, (t0, t1), False, transpose_outer)
+        staged = pack_numpy(ctx, x, (t0, t1), False, transpose_outer, extra_flags=rt.UK_PACK_NO_TMA)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (n0, n1)
+        assert np.array_equal(staged.view(np.uint8), want.view(np.uint8)), (n0, n1)
+        back = unpack_numpy(ctx, got, x.shape, False, transpose_outer)
+        back_staged = unpack_numpy(ctx, got, x.shape, False, transpose_outer, extra_flags=rt.UK_PACK_NO_TMA)
+        assert np.array_equal(back.view(np.uint8), x.view(np.uint8)), (n0, n1)
+        assert np.array_equal(back_staged.view(np.uint8), x.view(np.uint8)), (n0, n1)

@@ -1254,6 +1254,7 @@ const EntryDecl kEntries[] = {
     {"b200_mmt4d_bf16bf16f32", {512, 1, 1}, kGemmSmemBytes},
     {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kGemmSmemBytes},
     {"b200_tiling_tma", {32, 1, 1}, 1024 + 8 * 16384 + 128},
+    {"b200_pack_i8_rhs_16x2", {288, 1, 1}, 1024 + 4 * 16384 + 2 * 8 * (64 * 32 + 32) + 128},
     {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b16", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b32", {256, 1, 1}, kTilingStageBytes},
@@ -2361,6 +2362,71 @@ uint32_t tiling_grid(int64_t o0, int64_t o1, int64_t o2, int64_t o3, uint32_t fl
   return static_cast<uint32_t>(blocks < cap ? blocks : cap);
 }
 
+// Three rank-4 template maps (1-, 2-, 4-byte elements, no swizzle) and 256 bytes per CTA for the maps the
+// TMA tiling kernels build on the device.
+constexpr int kTilingScratchSlots = 1024;
+iree_b200_status_t ensure_tiling_scratch(iree_b200_context_t* ctx) {
+  if (ctx->tiling_scratch) return IREE_B200_STATUS_OK;
+  uint8_t host[3 * 128];
+  void* scratch = nullptr;
+  B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(ctx->device, 4096 + kTilingScratchSlots * 256, &scratch));
+  const CUtensorMapDataType types[3] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                                        CU_TENSOR_MAP_DATA_TYPE_UINT32};
+  for (int i = 0; i < 3; ++i) {
+    // any valid rank-4 tensor will do: address, extents, pitches and box are replaced on the device
+    const cuuint64_t e = 1ull << i;
+    const cuuint64_t dims[4] = {64, 4, 4, 4};
+    const cuuint64_t strides[3] = {64 * e, 256 * e, 1024 * e};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(16 / e), 1, 1, 1}, estrides[4] = {1, 1, 1, 1};
+    CUtensorMap map;
+    const CUresult r = g_cu.cuTensorMapEncodeTiled(&map, types[i], 4, scratch, dims, strides, box, estrides,
+                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      iree_hal_b200_buffer_free(ctx->device, scratch);
+      return fail(IREE_B200_STATUS_INTERNAL, "cuTensorMapEncodeTiled(rank-4 template) failed: %d", static_cast<int>(r));
+    }
+    memcpy(host + 128 * i, &map, 128);
+  }
+  const iree_b200_status_t st = iree_hal_b200_transfer_h2d(ctx->device, host, scratch, sizeof host);
+  if (st != IREE_B200_STATUS_OK) {
+    iree_hal_b200_buffer_free(ctx->device, scratch);
+    return st;
+  }
+  ctx->tiling_scratch = scratch;
+  return IREE_B200_STATUS_OK;
+}
+
+// The int8 right-hand side of the VNNI mmt4d ([K, N] -> [N1, K1, 16, 2], both transposes): TMA box in,
+// byte interleave in shared memory, bulk copies out (pack_vnni_sm100.cu).
+iree_b200_status_t pack_rhs_16x2(iree_b200_context_t* ctx, const void* in, void* out, int64_t K, int64_t N,
+                                 int64_t rm_stride0, int64_t rm_stride1, int64_t t0, int64_t t1, int64_t t2, int64_t t3,
+                                 int64_t t_stride0, uint32_t kernel_flags, uint64_t padding, bool* dispatched) {
+  *dispatched = false;
+  if (!(kernel_flags & kUkTransposeInner) || !(kernel_flags & kUkTransposeOuter) || t2 != 16 || t3 != 2) return IREE_B200_STATUS_OK;
+  if ((kernel_flags & (kTilingAccumulateI32 | kTilingAccumulateF32)) || rm_stride1 != 1) return IREE_B200_STATUS_OK;
+  const bool ragged = t1 * 2 != K || t0 * 16 != N;
+  if (ragged && (padding & 0xff)) return IREE_B200_STATUS_OK;  // the TMA unit fills with zero
+  if (t1 * 2 < K || t0 * 16 < N || rm_stride0 < N || t_stride0 < t1 * 32) return IREE_B200_STATUS_OK;
+  if ((rm_stride0 & 15) || (t_stride0 & 15) || ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15))
+    return IREE_B200_STATUS_OK;
+  const int ctas = 2 * usable_sms(ctx);  // two CTAs per SM: eight 16 KiB loads in flight on each SM
+  if (ctas > kTilingScratchSlots) return IREE_B200_STATUS_OK;
+  B200_RETURN_IF_ERROR(ensure_tiling_scratch(ctx));
+  const int32_t ord = iree_hal_b200_executable_lookup(ctx->executable, "b200_pack_i8_rhs_16x2");
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_pack_i8_rhs_16x2 missing from the executable");
+  const int64_t regions = ((t0 + 7) / 8) * ((t1 + 63) / 64);
+  uint8_t* scratch = static_cast<uint8_t*>(ctx->tiling_scratch);
+  iree_hal_b200_descriptor_set_binding_t bindings[4] = {{0, const_cast<void*>(in)}, {1, out}, {2, scratch}, {3, scratch + 4096}};
+  const int32_t c[6] = {(int32_t)K, (int32_t)N, (int32_t)rm_stride0, (int32_t)t0, (int32_t)t1, (int32_t)t_stride0};
+  auto* cb = ctx->command_buffer;
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
+  *dispatched = true;
+  return iree_hal_b200_command_buffer_dispatch(cb, ctx->executable, ord, 4, 6, static_cast<uint32_t>(regions < ctas ? regions : ctas), 1,
+                                               1);
+}
+
 // pack / unpack as a pure TMA copy (tiling_tma_sm100.cu), for the shapes it takes: tiles not transposed
 // inside, tile rows of whole 16-byte pieces, a matrix the tiles cover exactly, 16-byte aligned addresses
 // and pitches, no accumulation. Everything else goes to the staging kernels.
@@ -2385,27 +2451,8 @@ iree_b200_status_t tiling_by_tma(iree_b200_context_t* ctx, bool pack, int es, co
     if ((tiled[i] & 15) || (matrix[i] & 15) || !tiled[i] || !matrix[i] || tiled[i] >= (1ull << 40) || matrix[i] >= (1ull << 40))
       return IREE_B200_STATUS_OK;
   const int sms = usable_sms(ctx);
-  if (!ctx->tiling_scratch) {
-    uint8_t host[3 * 128];
-    B200_RETURN_IF_ERROR(iree_hal_b200_buffer_allocate(ctx->device, 4096 + 256 * 256, &ctx->tiling_scratch));
-    const CUtensorMapDataType types[3] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT16,
-                                          CU_TENSOR_MAP_DATA_TYPE_UINT32};
-    for (int i = 0; i < 3; ++i) {
-      // any valid rank-4 tensor will do: address, extents, pitches and box are replaced on the device
-      const cuuint64_t e = 1ull << i;
-      const cuuint64_t dims[4] = {64, 4, 4, 4};
-      const cuuint64_t strides[3] = {64 * e, 256 * e, 1024 * e};
-      const cuuint32_t box[4] = {static_cast<cuuint32_t>(16 / e), 1, 1, 1}, estrides[4] = {1, 1, 1, 1};
-      CUtensorMap map;
-      CU_RETURN_IF_ERROR(g_cu.cuTensorMapEncodeTiled(&map, types[i], 4, ctx->tiling_scratch, dims, strides, box, estrides,
-                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
-                         "cuTensorMapEncodeTiled(rank-4 template)");
-      memcpy(host + 128 * i, &map, 128);
-    }
-    B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(ctx->device, host, ctx->tiling_scratch, sizeof host));
-  }
-  if (sms > 256) return IREE_B200_STATUS_OK;
+  B200_RETURN_IF_ERROR(ensure_tiling_scratch(ctx));
+  if (sms > kTilingScratchSlots) return IREE_B200_STATUS_OK;
   // tiles per box: as many as fit 16 KiB, at most 256 and at most what one o0 index holds
   int64_t box2 = 16384 / (t2 * t3 * es);
   if (box2 > 256) box2 = 256;
@@ -2447,6 +2494,11 @@ iree_b200_status_t tiling_dispatch(iree_b200_context_t* ctx, bool pack, int es, 
   if (!in || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
   if (!(kernel_flags & kTilingNoTma)) {
     bool dispatched = false;
+    if (pack && es == 1) {
+      B200_RETURN_IF_ERROR(pack_rhs_16x2(ctx, in, out, rm_size0, rm_size1, rm_stride0, rm_stride1, t0, t1, t2, t3, t_stride0,
+                                         kernel_flags, padding, &dispatched));
+      if (dispatched) return IREE_B200_STATUS_OK;
+    }
     B200_RETURN_IF_ERROR(tiling_by_tma(ctx, pack, es, in, out, rm_size0, rm_size1, rm_stride0, rm_stride1, t0, t1, t2, t3,
                                        t_stride0, kernel_flags, &dispatched));
     if (dispatched) return IREE_B200_STATUS_OK;

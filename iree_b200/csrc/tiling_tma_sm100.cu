@@ -9,7 +9,7 @@
 // o0 pitch), on the row-major side (element, matrix row, and the tile steps along the matrix). A box of
 // {tile columns, tile rows, n tiles along o1, 1} is loaded from one description and stored through the
 // other; no thread touches the data. One warp per CTA: lane 0 builds the two tensor maps from a template
-// (tensormap.replace) in this CTA's slot of a scratch buffer, then keeps four loads and up to four stores
+// (tensormap.replace) in this CTA's slot of a scratch buffer, then keeps six loads and up to two stores
 // in flight over an eight-stage ring.
 //
 // Bindings: source, destination, template (one 128-byte rank-4 map of the element size, no swizzle),
@@ -22,7 +22,7 @@
 namespace b200 {
 
 constexpr int kTtStages = 8;
-constexpr int kTtLoadsAhead = 4;
+constexpr int kTtLoadsAhead = 6;
 constexpr int kTtStageBytes = 16384;
 constexpr int kTtSmemBytes = 1024 + kTtStages * kTtStageBytes + 128;
 

@@ -78,7 +78,7 @@ module attributes {transform.with_named_sequence} {
       objects({
         #cuda_target ordinal(0) = [#hal.executable.object<{path = "b200_contraction.cubin"}>]
       })
-      attributes {workgroup_size = [256 : index, 1 : index, 1 : index], workgroup_local_memory = 197888 : index}
+      attributes {workgroup_size = [256 : index, 1 : index, 1 : index], workgroup_local_memory = 230656 : index}
     util.return %out#0 : tensor<4096x4096xf16>
   }
 

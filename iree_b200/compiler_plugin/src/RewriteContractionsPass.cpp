@@ -48,7 +48,7 @@ namespace HAL = IREE::HAL;
 // written by compiler_plugin/gen_templates.py on a machine with the CUDA driver.
 #include "TensorMapTemplates.inc"
 
-constexpr int64_t kGemmThreads = 256, kGemmSmem = 197888;
+constexpr int64_t kGemmThreads = 256, kGemmSmem = 230656;
 constexpr int64_t kW4GemmThreads = 512, kW4GemmSmem = 230656, kW4WtThreads = 512, kW4WtSmem = 214528;
 constexpr int64_t kDecodeThreads = 512, kDecodeSmemM8 = 217984, kDecodeSmemM16 = 213760;
 constexpr int64_t kDecodeSliceK = 4096;

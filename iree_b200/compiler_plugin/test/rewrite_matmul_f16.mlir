@@ -35,5 +35,5 @@ module attributes {hal.device.targets = [#cuda]} {
 //  CHECK-SAME:       (%[[WS]], %c4096_i32, %c4096_i32, %c4096_i32, %c1_i32, %c0_i32, %c256_i32)
 //       CHECK:     hal.return %c148, %c1, %c1
 //       CHECK:     push_constants = 6
-//       CHECK:     workgroup_local_memory = 197888 : index
+//       CHECK:     workgroup_local_memory = 230656 : index
 //       CHECK:   util.return %[[OUT]]

@@ -37,5 +37,5 @@ module attributes {hal.device.targets = [#cuda]} {
 //  CHECK-SAME:       (%a_scale, %w_scale, %[[WS]], %c16_i32, %c11008_i32, %c4096_i32, %c1_i32, %c0_i32, %c128_i32)
 //       CHECK:     hal.return %c86, %c1, %c1
 //       CHECK:     push_constants = 6
-//       CHECK:     workgroup_size = [256 : index, 1 : index, 1 : index], workgroup_local_memory = 197888 : index
+//       CHECK:     workgroup_size = [256 : index, 1 : index, 1 : index], workgroup_local_memory = 230656 : index
 //       CHECK:   util.return %[[OUT]]

@@ -38,7 +38,11 @@ constexpr int kFewRowsStages = 9;
 __host__ __device__ constexpr bool few_rows_variant(int M, int bn) { return M <= kFewRows && bn <= kFewRowsMaxBN; }
 constexpr int kThreads = 256;
 constexpr int kTmemColumns = 512;
-constexpr int kGemmSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + 256 /*barriers*/;
+// Epilogue staging of the many-rows variant: two tiles of 128 result rows x 128 bytes in the 128-byte
+// swizzled layout, handed to the TMA unit (one store per tile) while the warps convert the next columns.
+constexpr int kOutTileBytes = kBM * 128;
+constexpr int kOutStageBytes = 2 * kOutTileBytes;
+constexpr int kGemmSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kOutStageBytes + 256 /*barriers*/;
 
 // Workspace binding: three 128-byte tensor maps followed by status words.
 struct alignas(128) Workspace {
@@ -106,6 +110,10 @@ struct KindTraits<kI8> {
   static constexpr uint32_t kFormat = 1, kCFormat = 2;
 };
 
+__device__ __forceinline__ void stage_st128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // One 32-byte store. A warp's epilogue store touches 32 different rows whatever its width, and the
 // load/store unit's cost is per row touched: twice the bytes per instruction halves the time.
 __device__ __forceinline__ void st_global_256(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e,
@@ -113,6 +121,46 @@ __device__ __forceinline__ void st_global_256(void* p, uint32_t a, uint32_t b, u
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d),
                "r"(e), "r"(f), "r"(g), "r"(h)
                : "memory");
+}
+
+// Two f32 -> one word of two f16 / bf16 (lo in the low half), round to nearest even, by the packed
+// conversion: one instruction of the ALU pipe where two scalar conversions go through the (16 lanes per
+// clock) conversion unit -- the scalar form made the f16 epilogues conversion-bound.
+template <int KIND>
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi) {
+  uint32_t r;
+  if constexpr (KIND == kBF16) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+// 32 accumulator columns of one row -> output words (32 for 4-byte results, 16 for 2-byte ones).
+template <int KIND, int EPI>
+__device__ __forceinline__ void convert_row_chunk(const uint32_t (&v)[32], int col0, int N, float row_scale,
+                                                  const float* col_scale, uint32_t (&w)[32]) {
+  if constexpr (EPI == kEpiRaw) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = v[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      float f[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if constexpr (EPI == kEpiRequantF16) {
+          // f16( (f32(acc) * a_scale[m]) * w_scale[n] ), same operation order as the consumer generic.
+          f[e] = static_cast<float>(static_cast<int32_t>(v[j + e])) * row_scale;
+          f[e] = f[e] * ((col0 + j + e < N) ? col_scale[col0 + j + e] : 0.f);
+        } else {
+          f[e] = __uint_as_float(v[j + e]);
+        }
+      }
+      w[j >> 1] = pack_16x2<KIND>(f[0], f[1]);
+    }
+  }
 }
 
 // The epilogue for one thread: 32 consecutive columns of one output row. vec_ok: 16-byte stores are
@@ -140,28 +188,10 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], void* c
       }
     }
   } else {
-    uint16_t h[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float f;
-      if constexpr (EPI == kEpiRequantF16) {
-        // f16( (f32(acc) * a_scale[m]) * w_scale[n] ), same operation order as the consumer generic.
-        f = static_cast<float>(static_cast<int32_t>(v[j])) * row_scale;
-        f = f * ((col0 + j < N) ? col_scale[col0 + j] : 0.f);
-      } else {
-        f = __uint_as_float(v[j]);
-      }
-      if constexpr (KIND == kBF16) {
-        h[j] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-      } else {
-        h[j] = __half_as_ushort(__float2half_rn(f));
-      }
-    }
+    uint32_t w[32];  // 16 words of two results each
+    convert_row_chunk<KIND, EPI>(v, col0, N, row_scale, col_scale, w);
     uint16_t* out = reinterpret_cast<uint16_t*>(c_base) + row_offset + col0;
     if (wide_ok && col0 + 31 < N) {
-      uint32_t w[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) w[j] = h[2 * j] | (uint32_t(h[2 * j + 1]) << 16);
       st_global_256(out, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
       st_global_256(out + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
       return;
@@ -169,15 +199,11 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&v)[32], void* c
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       if (vec_ok && col0 + j + 7 < N) {
-        uint4 q;
-        q.x = h[j] | (uint32_t(h[j + 1]) << 16);
-        q.y = h[j + 2] | (uint32_t(h[j + 3]) << 16);
-        q.z = h[j + 4] | (uint32_t(h[j + 5]) << 16);
-        q.w = h[j + 6] | (uint32_t(h[j + 7]) << 16);
-        *reinterpret_cast<uint4*>(out + j) = q;
+        *reinterpret_cast<uint4*>(out + j) = make_uint4(w[j / 2], w[j / 2 + 1], w[j / 2 + 2], w[j / 2 + 3]);
       } else {
+#pragma unroll
         for (int t = 0; t < 8; ++t)
-          if (col0 + j + t < N) out[j + t] = h[j + t];
+          if (col0 + j + t < N) out[j + t] = static_cast<uint16_t>(w[(j + t) / 2] >> (16 * ((j + t) & 1)));
       }
     }
   }
@@ -191,7 +217,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   constexpr int kStages = FEW_ROWS ? kFewRowsStages : b200::kStages;
   constexpr int kAStageBytes = (FEW_ROWS ? kFewRows : kBM) * kRowBytes;
   constexpr int kStageBytes = kAStageBytes + (FEW_ROWS ? kFewRowsMaxBN : kMaxBN) * kRowBytes;
-  static_assert(1024 + kStages * kStageBytes + 256 <= kGemmSmemBytes, "ring exceeds the export's shared memory");
+  static_assert(1024 + kStages * kStageBytes + kOutStageBytes + 256 <= kGemmSmemBytes, "ring exceeds the export's shared memory");
   static_assert(!FEW_ROWS || (kStages - 1) * kStageBytes + kBM * kRowBytes <= kStages * kStageBytes,
                 "the 128-row operand read of the last stage must stay inside the ring");
   using T = KindTraits<KIND>;
@@ -201,8 +227,10 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   constexpr int kChunkN = kRowBytes / kElem;      // columns per 128-byte row of a [K,N] tile
 
   extern __shared__ uint8_t smem_raw[];
+  __shared__ alignas(128) uint8_t out_map_stage[128];  // where the result's tensor map is assembled
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = smem_base + kStages * kStageBytes;
+  const uint32_t out_stage = smem_base + kStages * kStageBytes;  // epilogue staging (many-rows variant only)
+  const uint32_t bars = out_stage + kOutStageBytes;
   // barrier slots (8 bytes each): full[0..3], empty[4..7], tmem_full[8..9], tmem_empty[10..11]
   auto full_bar = [&](int i) { return bars + 8u * i; };
   auto empty_bar = [&](int i) { return bars + 8u * (kStages + i); };
@@ -211,9 +239,12 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   const uint32_t tmem_slot = bars + 8u * (2 * kStages + 4);
   uint8_t* smem_generic = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* abort_flag =
-      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + 8 * (2 * kStages + 4) + 4);
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytes + 8 * (2 * kStages + 4) + 4);
+  // Written by the epilogue warps only, before the barrier at which all four read it: they leave together.
+  volatile uint32_t* epilogue_abort =
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytes + 8 * (2 * kStages + 4) + 8);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + 8 * (2 * kStages + 4));
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytes + 8 * (2 * kStages + 4));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -257,6 +288,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
       mbar_init(tmem_empty_bar(i), 4);
     }
     *abort_flag = 0;
+    *epilogue_abort = 0;
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -378,7 +410,39 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
     constexpr int kOutBytes = (EPI == kEpiRaw) ? 4 : 2;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 16 == 0) && ((s.N * kOutBytes) % 16 == 0);
     const bool wide_ok = (reinterpret_cast<uintptr_t>(c_ptr) % 32 == 0) && ((s.N * kOutBytes) % 32 == 0);
-    uint32_t local_tile = 0;
+    // Results leave through the TMA unit when their rows can be addressed by it (16-byte aligned base and
+    // pitch): the tile is staged 128 bytes of every row at a time and stored by one instruction, while the
+    // warps convert the next columns. The map is map_a with address, extents, pitches and box replaced
+    // (a 4-byte result is described in the operand's narrower elements: the copy moves bytes). Every CTA
+    // assembles the same 128 bytes and publishes them to the same slot of the workspace, after the wait
+    // for the dispatch ahead (which may still be storing through that slot).
+    constexpr int kPassCols = 128 / kOutBytes;  // result columns per staged tile: 64 or 32
+    // (a store is always 128 bytes of a row wide: tiles must be whole multiples of that)
+    const bool tma_out = !FEW_ROWS && vec_ok && (s.bn % kPassCols) == 0;
+    const bool store_thread = threadIdx.x == 128;
+    if (tma_out && q == 0) {
+      reinterpret_cast<uint32_t*>(out_map_stage)[lane] = reinterpret_cast<const uint32_t*>(ws->map_a)[lane];
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t m = smem_u32(out_map_stage);
+        const uint64_t pitch = static_cast<uint64_t>(s.N) * kOutBytes;
+        tensormap_replace_address(m, c_ptr);
+        tensormap_replace_dim0(m, static_cast<uint32_t>(pitch / kElem));
+        tensormap_replace_dim1(m, s.M);
+        tensormap_replace_dim2(m, s.batch);
+        tensormap_replace_stride0(m, pitch);
+        tensormap_replace_stride1(m, pitch * s.M);
+        tensormap_replace_box0(m, 128 / kElem);
+        tensormap_replace_box1(m, kBM);
+        tensormap_replace_box2(m, 1);
+        reinterpret_cast<uint32_t*>(out_map_stage)[16] = kOutTileBytes;
+        tensormap_set_span_class(out_map_stage, pitch * s.M * s.batch);
+      }
+      __syncwarp();
+      tensormap_publish(ws->map_aux, smem_u32(out_map_stage));
+      if (lane == 0) tensormap_fence_acquire(ws->map_aux);
+    }
+    uint32_t local_tile = 0, pass = 0;
     for (int w = blockIdx.x; w < num_items; w += gridDim.x, ++local_tile) {
       int t, kb0, kb1, b, tm, tn;
       item_coords(w, t, kb0, kb1);
@@ -386,11 +450,18 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
       const int buf = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       // The warp must take the same branch: tcgen05.ld below is warp-collective.
-      if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_ph, abort_flag))) {
-        if (lane == 0) {
-          report(ws, kStatusTimeoutTmemFull, local_tile);
-          *abort_flag = 1;
-        }
+      const bool acc_ready = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_ph, abort_flag));
+      if (!acc_ready && lane == 0) {
+        report(ws, kStatusTimeoutTmemFull, local_tile);
+        *abort_flag = 1;
+        *epilogue_abort = 1;
+      }
+      if (tma_out) {
+        // The staged path meets at named barriers: a warp whose wait ran out must not leave the other
+        // three waiting there, so the four agree here first.
+        named_barrier_sync(1, 128);
+        if (*epilogue_abort) break;
+      } else if (!acc_ready) {
         break;
       }
       tc_fence_after_sync();
@@ -458,6 +529,52 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
         }
         continue;
       }
+      if (tma_out) {
+        const uint32_t my_row = static_cast<uint32_t>(q * 32 + lane) * 128u;
+        const uint32_t swz = static_cast<uint32_t>(lane & 7);
+        // columns of this tile inside the matrix (a tile may hang over the last column)
+        const int cols_here = s.N - tn * s.bn < s.bn ? s.N - tn * s.bn : s.bn;
+        for (int c0 = 0; c0 < cols_here; c0 += kPassCols, ++pass) {
+          // 128 bytes of this thread's row: 32 four-byte results or two chunks of 32 two-byte ones
+          uint32_t wv[32];
+          if constexpr (kOutBytes == 4) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxBN + c0, v);
+            tc_wait_ld();
+            convert_row_chunk<KIND, EPI>(v, tn * s.bn + c0, s.N, rs, col_scale, wv);
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32], wh[32];
+              tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxBN + c0 + 32 * h, v);
+              tc_wait_ld();
+              convert_row_chunk<KIND, EPI>(v, tn * s.bn + c0 + 32 * h, s.N, rs, col_scale, wh);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) wv[16 * h + j] = wh[j];
+            }
+          }
+          if (c0 + kPassCols >= cols_here) {  // the accumulator is in registers: the next tile's MMAs may start
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+          }
+          // the store that read this staging tile two passes ago has finished reading it
+          if (store_thread) bulk_wait_group_read<1>();
+          named_barrier_sync(1, 128);
+          const uint32_t tile = out_stage + (pass & 1) * kOutTileBytes;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            stage_st128(tile + my_row + ((static_cast<uint32_t>(j) ^ swz) << 4), wv[4 * j], wv[4 * j + 1], wv[4 * j + 2],
+                        wv[4 * j + 3]);
+          fence_proxy_async_smem();  // the TMA unit reads these bytes through the async proxy
+          named_barrier_sync(1, 128);
+          if (store_thread) {
+            tma_store_3d(ws->map_aux, tile, (tn * s.bn + c0) * kOutBytes / kElem, tm * kBM, b);
+            bulk_commit_group();
+          }
+        }
+        continue;
+      }
       for (int c = 0; c < s.bn; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxBN + c, v);
@@ -469,6 +586,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
     }
+    if (tma_out && store_thread) bulk_wait_group<0>();  // shared memory stays valid until the last store has read it
   }
 
   // Teardown: everyone meets here, also after an abort. After an abort TMA copies may still

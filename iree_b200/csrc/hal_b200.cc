@@ -1193,7 +1193,8 @@ iree_b200_status_t iree_hal_b200_command_buffer_join_collectives(iree_hal_b200_c
 namespace {
 
 constexpr uint32_t kGemmThreads = 256;
-constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
+constexpr uint32_t kGemmSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 2 * 128 * 128 /*epilogue staging*/ + 256;
+constexpr uint32_t kMmt4dSmemBytes = 1024 + 4 * (128 * 128 + 256 * 128) + 256;
 // weight ring (5 / 4 stages of 16 rows x 2048 B + 128 B), scale ring (4 KiB per stage), 3 slots of 16 per-warp
 // chunk sums, the per-warp offsets, barriers (decode_smem_bytes in w4a16_decode.cuh)
 constexpr uint32_t kDecodeSmemM8 = 5 * (16 * 2048 + 128) + 5 * 4096 + 3 * 16 * 32 * 16 * 1 + 16 * 1 * 2 * 32 * 8 + 256;
@@ -1248,11 +1249,11 @@ const EntryDecl kEntries[] = {
     {"b200_w4a16_gemm_wt", {512, 1, 1}, kW4WtSmemBytes},
     {"b200_wait_arrivals", {32, 1, 1}, 0},
     {"b200_w4a16_generic", {256, 1, 1}, 0},
-    {"b200_mmt4d_s8s8s32", {512, 1, 1}, kGemmSmemBytes},
-    {"b200_mmt4d_f16f16f32", {512, 1, 1}, kGemmSmemBytes},
-    {"b200_mmt4d_f16f16f16", {512, 1, 1}, kGemmSmemBytes},
-    {"b200_mmt4d_bf16bf16f32", {512, 1, 1}, kGemmSmemBytes},
-    {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kGemmSmemBytes},
+    {"b200_mmt4d_s8s8s32", {512, 1, 1}, kMmt4dSmemBytes},
+    {"b200_mmt4d_f16f16f32", {512, 1, 1}, kMmt4dSmemBytes},
+    {"b200_mmt4d_f16f16f16", {512, 1, 1}, kMmt4dSmemBytes},
+    {"b200_mmt4d_bf16bf16f32", {512, 1, 1}, kMmt4dSmemBytes},
+    {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kMmt4dSmemBytes},
     {"b200_tiling_tma", {32, 1, 1}, 1024 + 8 * 16384 + 128},
     {"b200_pack_i8_rhs_16x2", {288, 1, 1}, 1024 + 4 * 16384 + 2 * 8 * (64 * 32 + 32) + 128},
     {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},

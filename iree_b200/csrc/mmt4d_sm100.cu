@@ -38,6 +38,7 @@ namespace b200 {
 
 constexpr int kMtRunBytes = 32;                         // bytes of one tile row, both operands
 constexpr int kMtThreads = 512;
+constexpr int kMtSmemBytes = 1024 + kStages * kStageBytes + 256;
 constexpr int kMtProducerThreads = 256;                 // warps 8-15
 constexpr int kMtCopyDepth = 3;                         // stages of copies in flight per producer thread
 constexpr uint64_t kLayoutSwizzle32B = 6;
@@ -88,7 +89,7 @@ __device__ __forceinline__ void mmt4d_body(const void* __restrict__ lhs, const v
   constexpr int kUmmaK = 32 / kElem;                     // K1 steps per tcgen05.mma: 32 or 16
   constexpr int kTilesA = kBM / kRun;                    // outer tiles of the left operand per CTA tile: 4 or 8
   constexpr int kOutBytes = OUT16 ? 2 : 4;
-  static_assert(kStages * kStageBytes + 1024 + 256 <= kGemmSmemBytes, "ring");
+  static_assert(kStages * kStageBytes + 1024 + 256 <= kMtSmemBytes, "ring");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -343,13 +344,7 @@ __device__ __forceinline__ void mmt4d_body(const void* __restrict__ lhs, const v
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const float f0 = __uint_as_float(v[16 * h + 2 * j]), f1 = __uint_as_float(v[16 * h + 2 * j + 1]);
-                if constexpr (KIND == kBF16) {
-                  w[j] = __bfloat16_as_ushort(__float2bfloat16_rn(f0)) |
-                         (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f1))) << 16);
-                } else {
-                  w[j] = __half_as_ushort(__float2half_rn(f0)) |
-                         (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f1))) << 16);
-                }
+                w[j] = pack_16x2<KIND>(f0, f1);
               }
               st_global_256(reinterpret_cast<uint16_t*>(out) + at, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
             } else {

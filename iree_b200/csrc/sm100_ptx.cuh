@@ -221,6 +221,11 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem
                ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src_smem, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                ::"l"(tmap), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)

@@ -15,7 +15,7 @@ import json
 from dataclasses import dataclass, field, asdict
 from typing import Dict, List, Optional, Tuple
 
-GEMM_THREADS, GEMM_SMEM = 256, 197888
+GEMM_THREADS, GEMM_SMEM = 256, 230656
 W4_THREADS, W4_SMEM = 512, 230656  # 1024 + 224 KiB + 256
 W4_WT_THREADS = 512
 W4_WT_SMEM = 214528               # b200_w4a16_gemm_wt: 1024 + 4 x 32 KiB + 6 x 8 KiB + 2 x 16 KiB + 512

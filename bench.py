@@ -400,9 +400,10 @@ def run_b200(args, wl, table):
     ctx = ib.Context(local)
     lib = ib.library()
     peaks, peak_src = load_peaks()
-    # Exports that order themselves on the device (the decode kernels) may start, and prefetch their
-    # first weight tiles, before the dispatch ahead of them has finished; stream order of every
-    # read of an earlier result is kept by the kernels themselves.
+    # Exports that order themselves on the device (the decode kernels, the tensor-core GEMMs) may be
+    # launched, set up and -- the decode kernels -- prefetch their first weight tiles before the dispatch
+    # ahead of them has finished; stream order of every read of an earlier result is kept by the
+    # kernels themselves.
     ctx.set_dispatch_overlap(True)
     if world > 1 and int(os.environ.get("IREE_B200_RESERVED_SMS", "0")):
         # optional: leave SMs free for the collective's blocks (measured at 2 GPUs: no gain, off by default)

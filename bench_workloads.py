@@ -132,7 +132,7 @@ def describe(wl, world, steps):
     return {"workload": desc, "name": wl.name,
             "l2": "operand sets rotate so that every step's operands exceed the 126 MB L2 (2.2 x L2 in rotation)",
             "submission": ("CUDA graph of %d dispatches" % steps if world == 1 else "stream") +
-                          ", programmatic dependent launch for the decode exports",
+                          ", programmatic dependent launch for the exports that order themselves on the device (decode, tensor-core GEMMs)",
             "parallelism": "1 rank" if world == 1 else (
                 "N-sharded x%d, output all-gather (%s)" % (world, gather_mode_name(wl, world)) if wl.sharded
                 else "replicas x%d" % world)}

@@ -508,6 +508,13 @@ iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void*
                                        int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,
                                        int64_t in_size2, int64_t in_size3, int64_t out_size0, int64_t out_size1,
                                        uint32_t flags);
+/* pack and unpack take no workspace, so the kernels among them that wait on copies of their own (the
+ * TMA paths) report into a status word the context owns: after the device has been synchronised this
+ * returns OK, INVALID_ARGUMENT (a kernel rejected shape or alignment) or DEADLINE_EXCEEDED (a bounded wait
+ * ran out; the destination of that call is incomplete), and clears the word. No counterpart in the
+ * reference, whose ukernels run on the calling thread. */
+iree_b200_status_t iree_b200_uk_status(iree_b200_context_t* context);
+
 /* iree_uk_mmt4d: out[M,N,M0,N0] (+)= lhs[M,K,M0,K0] x rhs[N,K,N0,K0]
  * (runtime/src/iree/builtins/ukernel/mmt4d.c:55-141). Tiles whose rows are 32 bytes in both operands
  * (i8 16x16x2, the x86-64 VNNI tile; f16 / bf16 16x16x1), at 16-byte aligned operand addresses and

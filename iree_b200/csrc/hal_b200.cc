@@ -2366,6 +2366,7 @@ uint32_t tiling_grid(int64_t o0, int64_t o1, int64_t o2, int64_t o3, uint32_t fl
 // Three rank-4 template maps (1-, 2-, 4-byte elements, no swizzle) and 256 bytes per CTA for the maps the
 // TMA tiling kernels build on the device.
 constexpr int kTilingScratchSlots = 1024;
+constexpr size_t kTilingStatusOffset = 3072;  // a status word; the per-CTA slots follow 1024 bytes later
 iree_b200_status_t ensure_tiling_scratch(iree_b200_context_t* ctx) {
   if (ctx->tiling_scratch) return IREE_B200_STATUS_OK;
   uint8_t host[3 * 128];
@@ -2389,7 +2390,8 @@ iree_b200_status_t ensure_tiling_scratch(iree_b200_context_t* ctx) {
     }
     memcpy(host + 128 * i, &map, 128);
   }
-  const iree_b200_status_t st = iree_hal_b200_transfer_h2d(ctx->device, host, scratch, sizeof host);
+  iree_b200_status_t st = iree_hal_b200_fill_buffer(ctx->device, scratch, 4096, 0);
+  if (st == IREE_B200_STATUS_OK) st = iree_hal_b200_transfer_h2d(ctx->device, host, scratch, sizeof host);
   if (st != IREE_B200_STATUS_OK) {
     iree_hal_b200_buffer_free(ctx->device, scratch);
     return st;
@@ -2418,7 +2420,7 @@ iree_b200_status_t pack_rhs_16x2(iree_b200_context_t* ctx, const void* in, void*
   if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_pack_i8_rhs_16x2 missing from the executable");
   const int64_t regions = ((t0 + 7) / 8) * ((t1 + 63) / 64);
   uint8_t* scratch = static_cast<uint8_t*>(ctx->tiling_scratch);
-  iree_hal_b200_descriptor_set_binding_t bindings[4] = {{0, const_cast<void*>(in)}, {1, out}, {2, scratch}, {3, scratch + 4096}};
+  iree_hal_b200_descriptor_set_binding_t bindings[4] = {{0, const_cast<void*>(in)}, {1, out}, {2, scratch}, {3, scratch + kTilingStatusOffset}};
   const int32_t c[6] = {(int32_t)K, (int32_t)N, (int32_t)rm_stride0, (int32_t)t0, (int32_t)t1, (int32_t)t_stride0};
   auto* cb = ctx->command_buffer;
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
@@ -2465,7 +2467,7 @@ iree_b200_status_t tiling_by_tma(iree_b200_context_t* ctx, bool pack, int es, co
   const uint64_t* dp = pack ? tiled : matrix;
   uint8_t* scratch = static_cast<uint8_t*>(ctx->tiling_scratch);
   iree_hal_b200_descriptor_set_binding_t bindings[4] = {
-      {0, const_cast<void*>(in)}, {1, out}, {2, scratch + 128 * (es == 1 ? 0 : es == 2 ? 1 : 2)}, {3, scratch + 4096}};
+      {0, const_cast<void*>(in)}, {1, out}, {2, scratch + 128 * (es == 1 ? 0 : es == 2 ? 1 : 2)}, {3, scratch + kTilingStatusOffset}};
   const int32_t c[18] = {(int32_t)t3, (int32_t)t2, (int32_t)t1, (int32_t)t0, (int32_t)box2, es,
                          (int32_t)(uint32_t)sp[0], (int32_t)(sp[0] >> 32), (int32_t)(uint32_t)sp[1], (int32_t)(sp[1] >> 32),
                          (int32_t)(uint32_t)sp[2], (int32_t)(sp[2] >> 32), (int32_t)(uint32_t)dp[0], (int32_t)(dp[0] >> 32),
@@ -2546,6 +2548,19 @@ size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 }  // namespace
 
 extern "C" {
+
+iree_b200_status_t iree_b200_uk_status(iree_b200_context_t* context) {
+  if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  if (!context->tiling_scratch) return IREE_B200_STATUS_OK;  // no TMA pack / unpack was ever dispatched
+  uint32_t status = 0;
+  uint8_t* word = static_cast<uint8_t*>(context->tiling_scratch) + kTilingStatusOffset;
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_d2h(context->device, word, &status, sizeof status));
+  B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(context->device));
+  if (status == 0) return IREE_B200_STATUS_OK;
+  B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(context->device, word, 4, 0));
+  if (status == 5) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "a pack / unpack kernel rejected its arguments (shape / alignment)");
+  return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "a pack / unpack kernel gave up waiting for one of its copies (wait id %u)", status);
+}
 
 iree_b200_status_t iree_b200_uk_pack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
                                      int64_t in_stride0, int64_t in_stride1, void* out_buffer, int64_t out_offset,

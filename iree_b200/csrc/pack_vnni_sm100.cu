@@ -17,8 +17,8 @@
 //                into a 4-stage ring
 //   warps 1-8  : interleave into one of two output buffers; their first thread issues the bulk stores
 //
-// Bindings: in, out, template (the 128-byte rank-4 map for 1-byte elements, no swizzle), scratch (256
-// bytes per CTA). Constants: K, N, the matrix's row pitch, N1, K1 and the pitch of out's outermost
+// Bindings: in, out, template (the 128-byte rank-4 map for 1-byte elements, no swizzle), scratch (a status
+// word, then from byte 1024 on 256 bytes per CTA). Constants: K, N, the matrix's row pitch, N1, K1 and the pitch of out's outermost
 // dimension, in elements (= bytes).
 #include <stdint.h>
 
@@ -68,12 +68,16 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
   // What the host checks, checked again: nothing misaligned may reach the TMA unit or a bulk copy.
   const bool bad = K <= 0 || N <= 0 || N1 <= 0 || K1 <= 0 || in_pitch < N || (in_pitch & 15) || (out_pitch & 15) ||
                    out_pitch < K1 * 32 || (reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15);
-  if (bad) return;  // the host never launches this; the destination stays as it was
 
   const int groups_n = (N1 + kPvTilesN - 1) / kPvTilesN, groups_k = (K1 + kPvTilesK - 1) / kPvTilesK;
   const int64_t regions = static_cast<int64_t>(groups_n) * groups_k;
   const int64_t mine = regions > blockIdx.x ? (regions - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  uint8_t* my_map = static_cast<uint8_t*>(scratch) + blockIdx.x * 256;
+  uint8_t* my_map = static_cast<uint8_t*>(scratch) + 1024 + blockIdx.x * 256;
+  uint32_t* status = static_cast<uint32_t*>(scratch);  // word 0: first failure of any launch since the host last looked
+  if (bad) {  // the host never launches this; the destination stays as it was
+    if (threadIdx.x == 0) atomicCAS(status, 0u, static_cast<uint32_t>(kStatusBadArgument));
+    return;
+  }
 
   if (threadIdx.x == 0) {
     abort_word = 0;
@@ -180,6 +184,7 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
   }
   __syncthreads();
   if (abort_word) {
+    if (threadIdx.x == 0) atomicCAS(status, 0u, static_cast<uint32_t>(kStatusTimeoutFull));
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) {
     }

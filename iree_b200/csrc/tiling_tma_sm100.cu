@@ -13,7 +13,7 @@
 // in flight over an eight-stage ring.
 //
 // Bindings: source, destination, template (one 128-byte rank-4 map of the element size, no swizzle),
-// scratch (256 bytes per CTA). Constants: the four extents in elements, tiles per box, element size, and
+// scratch (a status word, then from byte 1024 on 256 bytes per CTA). Constants: the four extents in elements, tiles per box, element size, and
 // the three outer pitches in bytes (low, high word) of the source and of the destination.
 #include <stdint.h>
 
@@ -51,9 +51,12 @@ extern "C" __global__ void __launch_bounds__(32, 1)
              (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15);
   for (int i = 0; i < 2; ++i)
     for (int j = 0; j < 3; ++j) bad = bad || (pitch[i][j] & 15) || pitch[i][j] == 0 || pitch[i][j] >= (1ull << 40);
-  if (bad) return;  // the host never launches this; the destination stays as it was
-
-  uint8_t* my_maps = static_cast<uint8_t*>(scratch) + blockIdx.x * 256;
+  uint8_t* my_maps = static_cast<uint8_t*>(scratch) + 1024 + blockIdx.x * 256;
+  uint32_t* status = static_cast<uint32_t*>(scratch);  // word 0: first failure of any launch since the host last looked
+  if (bad) {  // the host never launches this; the destination stays as it was
+    if (lane == 0) atomicCAS(status, 0u, static_cast<uint32_t>(kStatusBadArgument));
+    return;
+  }
   for (int i = 0; i < 2; ++i)
     reinterpret_cast<uint32_t*>(map_stage[i])[lane] = static_cast<const uint32_t*>(templates)[lane];
   __syncwarp();
@@ -119,6 +122,7 @@ extern "C" __global__ void __launch_bounds__(32, 1)
   }
   bulk_wait_group<0>();
   if (!ok) {
+    atomicCAS(status, 0u, static_cast<uint32_t>(kStatusTimeoutFull));
     // a load that never completed may still land: give it a bounded grace period before the CTA exits
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) {

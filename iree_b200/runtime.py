@@ -386,6 +386,10 @@ class Context:
             i64(out_offset), i64(out_stride0), i64(out_stride1), i64(in_size0), i64(in_size1), i64(in_size2),
             i64(in_size3), i64(out_size0), i64(out_size1), C.c_uint32(flags)))
 
+    def uk_status(self) -> None:
+        """Raises if a pack / unpack kernel reported a rejected argument or a wait that ran out."""
+        check(library().iree_b200_uk_status(self.handle))
+
     def uk_mmt4d_workspace(self, M, N, K, M0, N0, K0, flags) -> DeviceBuffer:
         nbytes = int(library().iree_b200_uk_mmt4d_workspace_bytes(C.c_int64(M), C.c_int64(N), C.c_int64(K), C.c_int32(M0),
                                                                   C.c_int32(N0), C.c_int32(K0), C.c_uint32(flags)))
@@ -476,6 +480,7 @@ def pack_numpy(ctx: Context, x: np.ndarray, tile, transpose_inner=False, transpo
     ctx.uk_pack(dev_in, offset, stride0, stride1, dev_out, 0, out_shape[1] * out_shape[2] * out_shape[3],
                 out_shape[2] * out_shape[3], x.shape[0], x.shape[1], *out_shape, padding, flags)
     out = dev_out.download(x.dtype, out_shape)
+    ctx.uk_status()
     dev_in.free()
     dev_out.free()
     return out
@@ -494,6 +499,7 @@ def unpack_numpy(ctx: Context, x4: np.ndarray, out_shape, transpose_inner=False,
     ctx.uk_unpack(dev_in, 0, x4.shape[1] * x4.shape[2] * x4.shape[3], x4.shape[2] * x4.shape[3], dev_out, 0, out_shape[1], 1,
                   *x4.shape, out_shape[0], out_shape[1], flags)
     out = dev_out.download(x4.dtype, tuple(out_shape))
+    ctx.uk_status()
     dev_in.free()
     dev_out.free()
     return out

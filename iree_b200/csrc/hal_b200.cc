@@ -2426,8 +2426,7 @@ iree_b200_status_t pack_rhs_16x2(iree_b200_context_t* ctx, const void* in, void*
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
   *dispatched = true;
-  return iree_hal_b200_command_buffer_dispatch(cb, ctx->executable, ord, 4, 6, static_cast<uint32_t>(regions < ctas ? regions : ctas), 1,
-                                               1);
+  return dispatch_self_ordering(ctx, ord, 4, 6, static_cast<uint32_t>(regions < ctas ? regions : ctas));
 }
 
 // pack / unpack as a pure TMA copy (tiling_tma_sm100.cu), for the shapes it takes: tiles not transposed
@@ -2476,8 +2475,7 @@ iree_b200_status_t tiling_by_tma(iree_b200_context_t* ctx, bool pack, int es, co
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
   *dispatched = true;
-  return iree_hal_b200_command_buffer_dispatch(cb, ctx->executable, ord, 4, 18, static_cast<uint32_t>(regions < sms ? regions : sms),
-                                               1, 1);
+  return dispatch_self_ordering(ctx, ord, 4, 18, static_cast<uint32_t>(regions < sms ? regions : sms));
 }
 
 // Shared by pack (row-major -> tiled) and unpack; `rm_*` describe the row-major side.
@@ -2649,7 +2647,7 @@ static iree_b200_status_t mmt4d_direct(iree_b200_context_t* context, const Mmt4d
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
   B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, constants, sizeof constants));
   *dispatched = true;
-  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 4, 7, grid, 1, 1);
+  return dispatch_self_ordering(context, ord, 4, 7, grid);
 }
 
 iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* lhs_buffer, int64_t lhs_offset,

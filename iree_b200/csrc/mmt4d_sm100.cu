@@ -114,7 +114,10 @@ __device__ __forceinline__ void mmt4d_body(const void* __restrict__ lhs, const v
                    (reinterpret_cast<uintptr_t>(out) & 31) || ((static_cast<int64_t>(s.lhs_stride0) * kElem) & 15) ||
                    ((static_cast<int64_t>(s.rhs_stride0) * kElem) & 15) ||
                    ((static_cast<int64_t>(s.out_stride0) * kOutBytes) & 31) || s.lhs_stride0 <= 0 || s.rhs_stride0 <= 0;
+  // The next dispatch on the stream may be launched from here on; it orders itself on the device.
+  grid_launch_dependents();
   if (bad) {
+    grid_dependency_wait();
     if (threadIdx.x == 0) report(ws, kStatusBadArgument, 2);
     return;
   }
@@ -145,6 +148,9 @@ __device__ __forceinline__ void mmt4d_body(const void* __restrict__ lhs, const v
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Launched early under a programmatic dependency: only this CTA's shared and tensor memory was
+  // touched above; global memory is read and written only once the dispatch ahead is complete.
+  grid_dependency_wait();
 
   // m fastest inside a column of tiles: consecutive CTAs share the right operand's tiles.
   auto tile_coords = [&](int t, int& tm, int& tn) {

@@ -74,6 +74,10 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
   const int64_t mine = regions > blockIdx.x ? (regions - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   uint8_t* my_map = static_cast<uint8_t*>(scratch) + 1024 + blockIdx.x * 256;
   uint32_t* status = static_cast<uint32_t*>(scratch);  // word 0: first failure of any launch since the host last looked
+  // The next dispatch on the stream may be launched from here on; this one touches global memory (its
+  // map slot included) only once the dispatch ahead is complete.
+  grid_launch_dependents();
+  grid_dependency_wait();
   if (bad) {  // the host never launches this; the destination stays as it was
     if (threadIdx.x == 0) atomicCAS(status, 0u, static_cast<uint32_t>(kStatusBadArgument));
     return;

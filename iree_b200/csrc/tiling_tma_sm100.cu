@@ -53,6 +53,11 @@ extern "C" __global__ void __launch_bounds__(32, 1)
     for (int j = 0; j < 3; ++j) bad = bad || (pitch[i][j] & 15) || pitch[i][j] == 0 || pitch[i][j] >= (1ull << 40);
   uint8_t* my_maps = static_cast<uint8_t*>(scratch) + 1024 + blockIdx.x * 256;
   uint32_t* status = static_cast<uint32_t*>(scratch);  // word 0: first failure of any launch since the host last looked
+  // The next dispatch on the stream may be launched from here on; this one touches global memory (its
+  // map slot included: the dispatch ahead may be a launch of this kernel still using the same slots) only
+  // once the dispatch ahead is complete.
+  grid_launch_dependents();
+  grid_dependency_wait();
   if (bad) {  // the host never launches this; the destination stays as it was
     if (lane == 0) atomicCAS(status, 0u, static_cast<uint32_t>(kStatusBadArgument));
     return;

@@ -136,6 +136,13 @@ def cpu_arm(wl, steps=1, warmup=0, world=1, budget_s=1.5):
             def once():
                 fn(arrays[0], (N // 16, K // 2, 16, 2), True, True)
             ops_per, byts_per = 0.0, 2.0 * arrays[0].nbytes
+        elif wl.op == "pack_lhs":
+            fn = oracle.pack_ref if use_ref else oracle.pack_port
+            sample = sample.replace("iree_uk_pack_lhs", "iree_uk_pack")
+
+            def once():
+                fn(arrays[0], (wl.M // 16, wl.K // 2, 16, 2), False, False)
+            ops_per, byts_per = 0.0, 2.0 * arrays[0].nbytes
         elif wl.op == "unpack":
             fn = oracle.unpack_ref if use_ref else oracle.unpack_port
 

@@ -67,6 +67,9 @@ def workloads():
     w["f2_pack_rhs_c3"] = Workload("f2_pack_rhs_c3", "tiling", "pack of the C3 int8 weight matrix [4096, 11008] into RHS "
                                    "tiles [688, 2048, 16, 2] (transpose inner + outer)", "GB/s", "hbm", "u8", op="pack",
                                    M=0, N=11008, K=4096)
+    w["f2_pack_lhs_c3"] = Workload("f2_pack_lhs_c3", "tiling", "pack of C3 M=4096 int8 activations [4096, 4096] into LHS tiles "
+                                   "[256, 2048, 16, 2] (no transposes)", "GB/s", "hbm", "u8", op="pack_lhs",
+                                   M=4096, N=0, K=4096)
     w["f2_unpack_acc_c2"] = Workload("f2_unpack_acc_c2", "tiling", "unpack of a C2-sized f32 accumulator [256, 256, 16, 16] "
                                      "to row-major [4096, 4096]", "GB/s", "hbm", "u32", op="unpack", M=4096, N=4096, K=0)
     w["f2_mmt4d_c1"] = Workload("f2_mmt4d_c1", "tiling", "mmt4d s8s8s32 on C1-sized tiled operands [64, 512, 16, 2] x "
@@ -92,6 +95,8 @@ def algorithmic(wl, n_local=None):
     if wl.family == "tiling":
         if wl.op == "pack":
             return 0.0, 2.0 * wl.K * wl.N
+        if wl.op == "pack_lhs":
+            return 0.0, 2.0 * wl.M * wl.K
         if wl.op == "unpack":
             return 0.0, 2.0 * wl.M * wl.N * 4
         return 2.0 * wl.M * wl.N * wl.K, float(wl.M * wl.K + wl.N * wl.K + wl.M * wl.N * 4)
@@ -359,6 +364,9 @@ def tiling_operands(wl):
     if wl.op == "pack":
         _, w, _, _ = gen.c3_w8a8(1)            # the [K, N] int8 weight matrix of the W8A8 configuration
         return (w,)
+    if wl.op == "pack_lhs":
+        rng = np.random.default_rng(2)
+        return (rng.integers(-128, 128, (wl.M, wl.K), dtype=np.int8),)
     if wl.op == "unpack":
         rng = np.random.default_rng(1)
         return (rng.standard_normal((wl.M // 16, wl.N // 16, 16, 16), dtype=np.float32),)
@@ -378,6 +386,8 @@ def tiling_state(ctx, wl):
     if wl.op == "pack":
         K, N = arrays[0].shape
         out_shape, out_dtype = (N // 16, K // 2, 16, 2), np.int8
+    elif wl.op == "pack_lhs":
+        out_shape, out_dtype = (wl.M // 16, wl.K // 2, 16, 2), np.int8
     elif wl.op == "unpack":
         out_shape, out_dtype = (wl.M, wl.N), np.float32
     else:
@@ -396,6 +406,9 @@ def tiling_state(ctx, wl):
             K, N = arrays[0].shape
             ctx.uk_pack(ins[0], 0, N, 1, out, 0, (K // 2) * 32, 32, K, N, N // 16, K // 2, 16, 2, 0,
                         rt.UK_PACK_TYPE[1] | rt.UK_TRANSPOSE_INNER | rt.UK_TRANSPOSE_OUTER)
+        elif wl.op == "pack_lhs":
+            ctx.uk_pack(ins[0], 0, wl.K, 1, out, 0, (wl.K // 2) * 32, 32, wl.M, wl.K, wl.M // 16, wl.K // 2, 16, 2, 0,
+                        rt.UK_PACK_TYPE[1])
         elif wl.op == "unpack":
             ctx.uk_unpack(ins[0], 0, (wl.N // 16) * 256, 256, out, 0, wl.N, 1, wl.M // 16, wl.N // 16, 16, 16, wl.M, wl.N,
                           rt.UK_PACK_TYPE[4])

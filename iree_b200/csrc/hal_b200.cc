@@ -1256,6 +1256,7 @@ const EntryDecl kEntries[] = {
     {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kMmt4dSmemBytes},
     {"b200_tiling_tma", {32, 1, 1}, 1024 + 8 * 16384 + 128},
     {"b200_pack_i8_rhs_16x2", {288, 1, 1}, 1024 + 4 * 16384 + 2 * 8 * (64 * 32 + 32) + 128},
+    {"b200_pack_lhs_16x2b", {288, 1, 1}, 1024 + 4 * 16384 + 2 * 8 * (64 * 32 + 32) + 128},
     {"b200_pack_b8", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b16", {256, 1, 1}, kTilingStageBytes},
     {"b200_pack_b32", {256, 1, 1}, kTilingStageBytes},
@@ -2429,6 +2430,40 @@ iree_b200_status_t pack_rhs_16x2(iree_b200_context_t* ctx, const void* in, void*
   return dispatch_self_ordering(ctx, ord, 4, 6, static_cast<uint32_t>(regions < ctas ? regions : ctas));
 }
 
+// The left-hand side of the same family: tiles of sixteen rows x two bytes without transposes (int8 16 x 2,
+// f16 / bf16 16 x 1), same kernel file, two-byte pieces of sixteen rows gathered into a tile.
+iree_b200_status_t pack_lhs_16x2b(iree_b200_context_t* ctx, int es, const void* in, void* out, int64_t rows, int64_t cols,
+                                  int64_t rm_stride0, int64_t rm_stride1, int64_t t0, int64_t t1, int64_t t2, int64_t t3,
+                                  int64_t t_stride0, uint32_t kernel_flags, uint64_t padding, bool* dispatched) {
+  *dispatched = false;
+  if ((kernel_flags & (kUkTransposeInner | kUkTransposeOuter | kTilingAccumulateI32 | kTilingAccumulateF32)) || rm_stride1 != 1)
+    return IREE_B200_STATUS_OK;
+  if (t2 != 16 || t3 * es != 2) return IREE_B200_STATUS_OK;
+  const bool ragged = t0 * 16 != rows || t1 * t3 != cols;
+  const uint64_t pad_mask = es == 1 ? 0xffull : 0xffffull;
+  if (ragged && (padding & pad_mask)) return IREE_B200_STATUS_OK;  // the TMA unit fills with zero
+  if (t0 * 16 < rows || t1 * t3 < cols || rm_stride0 < cols || t_stride0 < t1 * 16 * t3) return IREE_B200_STATUS_OK;
+  const int64_t in_pitch = rm_stride0 * es, out_pitch = t_stride0 * es, row_bytes = cols * es;
+  if ((in_pitch & 15) || (out_pitch & 15) || !fits_i32(in_pitch) || !fits_i32(out_pitch) || !fits_i32(row_bytes) ||
+      ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15))
+    return IREE_B200_STATUS_OK;
+  const int ctas = 2 * usable_sms(ctx);
+  if (ctas > kTilingScratchSlots) return IREE_B200_STATUS_OK;
+  B200_RETURN_IF_ERROR(ensure_tiling_scratch(ctx));
+  const int32_t ord = iree_hal_b200_executable_lookup(ctx->executable, "b200_pack_lhs_16x2b");
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_pack_lhs_16x2b missing from the executable");
+  const int64_t regions = ((t0 + 7) / 8) * ((t1 + 63) / 64);
+  uint8_t* scratch = static_cast<uint8_t*>(ctx->tiling_scratch);
+  iree_hal_b200_descriptor_set_binding_t bindings[4] = {
+      {0, const_cast<void*>(in)}, {1, out}, {2, scratch}, {3, scratch + kTilingStatusOffset}};
+  const int32_t c[6] = {(int32_t)rows, (int32_t)row_bytes, (int32_t)in_pitch, (int32_t)t0, (int32_t)t1, (int32_t)out_pitch};
+  auto* cb = ctx->command_buffer;
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 4, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
+  *dispatched = true;
+  return dispatch_self_ordering(ctx, ord, 4, 6, static_cast<uint32_t>(regions < ctas ? regions : ctas));
+}
+
 // pack / unpack as a pure TMA copy (tiling_tma_sm100.cu), for the shapes it takes: tiles not transposed
 // inside, tile rows of whole 16-byte pieces, a matrix the tiles cover exactly, 16-byte aligned addresses
 // and pitches, no accumulation. Everything else goes to the staging kernels.
@@ -2437,7 +2472,13 @@ iree_b200_status_t tiling_by_tma(iree_b200_context_t* ctx, bool pack, int es, co
                                  int64_t rm_size1, int64_t rm_stride0, int64_t rm_stride1, int64_t t0, int64_t t1,
                                  int64_t t2, int64_t t3, int64_t t_stride0, uint32_t kernel_flags, bool* dispatched) {
   *dispatched = false;
-  const bool ti = kernel_flags & kUkTransposeInner, to = kernel_flags & kUkTransposeOuter;
+  bool ti = kernel_flags & kUkTransposeInner;
+  const bool to = kernel_flags & kUkTransposeOuter;
+  if (ti && t3 == 1) {  // a transposed tile one row high is that row: [t2][1] in memory = [1][t2] not transposed
+    t3 = t2;
+    t2 = 1;
+    ti = false;
+  }
   if (ti || (kernel_flags & (kTilingAccumulateI32 | kTilingAccumulateF32)) || rm_stride1 != 1) return IREE_B200_STATUS_OK;
   const int64_t outer0 = to ? t1 : t0, outer1 = to ? t0 : t1;  // tiles along matrix rows / columns
   if (outer0 * t2 != rm_size0 || outer1 * t3 != rm_size1) return IREE_B200_STATUS_OK;
@@ -2498,6 +2539,11 @@ iree_b200_status_t tiling_dispatch(iree_b200_context_t* ctx, bool pack, int es, 
     if (pack && es == 1) {
       B200_RETURN_IF_ERROR(pack_rhs_16x2(ctx, in, out, rm_size0, rm_size1, rm_stride0, rm_stride1, t0, t1, t2, t3, t_stride0,
                                          kernel_flags, padding, &dispatched));
+      if (dispatched) return IREE_B200_STATUS_OK;
+    }
+    if (pack && es <= 2) {
+      B200_RETURN_IF_ERROR(pack_lhs_16x2b(ctx, es, in, out, rm_size0, rm_size1, rm_stride0, rm_stride1, t0, t1, t2, t3,
+                                          t_stride0, kernel_flags, padding, &dispatched));
       if (dispatched) return IREE_B200_STATUS_OK;
     }
     B200_RETURN_IF_ERROR(tiling_by_tma(ctx, pack, es, in, out, rm_size0, rm_size1, rm_stride0, rm_stride1, t0, t1, t2, t3,

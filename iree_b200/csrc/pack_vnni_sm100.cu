@@ -1,25 +1,28 @@
-// pack of a row-major int8 matrix [K, N] into the right-hand-side tiles of the x86-64 VNNI mmt4d,
-// out[N1, K1, 16, 2] with out[n1, k1, n0, k0] = in[2 * k1 + k0, 16 * n1 + n0]
-// (runtime/src/iree/builtins/ukernel/pack.c:52-100 with TRANSPOSE_INNER and TRANSPOSE_OUTER, 1-byte
-// elements, tile 16 x 2): the one pack of the data-tiled int8 matmul that moves bytes inside a 16-byte
-// piece (rows 2 * k1 and 2 * k1 + 1 are interleaved byte by byte).
+// The two packs of the data-tiled matmul that move bytes inside a 16-byte piece
+// (runtime/src/iree/builtins/ukernel/pack.c:52-100), for tiles of 16 x 2 bytes:
+//   right-hand side (b200_pack_i8_rhs_16x2): int8 [K, N] -> out[N1, K1, 16, 2] with TRANSPOSE_INNER and
+//     TRANSPOSE_OUTER, out[n1, k1, n0, k0] = in[2 k1 + k0, 16 n1 + n0]: rows 2 k1 and 2 k1 + 1 are
+//     interleaved byte by byte;
+//   left-hand side (b200_pack_lhs_16x2b): [M, C bytes] -> out[M1, C / 2, 16, 2 bytes] without transposes,
+//     out[m1, c1, m0, :] = in[16 m1 + m0, 2 c1 .. 2 c1 + 1]: int8 16 x 2 tiles, and f16 / bf16 16 x 1
+//     tiles (the two bytes are one element): two-byte pieces of sixteen rows are gathered into a tile.
 //
-// Both sides of the copy are long contiguous runs: a region of 128 matrix rows x 128 columns arrives
-// as one TMA box (128-byte rows), and leaves as eight runs of 64 tiles = 2 KiB each (the tiles of one n1
-// are consecutive along k1) written by bulk copies from shared memory. In between, 256 threads read two
-// 8-byte words (the same eight columns of a row pair), interleave them with four byte permutes and write
-// one 16-byte half tile. Rows and columns past the matrix read as zero (the TMA unit's fill), which is
-// the padding value this kernel supports.
+// Both sides of the copy are long contiguous runs: a region of 128 matrix rows x 128 bytes arrives as
+// one TMA box (128-byte rows), and leaves as eight runs of 64 tiles = 2 KiB each (the tiles of one outer
+// index are consecutive along the other) written by bulk copies from shared memory. In between, 256
+// threads build 16-byte half tiles: two 8-byte words of a row pair interleaved with four byte permutes
+// (right-hand side), or eight 2-byte pieces of eight rows (left-hand side). Rows and columns past the
+// matrix read as zero (the TMA unit's fill), which is the padding value these kernels support.
 //
 // Two CTAs per SM (100 KB of shared memory each), so that eight region loads are in flight on every SM.
 //
 //   warp 0     : builds this CTA's tensor map over the matrix in its scratch slot, then loads regions
 //                into a 4-stage ring
-//   warps 1-8  : interleave into one of two output buffers; their first thread issues the bulk stores
+//   warps 1-8  : build half tiles into one of two output buffers; their first thread issues the bulk stores
 //
 // Bindings: in, out, template (the 128-byte rank-4 map for 1-byte elements, no swizzle), scratch (a status
-// word, then from byte 1024 on 256 bytes per CTA). Constants: K, N, the matrix's row pitch, N1, K1 and the pitch of out's outermost
-// dimension, in elements (= bytes).
+// word, then from byte 1024 on 256 bytes per CTA). Constants: rows and bytes per row of the matrix, its
+// row pitch in bytes, the two outer extents of out and the pitch of its outermost dimension in bytes.
 #include <stdint.h>
 
 #include "sm100_ptx.cuh"
@@ -45,16 +48,26 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(addr) : "memory");
   return r;
 }
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t r;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(r) : "r"(addr) : "memory");
+  return r;
+}
 __device__ __forceinline__ void sts128v(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 }  // namespace b200
 
-extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
-    b200_pack_i8_rhs_16x2(const void* in, void* out, const void* templates, void* scratch, int K, int N, int in_pitch,
-                          int N1, int K1, int out_pitch) {
-  using namespace b200;
+namespace b200 {
+
+// RHS: matrix rows are K (tile index k1 = row / 2), columns N (n1 = column / 16); out is [N1][K1].
+// LHS (!RHS): matrix rows are M (m1 = row / 16), byte columns C (c1 = column / 2); out is [M1][C1]; in the
+// code below N1 then stands for M1 and K1 for C1: the first outer index of out and the one whose tiles
+// are consecutive in memory.
+template <bool RHS>
+__device__ __forceinline__ void pack_16x2_body(const void* in, void* out, const void* templates, void* scratch, int K,
+                                               int N, int in_pitch, int N1, int K1, int out_pitch) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ alignas(128) uint8_t map_stage[128];
   __shared__ uint32_t abort_word;
@@ -69,6 +82,7 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
   const bool bad = K <= 0 || N <= 0 || N1 <= 0 || K1 <= 0 || in_pitch < N || (in_pitch & 15) || (out_pitch & 15) ||
                    out_pitch < K1 * 32 || (reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15);
 
+  // a region is eight tiles of the first outer index x 64 of the second: 128 x 128 bytes of the matrix
   const int groups_n = (N1 + kPvTilesN - 1) / kPvTilesN, groups_k = (K1 + kPvTilesK - 1) / kPvTilesK;
   const int64_t regions = static_cast<int64_t>(groups_n) * groups_k;
   const int64_t mine = regions > blockIdx.x ? (regions - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -118,11 +132,16 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
   }
   __syncthreads();
 
-  // column groups fastest: CTAs that run together read neighbouring pieces of the same matrix rows
+  // groups along the matrix's columns fastest: CTAs that run together read neighbouring pieces of the same rows
   auto region_coords = [&](int64_t j, int& gn, int& gk) {
     const int64_t r = blockIdx.x + j * gridDim.x;
-    gn = static_cast<int>(r % groups_n);
-    gk = static_cast<int>(r / groups_n);
+    if constexpr (RHS) {
+      gn = static_cast<int>(r % groups_n);
+      gk = static_cast<int>(r / groups_n);
+    } else {
+      gk = static_cast<int>(r % groups_k);
+      gn = static_cast<int>(r / groups_k);
+    }
   };
 
   if (warp == 0) {
@@ -137,7 +156,10 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
         int gn, gk;
         region_coords(j, gn, gk);
         mbar_arrive_expect_tx(full_bar(st), kPvInBytes);
-        tma_load_4d(smem_base + st * kPvInBytes, my_map, full_bar(st), gn * kPvRegionCols, gk * kPvRegionRows, 0, 0);
+        if constexpr (RHS)
+          tma_load_4d(smem_base + st * kPvInBytes, my_map, full_bar(st), gn * kPvRegionCols, gk * kPvRegionRows, 0, 0);
+        else  // rows follow the first outer index, byte columns the second
+          tma_load_4d(smem_base + st * kPvInBytes, my_map, full_bar(st), gk * kPvRegionCols, gn * kPvRegionRows, 0, 0);
       }
     }
   } else {
@@ -160,13 +182,29 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
         ok = false;
         break;
       }
-      const uint32_t src = smem_base + st * kPvInBytes + c * 8;
+      if constexpr (RHS) {
+        const uint32_t src = smem_base + st * kPvInBytes + c * 8;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k1l = (t >> 4) + 16 * i;
-        const uint2 a = lds64(src + (2 * k1l) * kPvRegionCols), b = lds64(src + (2 * k1l + 1) * kPvRegionCols);
-        sts128v(ob + n1l * kPvOutPitch + k1l * 32 + half * 16, __byte_perm(a.x, b.x, 0x5140), __byte_perm(a.x, b.x, 0x7362),
-                __byte_perm(a.y, b.y, 0x5140), __byte_perm(a.y, b.y, 0x7362));
+        for (int i = 0; i < 4; ++i) {
+          const int k1l = (t >> 4) + 16 * i;
+          const uint2 a = lds64(src + (2 * k1l) * kPvRegionCols), b = lds64(src + (2 * k1l + 1) * kPvRegionCols);
+          sts128v(ob + n1l * kPvOutPitch + k1l * 32 + half * 16, __byte_perm(a.x, b.x, 0x5140), __byte_perm(a.x, b.x, 0x7362),
+                  __byte_perm(a.y, b.y, 0x5140), __byte_perm(a.y, b.y, 0x7362));
+        }
+      } else {
+        // Half tile (outer tile o, eight rows h, column pair c1): a warp takes 32 consecutive column pairs
+        // of the same eight rows, so each of its eight reads is 64 consecutive bytes of one row.
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int u = t + 256 * i;
+          const int c1l = u & 63, h = (u >> 6) & 1, o = u >> 7;
+          const uint32_t src = smem_base + st * kPvInBytes + (o * 16 + h * 8) * kPvRegionCols + c1l * 2;
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            w[j] = lds16(src + (2 * j) * kPvRegionCols) | (lds16(src + (2 * j + 1) * kPvRegionCols) << 16);
+          sts128v(ob + o * kPvOutPitch + c1l * 32 + h * 16, w[0], w[1], w[2], w[3]);
+        }
       }
       fence_proxy_async_smem();  // the bulk copies read these bytes through the async proxy
       __syncwarp();
@@ -193,4 +231,17 @@ extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
     while (global_timer_ns() - t0 < 200000ull) {
     }
   }
+}
+
+}  // namespace b200
+
+extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
+    b200_pack_i8_rhs_16x2(const void* in, void* out, const void* templates, void* scratch, int K, int N, int in_pitch,
+                          int N1, int K1, int out_pitch) {
+  b200::pack_16x2_body<true>(in, out, templates, scratch, K, N, in_pitch, N1, K1, out_pitch);
+}
+extern "C" __global__ void __launch_bounds__(b200::kPvThreads, 2)
+    b200_pack_lhs_16x2b(const void* in, void* out, const void* templates, void* scratch, int M, int C, int in_pitch,
+                        int M1, int C1, int out_pitch) {
+  b200::pack_16x2_body<false>(in, out, templates, scratch, M, C, in_pitch, M1, C1, out_pitch);
 }

@@ -347,3 +347,33 @@ def test_overlapped_data_tiled_chain_equals_the_reference(ctx, graph):
     ctx.uk_status()
     for x in (da, db, pl, pr, po, out, ws):
         x.free()
+
+
+@pytest.mark.parametrize("dtype,tile", [(np.int8, (16, 2)), (np.float16, (16, 1))])
+def test_left_hand_side_pack_of_two_byte_tile_rows(ctx, dtype, tile):
+    """[M, K] -> [M1, K1, 16, K0] without transposes where a tile row is two bytes (int8 16 x 2, f16
+    16 x 1): the TMA-box / gather / bulk-copy kernel against the staging kernel and the oracle, whole and
+    ragged matrices (zero padding), many regions per CTA."""
+    rng = np.random.default_rng(8)
+    t0, t1 = tile
+    for (M, K) in [(16, 2), (128, 128), (100, 61 * t1), (512, 4096), (1000, 130 * t1)]:
+        x = rng.integers(-100, 100, (M, K)).astype(dtype)
+        shape4 = (-(-M // t0), -(-K // t1), t0, t1)
+        want = oracle.pack_port(x, shape4, False, False)
+        got = pack_numpy(ctx, x, (t0, t1))
+        staged = pack_numpy(ctx, x, (t0, t1), extra_flags=rt.UK_PACK_NO_TMA)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (M, K)
+        assert np.array_equal(staged.view(np.uint8), want.view(np.uint8)), (M, K)
+
+
+def test_right_hand_side_pack_of_f16_tiles_is_a_tma_copy(ctx):
+    """[K, N] f16 -> [N1, K1, 16, 1] with both transposes: a transposed tile one row high is that row, so
+    the TMA-only copy takes it; equal to the staging kernel and the oracle."""
+    rng = np.random.default_rng(9)
+    for (K, N) in [(64, 16), (300, 160), (1024, 2048)]:
+        x = rng.standard_normal((K, N)).astype(np.float16)
+        want = oracle.pack_port(x, (N // 16, K, 16, 1), True, True)
+        got = pack_numpy(ctx, x, (1, 16), True, True)
+        staged = pack_numpy(ctx, x, (1, 16), True, True, extra_flags=rt.UK_PACK_NO_TMA)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), (K, N)
+        assert np.array_equal(staged.view(np.uint16), want.view(np.uint16)), (K, N)

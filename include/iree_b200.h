@@ -494,7 +494,14 @@ iree_b200_status_t iree_b200_context_set_reserved_sms(iree_b200_context_t* conte
  * memory even where the shape allows the copy to be done by the TMA unit alone. */
 #define IREE_B200_UK_FLAG_PACK_NO_TMA 0x40000
 /* iree_uk_pack: row-major [in_size0, in_size1] -> tiled [out_size0..3], ragged edge filled with
- * the low bytes of padding_value. out_stride1 must equal out_size2 * out_size3 (pack.c:72). */
+ * the low bytes of padding_value. out_stride1 must equal out_size2 * out_size3 (pack.c:72).
+ * Kernels, chosen from shape and alignment (results are the same bytes on every path): a copy done
+ * by the TMA unit alone when no element moves inside a 16-byte piece (no inner transpose, or a
+ * transposed tile one row high; tile rows of whole 16-byte pieces; a matrix the tiles cover exactly;
+ * 16-byte aligned addresses and pitches), in both directions; TMA box in / bulk copies out with a
+ * byte interleave or gather in shared memory for tiles of sixteen rows x two bytes (the int8 16x2
+ * right-hand side with both transposes, the int8 16x2 and f16 / bf16 16x1 left-hand sides; zero
+ * padding only); regions staged in shared memory for everything else. */
 iree_b200_status_t iree_b200_uk_pack(iree_b200_context_t* context, const void* in_buffer, int64_t in_offset,
                                      int64_t in_stride0, int64_t in_stride1, void* out_buffer, int64_t out_offset,
                                      int64_t out_stride0, int64_t out_stride1, int64_t in_size0, int64_t in_size1,

@@ -64,6 +64,8 @@ typedef struct iree_hal_b200_executable_t iree_hal_b200_executable_t;
 typedef struct iree_hal_b200_command_buffer_t iree_hal_b200_command_buffer_t;
 typedef struct iree_hal_b200_channel_t iree_hal_b200_channel_t;
 typedef struct iree_hal_b200_graph_t iree_hal_b200_graph_t;
+typedef struct iree_hal_b200_descriptor_set_layout_t iree_hal_b200_descriptor_set_layout_t;
+typedef struct iree_hal_b200_pipeline_layout_t iree_hal_b200_pipeline_layout_t;
 
 /* ---- device -------------------------------------------------------------------------------
  * Stands in for iree_hal_cuda_driver_create + device creation
@@ -171,6 +173,52 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
                                                          uint32_t binding_count, uint32_t constant_count,
                                                          uint32_t workgroup_x, uint32_t workgroup_y,
                                                          uint32_t workgroup_z);
+/* iree_hal_command_buffer_begin / _end (runtime/src/iree/hal/command_buffer.h:532-540): bracket a
+ * recording. Optional here (the other commands do not require them); FAILED_PRECONDITION when
+ * unpaired. */
+iree_b200_status_t iree_hal_b200_command_buffer_begin(iree_hal_b200_command_buffer_t* command_buffer);
+iree_b200_status_t iree_hal_b200_command_buffer_end(iree_hal_b200_command_buffer_t* command_buffer);
+/* iree_hal_command_buffer_execution_barrier (command_buffer.h:563-571; the CUDA driver's is a no-op
+ * on its in-order stream, stream_command_buffer.c:234-250, and a plain dependency between graph
+ * nodes). Commands here already execute in recording order; what the barrier adds is that the dispatch
+ * after it is not launched early under set_dispatch_overlap. The masks and flags are accepted and
+ * ignored, as the reference's driver does; memory / buffer barrier lists are not taken. */
+iree_b200_status_t iree_hal_b200_command_buffer_execution_barrier(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                  uint32_t source_stage_mask, uint32_t target_stage_mask,
+                                                                  uint32_t flags);
+/* iree_hal_command_buffer_fill_buffer (command_buffer.h:623-627; stream_command_buffer.c:300-340):
+ * pattern_length 1, 2 or 4; offset and length aligned to it. Stream mode: cuMemsetD{8,16,32}Async;
+ * graph mode: a memset node. */
+iree_b200_status_t iree_hal_b200_command_buffer_fill_buffer(iree_hal_b200_command_buffer_t* command_buffer,
+                                                            void* target_device_ptr, size_t target_offset, size_t length,
+                                                            const void* pattern, size_t pattern_length);
+/* iree_hal_command_buffer_copy_buffer (command_buffer.h:650-654; stream_command_buffer.c:396-425),
+ * device to device; the ranges must not overlap. Stream mode: cuMemcpyDtoDAsync; graph mode: a memcpy
+ * node. */
+iree_b200_status_t iree_hal_b200_command_buffer_copy_buffer(iree_hal_b200_command_buffer_t* command_buffer,
+                                                            const void* source_device_ptr, size_t source_offset,
+                                                            void* target_device_ptr, size_t target_offset, size_t length);
+/* Descriptor-set and pipeline layouts (runtime/src/iree/hal/drivers/cuda/pipeline_layout.c:47-80 and
+ * :145-190): a set layout is its binding count; a pipeline layout records every set's count -- the
+ * kernel parameters of a dispatch are the bindings of set 0, then of set 1, ..., each set starting at
+ * the running sum of the counts before it -- and the push constant count, whose parameters follow the
+ * last set. The pipeline layout copies the counts; set layouts may be released after it was created. */
+iree_b200_status_t iree_hal_b200_descriptor_set_layout_create(iree_hal_b200_device_t* device, uint32_t binding_count,
+                                                              iree_hal_b200_descriptor_set_layout_t** out_layout);
+void iree_hal_b200_descriptor_set_layout_release(iree_hal_b200_descriptor_set_layout_t* layout);
+iree_b200_status_t iree_hal_b200_pipeline_layout_create(iree_hal_b200_device_t* device, uint32_t push_constant_count,
+                                                        uint32_t set_layout_count,
+                                                        iree_hal_b200_descriptor_set_layout_t* const* set_layouts,
+                                                        iree_hal_b200_pipeline_layout_t** out_layout);
+void iree_hal_b200_pipeline_layout_release(iree_hal_b200_pipeline_layout_t* layout);
+/* iree_hal_command_buffer_dispatch with the executable's pipeline layout (stream_command_buffer.c:530-603):
+ * parameters = every set's bound pointers in set order, then the layout's push constants. */
+iree_b200_status_t iree_hal_b200_command_buffer_dispatch_with_layout(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                     iree_hal_b200_executable_t* executable,
+                                                                     int32_t entry_point,
+                                                                     const iree_hal_b200_pipeline_layout_t* layout,
+                                                                     uint32_t workgroup_x, uint32_t workgroup_y,
+                                                                     uint32_t workgroup_z);
 /* Number of kernel launches this command buffer has issued (for launch accounting). */
 uint64_t iree_hal_b200_command_buffer_launch_count(const iree_hal_b200_command_buffer_t* command_buffer);
 /* Dispatch overlap (programmatic dependent launch; no counterpart in the reference's CUDA driver,
@@ -208,6 +256,12 @@ iree_b200_status_t iree_hal_b200_channel_create(iree_hal_b200_device_t* device, 
                                                 int32_t rank, int32_t count,
                                                 iree_hal_b200_channel_t** out_channel);
 void iree_hal_b200_channel_release(iree_hal_b200_channel_t* channel);
+/* iree_hal_channel_split (runtime/src/iree/hal/channel.h:85-96; drivers/cuda/nccl_channel.c:176-215, ncclCommSplit):
+ * every rank of base_channel calls it; ranks with the same non-negative color form a channel, ordered
+ * by key. A negative color (IREE_HAL_CHANNEL_NO_COLOR) takes part in the call and yields *out_channel
+ * = NULL. UNAVAILABLE with an NCCL older than 2.18. */
+iree_b200_status_t iree_hal_b200_channel_split(iree_hal_b200_channel_t* base_channel, int32_t color, int32_t key,
+                                               iree_hal_b200_channel_t** out_channel);
 int32_t iree_hal_b200_channel_rank(const iree_hal_b200_channel_t* channel);
 int32_t iree_hal_b200_channel_count(const iree_hal_b200_channel_t* channel);
 

@@ -93,6 +93,11 @@ struct CudaSymbols {
   CU_FN(cuMemcpyDtoDAsync, CUdeviceptr, CUdeviceptr, size_t, CUstream)
   CU_FN(cuLaunchKernelEx, const CUlaunchConfig*, CUfunction, void**, void**)
   CU_FN(cuGraphAddDependencies_v2, CUgraph, const CUgraphNode*, const CUgraphNode*, const CUgraphEdgeData*, size_t)
+  // optional (transfer commands)
+  CU_FN(cuMemsetD16Async, CUdeviceptr, unsigned short, size_t, CUstream)
+  CU_FN(cuMemsetD32Async, CUdeviceptr, unsigned int, size_t, CUstream)
+  CU_FN(cuGraphAddMemcpyNode, CUgraphNode*, CUgraph, const CUgraphNode*, size_t, const CUDA_MEMCPY3D*, CUcontext)
+  CU_FN(cuGraphAddMemsetNode, CUgraphNode*, CUgraph, const CUgraphNode*, size_t, const CUDA_MEMSET_NODE_PARAMS*, CUcontext)
   CU_FN(cuGetErrorName, CUresult, const char**)
   CU_FN(cuGetErrorString, CUresult, const char**)
   CU_FN(cuTensorMapEncodeTiled, CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -168,6 +173,10 @@ iree_b200_status_t ensure_cuda() {
       load_sym(g_cu.handle, "cuMemcpyDtoDAsync_v2", g_cu.cuMemcpyDtoDAsync);
       load_sym(g_cu.handle, "cuLaunchKernelEx", g_cu.cuLaunchKernelEx);
       load_sym(g_cu.handle, "cuGraphAddDependencies_v2", g_cu.cuGraphAddDependencies_v2);
+      load_sym(g_cu.handle, "cuMemsetD16Async", g_cu.cuMemsetD16Async);
+      load_sym(g_cu.handle, "cuMemsetD32Async", g_cu.cuMemsetD32Async);
+      load_sym(g_cu.handle, "cuGraphAddMemcpyNode", g_cu.cuGraphAddMemcpyNode);
+      load_sym(g_cu.handle, "cuGraphAddMemsetNode", g_cu.cuGraphAddMemsetNode);
       if (!ok) {
         g_cu.error = "CUDA driver library is missing required symbols";
         g_cu.handle = nullptr;
@@ -215,6 +224,9 @@ struct NcclSymbols {
   int (*ncclAllReduce)(const void*, void*, size_t, int, int, ncclComm_t, CUstream) = nullptr;  // optional
   int (*ncclGroupStart)() = nullptr;
   int (*ncclGroupEnd)() = nullptr;
+  int (*ncclCommSplit)(ncclComm_t, int, int, ncclComm_t*, void*) = nullptr;  // optional (NCCL >= 2.18)
+  int (*ncclCommCount)(const ncclComm_t, int*) = nullptr;                   // optional
+  int (*ncclCommUserRank)(const ncclComm_t, int*) = nullptr;                // optional
   const char* (*ncclGetErrorString)(int) = nullptr;
 };
 NcclSymbols g_nccl;
@@ -246,6 +258,9 @@ iree_b200_status_t ensure_nccl() {
       ok = load_sym(g_nccl.handle, "ncclCommDestroy", g_nccl.ncclCommDestroy) && ok;
       ok = load_sym(g_nccl.handle, "ncclAllGather", g_nccl.ncclAllGather) && ok;
       load_sym(g_nccl.handle, "ncclAllReduce", g_nccl.ncclAllReduce);
+      load_sym(g_nccl.handle, "ncclCommSplit", g_nccl.ncclCommSplit);
+      load_sym(g_nccl.handle, "ncclCommCount", g_nccl.ncclCommCount);
+      load_sym(g_nccl.handle, "ncclCommUserRank", g_nccl.ncclCommUserRank);
       ok = load_sym(g_nccl.handle, "ncclGroupStart", g_nccl.ncclGroupStart) && ok;
       ok = load_sym(g_nccl.handle, "ncclGroupEnd", g_nccl.ncclGroupEnd) && ok;
       ok = load_sym(g_nccl.handle, "ncclGetErrorString", g_nccl.ncclGetErrorString) && ok;
@@ -440,9 +455,21 @@ struct iree_hal_b200_command_buffer_t {
   // The next dispatches may start before the dispatch ahead of them has finished (programmatic
   // dependent launch); the caller vouches that their exports order themselves on the device.
   bool overlap = false;
+  bool open = false;             // between begin and end
+  bool barrier_pending = false;  // an execution barrier was recorded: the next dispatch takes a full dependency
   uint32_t constants[IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT] = {0};
   void* bindings[IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT][IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT] = {{nullptr}};
   uint64_t launches = 0;
+};
+
+struct iree_hal_b200_descriptor_set_layout_t {
+  uint32_t binding_count = 0;
+};
+struct iree_hal_b200_pipeline_layout_t {
+  // what pipeline_layout.c:178-188 records: every set's binding count and, through the running sum, the
+  // index of its first kernel parameter; the push constants follow the last set
+  std::vector<uint32_t> set_binding_counts;
+  uint32_t push_constant_count = 0;
 };
 
 struct iree_hal_b200_channel_t {
@@ -845,7 +872,8 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
     np.sharedMemBytes = e.smem;
     np.kernelParams = params;
     CUgraphNode node = nullptr;
-    const bool programmatic = command_buffer->overlap && command_buffer->last_node;
+    const bool programmatic = command_buffer->overlap && command_buffer->last_node && !command_buffer->barrier_pending;
+    command_buffer->barrier_pending = false;
     CU_RETURN_IF_ERROR(g_cu.cuGraphAddKernelNode(&node, command_buffer->recording,
                                                  command_buffer->last_node && !programmatic ? &command_buffer->last_node : nullptr,
                                                  command_buffer->last_node && !programmatic ? 1 : 0, &np),
@@ -867,7 +895,9 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
     ++command_buffer->recorded_nodes;
     return IREE_B200_STATUS_OK;
   }
-  if (command_buffer->overlap) {
+  const bool early = command_buffer->overlap && !command_buffer->barrier_pending;
+  command_buffer->barrier_pending = false;
+  if (early) {
     CUlaunchConfig config;
     memset(&config, 0, sizeof config);
     config.gridDimX = workgroup_x;
@@ -892,6 +922,195 @@ iree_b200_status_t iree_hal_b200_command_buffer_dispatch(iree_hal_b200_command_b
   }
   ++command_buffer->launches;
   return IREE_B200_STATUS_OK;
+}
+
+// ---- begin / end, barriers, transfer commands ---------------------------------------------------------
+iree_b200_status_t iree_hal_b200_command_buffer_begin(iree_hal_b200_command_buffer_t* command_buffer) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command_buffer is NULL");
+  if (command_buffer->open) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "command buffer is already recording");
+  command_buffer->open = true;
+  return IREE_B200_STATUS_OK;
+}
+iree_b200_status_t iree_hal_b200_command_buffer_end(iree_hal_b200_command_buffer_t* command_buffer) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command_buffer is NULL");
+  if (!command_buffer->open) return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "command buffer is not recording");
+  command_buffer->open = false;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_execution_barrier(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                  uint32_t source_stage_mask, uint32_t target_stage_mask,
+                                                                  uint32_t flags) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command_buffer is NULL");
+  (void)source_stage_mask;
+  (void)target_stage_mask;
+  (void)flags;
+  // Commands already execute in recording order (one stream; a linear chain of graph nodes). What a
+  // barrier changes here: the dispatch after it is not launched early, whatever the overlap setting.
+  command_buffer->barrier_pending = true;
+  return IREE_B200_STATUS_OK;
+}
+
+// A transfer command as a node of the recording (after the previous node) or on the dispatch stream.
+static iree_b200_status_t chain_node(iree_hal_b200_command_buffer_t* cb, CUgraphNode node) {
+  cb->last_node = node;
+  ++cb->recorded_nodes;
+  cb->barrier_pending = true;  // a kernel may not be launched early behind a copy or a fill
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_fill_buffer(iree_hal_b200_command_buffer_t* command_buffer,
+                                                            void* target_device_ptr, size_t target_offset, size_t length,
+                                                            const void* pattern, size_t pattern_length) {
+  if (!command_buffer || !pattern) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (pattern_length != 1 && pattern_length != 2 && pattern_length != 4)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "fill patterns must be 1, 2 or 4 bytes long (got %zu)", pattern_length);
+  if ((target_offset % pattern_length) || (length % pattern_length))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "fill offset and length must be aligned to the pattern length");
+  if (!length) return IREE_B200_STATUS_OK;
+  if (!target_device_ptr) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "target buffer is NULL");
+  uint32_t value = 0;
+  memcpy(&value, pattern, pattern_length);
+  iree_hal_b200_device_t* d = command_buffer->device;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  const CUdeviceptr dst = reinterpret_cast<CUdeviceptr>(static_cast<uint8_t*>(target_device_ptr) + target_offset);
+  const size_t count = length / pattern_length;
+  if (command_buffer->recording) {
+    if (!g_cu.cuGraphAddMemsetNode) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no cuGraphAddMemsetNode");
+    CUDA_MEMSET_NODE_PARAMS mp;
+    memset(&mp, 0, sizeof mp);
+    mp.dst = dst;
+    mp.elementSize = static_cast<unsigned>(pattern_length);
+    mp.value = value;
+    mp.width = count;
+    mp.height = 1;
+    CUgraphNode node = nullptr;
+    CU_RETURN_IF_ERROR(g_cu.cuGraphAddMemsetNode(&node, command_buffer->recording,
+                                                 command_buffer->last_node ? &command_buffer->last_node : nullptr,
+                                                 command_buffer->last_node ? 1 : 0, &mp, d->context),
+                       "cuGraphAddMemsetNode");
+    return chain_node(command_buffer, node);
+  }
+  command_buffer->barrier_pending = true;
+  if (pattern_length == 1) {
+    CU_RETURN_IF_ERROR(g_cu.cuMemsetD8Async(dst, static_cast<unsigned char>(value), count, d->stream), "cuMemsetD8Async");
+  } else if (pattern_length == 2) {
+    if (!g_cu.cuMemsetD16Async) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no cuMemsetD16Async");
+    CU_RETURN_IF_ERROR(g_cu.cuMemsetD16Async(dst, static_cast<unsigned short>(value), count, d->stream), "cuMemsetD16Async");
+  } else {
+    if (!g_cu.cuMemsetD32Async) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no cuMemsetD32Async");
+    CU_RETURN_IF_ERROR(g_cu.cuMemsetD32Async(dst, value, count, d->stream), "cuMemsetD32Async");
+  }
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_command_buffer_copy_buffer(iree_hal_b200_command_buffer_t* command_buffer,
+                                                            const void* source_device_ptr, size_t source_offset,
+                                                            void* target_device_ptr, size_t target_offset, size_t length) {
+  if (!command_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command_buffer is NULL");
+  if (!length) return IREE_B200_STATUS_OK;
+  if (!source_device_ptr || !target_device_ptr) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
+  const uint8_t* src = static_cast<const uint8_t*>(source_device_ptr) + source_offset;
+  uint8_t* dst = static_cast<uint8_t*>(target_device_ptr) + target_offset;
+  if (src < dst + length && dst < src + length)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "source and target ranges of a copy must not overlap");
+  iree_hal_b200_device_t* d = command_buffer->device;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  if (command_buffer->recording) {
+    if (!g_cu.cuGraphAddMemcpyNode) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no cuGraphAddMemcpyNode");
+    CUDA_MEMCPY3D cp;
+    memset(&cp, 0, sizeof cp);
+    cp.srcMemoryType = CU_MEMORYTYPE_DEVICE;
+    cp.srcDevice = reinterpret_cast<CUdeviceptr>(src);
+    cp.dstMemoryType = CU_MEMORYTYPE_DEVICE;
+    cp.dstDevice = reinterpret_cast<CUdeviceptr>(dst);
+    cp.WidthInBytes = length;
+    cp.Height = 1;
+    cp.Depth = 1;
+    CUgraphNode node = nullptr;
+    CU_RETURN_IF_ERROR(g_cu.cuGraphAddMemcpyNode(&node, command_buffer->recording,
+                                                 command_buffer->last_node ? &command_buffer->last_node : nullptr,
+                                                 command_buffer->last_node ? 1 : 0, &cp, d->context),
+                       "cuGraphAddMemcpyNode");
+    return chain_node(command_buffer, node);
+  }
+  if (!g_cu.cuMemcpyDtoDAsync) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no cuMemcpyDtoDAsync");
+  command_buffer->barrier_pending = true;
+  CU_RETURN_IF_ERROR(g_cu.cuMemcpyDtoDAsync(reinterpret_cast<CUdeviceptr>(dst), reinterpret_cast<CUdeviceptr>(src), length,
+                                            d->stream),
+                     "cuMemcpyDtoDAsync");
+  return IREE_B200_STATUS_OK;
+}
+
+// ---- pipeline layouts ------------------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_descriptor_set_layout_create(iree_hal_b200_device_t* device, uint32_t binding_count,
+                                                              iree_hal_b200_descriptor_set_layout_t** out_layout) {
+  if (!device || !out_layout) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  *out_layout = nullptr;
+  if (binding_count > IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "binding count %u over the limit of %d", binding_count,
+                IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT);
+  auto* l = new iree_hal_b200_descriptor_set_layout_t();
+  l->binding_count = binding_count;
+  *out_layout = l;
+  return IREE_B200_STATUS_OK;
+}
+void iree_hal_b200_descriptor_set_layout_release(iree_hal_b200_descriptor_set_layout_t* layout) { delete layout; }
+
+iree_b200_status_t iree_hal_b200_pipeline_layout_create(iree_hal_b200_device_t* device, uint32_t push_constant_count,
+                                                        uint32_t set_layout_count,
+                                                        iree_hal_b200_descriptor_set_layout_t* const* set_layouts,
+                                                        iree_hal_b200_pipeline_layout_t** out_layout) {
+  if (!device || !out_layout || (set_layout_count && !set_layouts)) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  *out_layout = nullptr;
+  if (push_constant_count > IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "push constant count %u over the limit of %d", push_constant_count,
+                IREE_HAL_B200_MAX_PUSH_CONSTANT_COUNT);
+  if (set_layout_count > IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT)
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "descriptor set count %u over the limit of %d", set_layout_count,
+                IREE_HAL_B200_MAX_DESCRIPTOR_SET_COUNT);
+  auto* l = new iree_hal_b200_pipeline_layout_t();
+  l->push_constant_count = push_constant_count;
+  for (uint32_t i = 0; i < set_layout_count; ++i) {
+    if (!set_layouts[i]) {
+      delete l;
+      return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "descriptor set layout %u is NULL", i);
+    }
+    l->set_binding_counts.push_back(set_layouts[i]->binding_count);  // copied: the set layout may be released
+  }
+  *out_layout = l;
+  return IREE_B200_STATUS_OK;
+}
+void iree_hal_b200_pipeline_layout_release(iree_hal_b200_pipeline_layout_t* layout) { delete layout; }
+
+iree_b200_status_t iree_hal_b200_command_buffer_dispatch_with_layout(iree_hal_b200_command_buffer_t* command_buffer,
+                                                                     iree_hal_b200_executable_t* executable,
+                                                                     int32_t entry_point,
+                                                                     const iree_hal_b200_pipeline_layout_t* layout,
+                                                                     uint32_t workgroup_x, uint32_t workgroup_y,
+                                                                     uint32_t workgroup_z) {
+  if (!command_buffer || !layout) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  // Kernel parameters: the bindings of set 0, then of set 1, ... (each set's first parameter index is the
+  // running sum of the binding counts before it), then the push constants. The sets are flattened into
+  // the slots of set 0 for the launch and put back afterwards.
+  void* saved[IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT];
+  memcpy(saved, command_buffer->bindings[0], sizeof saved);
+  uint32_t total = 0;
+  void* flat[IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT];
+  for (size_t set = 0; set < layout->set_binding_counts.size(); ++set) {
+    for (uint32_t b = 0; b < layout->set_binding_counts[set]; ++b) {
+      if (total >= IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT)
+        return fail(IREE_B200_STATUS_OUT_OF_RANGE, "the layout's sets hold more than %d bindings",
+                    IREE_HAL_B200_MAX_DESCRIPTOR_SET_BINDING_COUNT);
+      flat[total++] = command_buffer->bindings[set][b];
+    }
+  }
+  memcpy(command_buffer->bindings[0], flat, total * sizeof(void*));
+  const iree_b200_status_t st = iree_hal_b200_command_buffer_dispatch(command_buffer, executable, entry_point, total,
+                                                                      layout->push_constant_count, workgroup_x, workgroup_y,
+                                                                      workgroup_z);
+  memcpy(command_buffer->bindings[0], saved, sizeof saved);
+  return st;
 }
 
 iree_b200_status_t iree_hal_b200_command_buffer_set_dispatch_overlap(iree_hal_b200_command_buffer_t* command_buffer,
@@ -994,6 +1213,37 @@ iree_b200_status_t iree_hal_b200_channel_create(iree_hal_b200_device_t* device, 
     delete ch;
     return st;
   }
+  *out_channel = ch;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_channel_split(iree_hal_b200_channel_t* base_channel, int32_t color, int32_t key,
+                                               iree_hal_b200_channel_t** out_channel) {
+  if (!out_channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "out_channel is NULL");
+  *out_channel = nullptr;
+  if (!base_channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "base_channel is NULL");
+  B200_RETURN_IF_ERROR(ensure_nccl());
+  if (!g_nccl.ncclCommSplit || !g_nccl.ncclCommCount || !g_nccl.ncclCommUserRank)
+    return fail(IREE_B200_STATUS_UNAVAILABLE, "this NCCL has no ncclCommSplit");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(base_channel->device->context), "cuCtxSetCurrent");
+  ncclComm_t comm = nullptr;
+  // a negative color is NCCL_SPLIT_NOCOLOR: the rank takes part in the call and gets no channel
+  B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclCommSplit(base_channel->comm, color < 0 ? -1 : color, key, &comm, nullptr),
+                                  "ncclCommSplit"));
+  if (color < 0 || !comm) return IREE_B200_STATUS_OK;
+  auto* ch = new iree_hal_b200_channel_t();
+  ch->device = base_channel->device;
+  ch->comm = comm;
+  int count = 0, rank = 0;
+  iree_b200_status_t st = nccl_check(g_nccl.ncclCommCount(comm, &count), "ncclCommCount");
+  if (!st) st = nccl_check(g_nccl.ncclCommUserRank(comm, &rank), "ncclCommUserRank");
+  if (st) {
+    g_nccl.ncclCommDestroy(comm);
+    delete ch;
+    return st;
+  }
+  ch->count = count;
+  ch->rank = rank;
   *out_channel = ch;
   return IREE_B200_STATUS_OK;
 }

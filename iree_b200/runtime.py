@@ -386,6 +386,64 @@ class Context:
             i64(out_offset), i64(out_stride0), i64(out_stride1), i64(in_size0), i64(in_size1), i64(in_size2),
             i64(in_size3), i64(out_size0), i64(out_size1), C.c_uint32(flags)))
 
+    # -- transfer commands, barriers, layouts (the reference's command-buffer API beyond dispatch) ----
+    def begin(self) -> None:
+        check(library().iree_hal_b200_command_buffer_begin(self.command_buffer))
+
+    def end(self) -> None:
+        check(library().iree_hal_b200_command_buffer_end(self.command_buffer))
+
+    def execution_barrier(self) -> None:
+        check(library().iree_hal_b200_command_buffer_execution_barrier(self.command_buffer, C.c_uint32(0), C.c_uint32(0),
+                                                                        C.c_uint32(0)))
+
+    def fill_buffer(self, target, offset: int, length: int, pattern: bytes) -> None:
+        check(library().iree_hal_b200_command_buffer_fill_buffer(self.command_buffer, _vp(target), C.c_size_t(offset),
+                                                                  C.c_size_t(length), pattern, C.c_size_t(len(pattern))))
+
+    def copy_buffer(self, source, source_offset: int, target, target_offset: int, length: int) -> None:
+        check(library().iree_hal_b200_command_buffer_copy_buffer(self.command_buffer, _vp(source), C.c_size_t(source_offset),
+                                                                  _vp(target), C.c_size_t(target_offset), C.c_size_t(length)))
+
+    def pipeline_layout(self, push_constant_count: int, set_binding_counts) -> C.c_void_p:
+        """A pipeline layout of len(set_binding_counts) descriptor sets; free with release_pipeline_layout."""
+        lib = library()
+        sets = (C.c_void_p * max(len(set_binding_counts), 1))()
+        for i, n in enumerate(set_binding_counts):
+            h = C.c_void_p()
+            check(lib.iree_hal_b200_descriptor_set_layout_create(self.device, C.c_uint32(n), C.byref(h)))
+            sets[i] = h
+        out = C.c_void_p()
+        try:
+            check(lib.iree_hal_b200_pipeline_layout_create(self.device, C.c_uint32(push_constant_count),
+                                                           C.c_uint32(len(set_binding_counts)), sets, C.byref(out)))
+        finally:
+            for i in range(len(set_binding_counts)):
+                lib.iree_hal_b200_descriptor_set_layout_release(C.c_void_p(sets[i]))
+        return out
+
+    def release_pipeline_layout(self, layout) -> None:
+        library().iree_hal_b200_pipeline_layout_release(layout)
+
+    def push_descriptor_set(self, set_index: int, pointers) -> None:
+        arr = (_Binding * len(pointers))()
+        for i, b in enumerate(pointers):
+            arr[i].binding, arr[i].device_ptr = i, _vp(b).value
+        check(library().iree_hal_b200_command_buffer_push_descriptor_set(self.command_buffer, C.c_uint32(set_index),
+                                                                         C.c_size_t(len(pointers)), arr))
+
+    def dispatch_with_layout(self, entry_name: str, layout, constants, grid) -> None:
+        lib = library()
+        ordinal = self.lookup(entry_name)
+        if ordinal < 0:
+            raise IreeB200Error(5, "no export named " + entry_name)
+        consts = np.asarray(constants, dtype=np.int32)
+        check(lib.iree_hal_b200_command_buffer_push_constants(self.command_buffer, C.c_size_t(0), _vp(consts),
+                                                              C.c_size_t(consts.nbytes)))
+        gx, gy, gz = grid
+        check(lib.iree_hal_b200_command_buffer_dispatch_with_layout(self.command_buffer, self.executable, C.c_int32(ordinal),
+                                                                    layout, C.c_uint32(gx), C.c_uint32(gy), C.c_uint32(gz)))
+
     def uk_status(self) -> None:
         """Raises if a pack / unpack kernel reported a rejected argument or a wait that ran out."""
         check(library().iree_b200_uk_status(self.handle))

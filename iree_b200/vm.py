@@ -347,7 +347,16 @@ class HalModule:
         return cb
 
     def hal_command_buffer__fill_buffer(self, cb, buffer, offset, length, pattern, pattern_length):
-        raise VmError("UNIMPLEMENTED", "fill_buffer inside a recorded command buffer; zero transients with allocator-side fills")
+        # a memset node of the recording; the pattern arrives as an i32 of which pattern_length bytes count
+        raw = int(pattern & 0xFFFFFFFF).to_bytes(4, "little")[:pattern_length]
+        self.rt.check(self.lib.iree_hal_b200_command_buffer_fill_buffer(
+            self.ctx.command_buffer, self.rt._vp(buffer), C.c_size_t(offset), C.c_size_t(length), raw,
+            C.c_size_t(pattern_length)))
+
+    def hal_command_buffer__copy_buffer(self, cb, source, source_offset, target, target_offset, length):
+        self.rt.check(self.lib.iree_hal_b200_command_buffer_copy_buffer(
+            self.ctx.command_buffer, self.rt._vp(source), C.c_size_t(source_offset), self.rt._vp(target),
+            C.c_size_t(target_offset), C.c_size_t(length)))
 
     def hal_command_buffer__push_constants(self, cb, pipeline_layout, offset, values):
         for i, (v,) in enumerate(values):
@@ -375,7 +384,11 @@ class HalModule:
         cb.constants, cb.bindings = {}, {}
 
     def hal_command_buffer__execution_barrier(self, cb, source_stage_mask, target_stage_mask, flags):
-        pass      # kernel nodes of the recording already depend on each other in order
+        # nodes of the recording already depend on each other in order; the barrier keeps the next dispatch
+        # from being launched early
+        self.rt.check(self.lib.iree_hal_b200_command_buffer_execution_barrier(
+            self.ctx.command_buffer, C.c_uint32(source_stage_mask & 0xFFFFFFFF), C.c_uint32(target_stage_mask & 0xFFFFFFFF),
+            C.c_uint32(flags & 0xFFFFFFFF)))
 
     def hal_command_buffer__finalize(self, cb):
         g = C.c_void_p()

@@ -48,6 +48,28 @@ def main() -> int:
             ok = ok and np.array_equal(got[p], want)
         dist.barrier()  # nobody overwrites `send` or a receive buffer while a peer still checks
     peer.close()
+    # iree_hal_channel_split: one colour, keys in reverse rank order -> the same ranks in reverse; an
+    # all-gather through the new channel is ordered by the new ranks. Then a split in which the last rank
+    # passes no colour: it gets no channel, the others a channel without it.
+    sub = C.c_void_p()
+    rt.check(lib.iree_hal_b200_channel_split(channel, C.c_int32(0), C.c_int32(world - 1 - rank), C.byref(sub)))
+    ok = ok and bool(sub.value) and lib.iree_hal_b200_channel_count(sub) == world
+    ok = ok and lib.iree_hal_b200_channel_rank(sub) == world - 1 - rank
+    word = ctx.to_device(np.array([100 + rank], np.int32))
+    words = ctx.alloc(world * 4).fill(0)
+    rt.check(lib.iree_hal_b200_command_buffer_all_gather(ctx.command_buffer, sub, C.c_int32(2), C.c_void_p(word.ptr),
+                                                         C.c_void_p(words.ptr), C.c_size_t(1)))
+    ctx.synchronize()
+    ok = ok and np.array_equal(words.download(np.int32, (world,)), 100 + np.arange(world - 1, -1, -1, dtype=np.int32))
+    lib.iree_hal_b200_channel_release(sub)
+    sub2 = C.c_void_p()
+    rt.check(lib.iree_hal_b200_channel_split(channel, C.c_int32(-1 if rank == world - 1 else 7), C.c_int32(rank), C.byref(sub2)))
+    if rank == world - 1:
+        ok = ok and not sub2.value
+    else:
+        ok = ok and bool(sub2.value) and lib.iree_hal_b200_channel_count(sub2) == world - 1
+        ok = ok and lib.iree_hal_b200_channel_rank(sub2) == rank
+        lib.iree_hal_b200_channel_release(sub2)
     lib.iree_hal_b200_channel_release(channel)
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -527,11 +527,16 @@ iree_b200_status_t iree_b200_context_set_reserved_sms(iree_b200_context_t* conte
  * are device pointers, sizes / strides / offsets are in elements, flags carry the reference's
  * bit values (exported_bits.h:29-83). Work is enqueued on the context's stream. */
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_MASK 0xFF
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_F32F32F32 0x01
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_S8S8S32 0x02
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_F16F16F32 0x03
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_F16F16F16 0x04
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16F32 0x05
 #define IREE_B200_UK_FLAG_MMT4D_TYPE_BF16BF16BF16 0x06
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_S16S16S32 0x07
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_S16U4S32 0x08
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_S16S8S32 0x09
+#define IREE_B200_UK_FLAG_MMT4D_TYPE_S8S4S32 0x0A
 #define IREE_B200_UK_FLAG_MMT4D_ACCUMULATE 0x100
 /* No counterpart in the reference: take the path that brings both operands back to row-major first
  * (un-tile, row-major contraction, re-tile) even where the kernel that reads tiled operands applies. */
@@ -586,7 +591,10 @@ iree_b200_status_t iree_b200_uk_status(iree_b200_context_t* context);
  * added, with ACCUMULATE) by the pack kernel. `workspace` is a zero-filled device buffer of
  * iree_b200_uk_mmt4d_workspace_bytes() bytes, 256-byte aligned.
  * Types: S8S8S32 (bit-exact), F16F16F32, BF16BF16F32, F16F16F16, BF16BF16BF16 (f32 accumulation
- * in tensor-core order; ACCUMULATE only with 32-bit outputs); other types: UNIMPLEMENTED. The
+ * in tensor-core order; ACCUMULATE only with 32-bit outputs) on the tensor cores; F32F32F32, S16S16S32,
+ * S16U4S32, S16S8S32, S8S4S32 through a one-thread-per-element kernel in the order of the reference's
+ * generic tile functions (integer types bit-exact; offsets and strides in elements of each operand's
+ * type, a 4-bit element being half a byte; K0 even for the 4-bit right-hand sides; no workspace needed). The
  * 16-bit-output types always accumulate in f32 and round once at the end, i.e. they behave as the
  * reference does with IREE_UK_FLAG_MMT4D_SKIP_INTERMEDIATE_ROUNDINGS (0x400) set, whether or not
  * the caller passes that flag (without it the reference's generic tile rounds to the narrow type

@@ -21,7 +21,7 @@ LIB = os.path.join(HERE, "libiree_b200.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 KERNEL_SOURCES = ["contraction_sm100.cu", "contraction_pair_sm100.cu", "w4a16_sm100.cu", "w4a16_wt_sm100.cu", "w4a16_decode_tc_sm100.cu",
-                  "mmt4d_sm100.cu", "data_tiling_sm100.cu", "tiling_tma_sm100.cu", "pack_vnni_sm100.cu"]
+                  "mmt4d_sm100.cu", "mmt4d_generic_sm100.cu", "data_tiling_sm100.cu", "tiling_tma_sm100.cu", "pack_vnni_sm100.cu"]
 HOST_SOURCES = ["hal_b200.cc", "parameters.cc", "w4a16_noalloc.cu"]
 HEADERS = ["sm100_ptx.cuh", "w4a16_decode.cuh", "w4a16_decode_tc.h", "hal_b200_internal.h", os.path.join("..", "..", "include", "iree_b200.h")]
 

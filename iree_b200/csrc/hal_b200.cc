@@ -1504,6 +1504,7 @@ const EntryDecl kEntries[] = {
     {"b200_mmt4d_f16f16f16", {512, 1, 1}, kMmt4dSmemBytes},
     {"b200_mmt4d_bf16bf16f32", {512, 1, 1}, kMmt4dSmemBytes},
     {"b200_mmt4d_bf16bf16bf16", {512, 1, 1}, kMmt4dSmemBytes},
+    {"b200_mmt4d_generic", {256, 1, 1}, 0},
     {"b200_tiling_tma", {32, 1, 1}, 1024 + 8 * 16384 + 128},
     {"b200_pack_i8_rhs_16x2", {288, 1, 1}, 1024 + 4 * 16384 + 2 * 8 * (64 * 32 + 32) + 128},
     {"b200_pack_lhs_16x2b", {288, 1, 1}, 1024 + 4 * 16384 + 2 * 8 * (64 * 32 + 32) + 128},
@@ -2892,6 +2893,55 @@ iree_b200_status_t iree_b200_uk_unpack(iree_b200_context_t* context, const void*
                          flags & (kUkTransposeInner | kUkTransposeOuter | kTilingNoTma), 0);
 }
 
+// The element types without a tensor-core kernel (f32f32f32, s16s16s32, s16u4s32, s16s8s32, s8s4s32):
+// one thread per output element, the reference's generic reduction order (mmt4d_generic_sm100.cu).
+// Offsets and strides are in elements of each operand's type; a 4-bit element is half a byte
+// (mmt4d.c:67-86).
+static iree_b200_status_t mmt4d_other_types(iree_b200_context_t* context, const void* lhs_buffer, int64_t lhs_offset,
+                                            int64_t lhs_stride0, const void* rhs_buffer, int64_t rhs_offset,
+                                            int64_t rhs_stride0, void* out_buffer, int64_t out_offset, int64_t out_stride0,
+                                            int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
+                                            uint32_t flags) {
+  const uint32_t type = flags & IREE_B200_UK_FLAG_MMT4D_TYPE_MASK;
+  int lhs_bits, rhs_bits;
+  switch (type) {
+    case 0x01: lhs_bits = 32, rhs_bits = 32; break;  // F32F32F32
+    case 0x07: lhs_bits = 16, rhs_bits = 16; break;  // S16S16S32
+    case 0x08: lhs_bits = 16, rhs_bits = 4; break;   // S16U4S32
+    case 0x09: lhs_bits = 16, rhs_bits = 8; break;   // S16S8S32
+    case 0x0A: lhs_bits = 8, rhs_bits = 4; break;    // S8S4S32
+    default: return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown mmt4d type 0x%x", type);
+  }
+  if (flags & ~(IREE_B200_UK_FLAG_MMT4D_TYPE_MASK | IREE_B200_UK_FLAG_MMT4D_ACCUMULATE | 0x200u | 0x400u |
+                IREE_B200_UK_FLAG_MMT4D_UNTILE))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown mmt4d flags 0x%x", flags);
+  const bool accumulate = flags & IREE_B200_UK_FLAG_MMT4D_ACCUMULATE;
+  if (M < 0 || N < 0 || K < 0 || M0 < 0 || N0 < 0 || K0 < 0) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "negative dimension");
+  if (M == 0 || N == 0 || M0 == 0 || N0 == 0) return IREE_B200_STATUS_OK;  // nothing to write
+  if (K == 0 && accumulate) return IREE_B200_STATUS_OK;
+  if (rhs_bits == 4 && ((K0 & 1) || (rhs_offset & 1) || (rhs_stride0 & 1)))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "4-bit right-hand sides need an even K0, offset and stride");
+  if (!lhs_buffer || !rhs_buffer || !out_buffer) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
+  const int64_t lhs_pitch = lhs_stride0 * lhs_bits / 8, rhs_pitch = rhs_stride0 * rhs_bits / 8;
+  if (!fits_i32(M) || !fits_i32(N) || !fits_i32(K) || !fits_i32(lhs_pitch) || !fits_i32(rhs_pitch) || !fits_i32(out_stride0))
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "dimension or pitch above 2^31");
+  const uint8_t* lhs = static_cast<const uint8_t*>(lhs_buffer) + lhs_offset * lhs_bits / 8;
+  const uint8_t* rhs = static_cast<const uint8_t*>(rhs_buffer) + rhs_offset * rhs_bits / 8;
+  uint8_t* out = static_cast<uint8_t*>(out_buffer) + out_offset * 4;
+  const int32_t ord = iree_hal_b200_executable_lookup(context->executable, "b200_mmt4d_generic");
+  if (ord < 0) return fail(IREE_B200_STATUS_NOT_FOUND, "export b200_mmt4d_generic missing from the executable");
+  const int64_t total = M * N * M0 * N0;
+  const int64_t cap = static_cast<int64_t>(usable_sms(context)) * 16;
+  const int64_t blocks = (total + 255) / 256;
+  iree_hal_b200_descriptor_set_binding_t bindings[3] = {{0, const_cast<uint8_t*>(lhs)}, {1, const_cast<uint8_t*>(rhs)}, {2, out}};
+  const int32_t c[11] = {(int32_t)M, (int32_t)N, (int32_t)K, M0, N0, K0, (int32_t)lhs_pitch, (int32_t)rhs_pitch,
+                         (int32_t)out_stride0, (int32_t)type, accumulate ? 1 : 0};
+  auto* cb = context->command_buffer;
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_descriptor_set(cb, 0, 3, bindings));
+  B200_RETURN_IF_ERROR(iree_hal_b200_command_buffer_push_constants(cb, 0, c, sizeof c));
+  return iree_hal_b200_command_buffer_dispatch(cb, context->executable, ord, 3, 11, static_cast<uint32_t>(blocks < cap ? blocks : cap), 1, 1);
+}
+
 size_t iree_b200_uk_mmt4d_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t M0, int32_t N0, int32_t K0,
                                           uint32_t flags) {
   Mmt4dTypes t;
@@ -2954,7 +3004,8 @@ iree_b200_status_t iree_b200_uk_mmt4d(iree_b200_context_t* context, const void* 
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
   Mmt4dTypes t;
   if (!mmt4d_types(flags, &t))
-    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "mmt4d type 0x%x has no tensor-core kernel", flags & 0xFF);
+    return mmt4d_other_types(context, lhs_buffer, lhs_offset, lhs_stride0, rhs_buffer, rhs_offset, rhs_stride0, out_buffer,
+                             out_offset, out_stride0, M, N, K, M0, N0, K0, flags);
   if (flags & ~(IREE_B200_UK_FLAG_MMT4D_TYPE_MASK | IREE_B200_UK_FLAG_MMT4D_ACCUMULATE | 0x200u | 0x400u |
                 IREE_B200_UK_FLAG_MMT4D_UNTILE))
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown mmt4d flags 0x%x", flags);

@@ -507,6 +507,7 @@ UK_TRANSPOSE_INNER, UK_TRANSPOSE_OUTER = 0x100, 0x200
 UK_PACK_NO_TMA = 0x40000     # this library's own: the staging kernels even where the TMA unit alone could copy
 UK_MMT4D_S8S8S32, UK_MMT4D_F16F16F32, UK_MMT4D_F16F16F16 = 0x02, 0x03, 0x04
 UK_MMT4D_BF16BF16F32, UK_MMT4D_BF16BF16BF16, UK_MMT4D_ACCUMULATE = 0x05, 0x06, 0x100
+UK_MMT4D_F32F32F32, UK_MMT4D_S16S16S32, UK_MMT4D_S16U4S32, UK_MMT4D_S16S8S32, UK_MMT4D_S8S4S32 = 0x01, 0x07, 0x08, 0x09, 0x0A
 UK_MMT4D_UNTILE = 0x10000   # this library's own: take the un-tiling path even where the tiled-operand kernel applies
 
 
@@ -568,9 +569,12 @@ def mmt4d_numpy(ctx: Context, type_flag: int, lhs4: np.ndarray, rhs4: np.ndarray
     lhs4, rhs4 = np.ascontiguousarray(lhs4), np.ascontiguousarray(rhs4)
     M, K, M0, K0 = lhs4.shape
     N, K2, N0, K02 = rhs4.shape
-    assert (K, K0) == (K2, K02)
+    four_bit = type_flag in (UK_MMT4D_S16U4S32, UK_MMT4D_S8S4S32)   # right-hand side: two elements per byte
+    assert (K, K0) == (K2, K02 * 2 if four_bit else K02)
     odt = {UK_MMT4D_S8S8S32: np.int32, UK_MMT4D_F16F16F32: np.float32, UK_MMT4D_BF16BF16F32: np.float32,
-           UK_MMT4D_F16F16F16: np.float16, UK_MMT4D_BF16BF16BF16: np.uint16}[type_flag]
+           UK_MMT4D_F16F16F16: np.float16, UK_MMT4D_BF16BF16BF16: np.uint16, UK_MMT4D_F32F32F32: np.float32,
+           UK_MMT4D_S16S16S32: np.int32, UK_MMT4D_S16U4S32: np.int32, UK_MMT4D_S16S8S32: np.int32,
+           UK_MMT4D_S8S4S32: np.int32}[type_flag]
     flags = type_flag | (UK_MMT4D_ACCUMULATE if acc4 is not None else 0)
     out_shape = (M, N, M0, N0)
     count = int(np.prod(out_shape))

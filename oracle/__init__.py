@@ -27,6 +27,7 @@ TYPE_F32F32F32 = 1  # IREE_UK_FLAG_MMT4D_TYPE_* (builtins/ukernel/exported_bits.
 TYPE_S8S8S32 = 2
 TYPE_F16F16F32 = 3
 TYPE_BF16BF16F32 = 5
+TYPE_S16S16S32, TYPE_S16U4S32, TYPE_S16S8S32, TYPE_S8S4S32 = 7, 8, 9, 10   # the reference's ukernel only (mmt4d_ref)
 
 PACK_F32, PACK_I8, PACK_I32, PACK_F16, PACK_BF16 = 1, 2, 3, 4, 5  # exported_bits.h:56-62
 TRANSPOSE_INNER, TRANSPOSE_OUTER = 0x100, 0x200
@@ -35,7 +36,8 @@ MMT4D_ACCUMULATE, MMT4D_ALLOW_GENERIC, MMT4D_SKIP_ROUNDINGS = 0x100, 0x200, 0x40
 _IN_DTYPE = {TYPE_F32F32F32: np.float32, TYPE_S8S8S32: np.int8, TYPE_F16F16F32: np.float16,
              TYPE_BF16BF16F32: np.uint16}
 _ACC_DTYPE = {TYPE_F32F32F32: np.float32, TYPE_S8S8S32: np.int32, TYPE_F16F16F32: np.float32,
-              TYPE_BF16BF16F32: np.float32}
+              TYPE_BF16BF16F32: np.float32, TYPE_S16S16S32: np.int32, TYPE_S16U4S32: np.int32,
+              TYPE_S16S8S32: np.int32, TYPE_S8S4S32: np.int32}
 
 
 def build(verbose: bool = False) -> None:
@@ -357,3 +359,23 @@ def ref_has_arch_tile(t, m0, n0, k0, cpu_mode=1) -> bool:
     flags = t | MMT4D_SKIP_ROUNDINGS
     return bool(ref_lib().uk_chain_mmt4d_info(C.c_int(m0), C.c_int(n0), C.c_int(k0), C.c_uint32(flags),
                                               C.c_int(cpu_mode)) & 1)
+
+
+def mmt4d_int_types_port(t, lhs4, rhs4, acc4=None):
+    """numpy restatement of the reference's generic tile functions for the s16 / 4-bit mmt4d types
+    (builtins/ukernel/mmt4d_tile_generic.c:11-180): int32 accumulation with wrap-around; a 4-bit
+    right-hand side holds two reduction elements per byte, low nibble first, unsigned for u4
+    (S16U4S32) and sign-extended for s4 (S8S4S32). Pinned against the reference's own ukernel in
+    tests/test_oracle.py."""
+    lhs4, rhs4 = np.asarray(lhs4), np.asarray(rhs4)
+    if t in (TYPE_S16U4S32, TYPE_S8S4S32):
+        lo, hi = (rhs4 & 0xF).astype(np.int64), (rhs4 >> 4).astype(np.int64)
+        if t == TYPE_S8S4S32:
+            lo, hi = np.where(lo >= 8, lo - 16, lo), np.where(hi >= 8, hi - 16, hi)
+        r = np.stack([lo, hi], axis=-1).reshape(rhs4.shape[:-1] + (rhs4.shape[-1] * 2,))
+    else:
+        r = rhs4.astype(np.int64)
+    total = np.einsum("mkac,nkbc->mnab", lhs4.astype(np.int64), r)
+    if acc4 is not None:
+        total = total + np.asarray(acc4).astype(np.int64)
+    return (total & 0xFFFFFFFF).astype(np.uint32).view(np.int32)

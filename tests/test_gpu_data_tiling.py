@@ -129,8 +129,11 @@ def test_argument_errors(ctx):
         ctx.uk_pack(buf, 0, 8, 1, buf, 0, 8, 8, 8, 8, 1, 1, 4, 2, 0, 0x02)    # tiles do not cover the matrix
     assert e.value.code_name == "INVALID_ARGUMENT"
     with pytest.raises(ib.IreeB200Error) as e:
-        ctx.uk_mmt4d(buf, 0, 8, buf, 0, 8, buf, 0, 8, 1, 1, 1, 2, 2, 2, 0x01, buf)  # f32f32f32
-    assert e.value.code_name == "UNIMPLEMENTED"
+        ctx.uk_mmt4d(buf, 0, 8, buf, 0, 8, buf, 0, 8, 1, 1, 1, 2, 2, 2, 0x0B, buf)  # no such type
+    assert e.value.code_name == "INVALID_ARGUMENT"
+    with pytest.raises(ib.IreeB200Error) as e:
+        ctx.uk_mmt4d(buf, 0, 8, buf, 0, 8, buf, 0, 8, 1, 1, 1, 2, 2, 3, 0x0A, buf)  # s8s4s32 with an odd K0
+    assert e.value.code_name == "INVALID_ARGUMENT"
     buf.free()
 
 
@@ -377,3 +380,62 @@ def test_right_hand_side_pack_of_f16_tiles_is_a_tma_copy(ctx):
         staged = pack_numpy(ctx, x, (1, 16), True, True, extra_flags=rt.UK_PACK_NO_TMA)
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), (K, N)
         assert np.array_equal(staged.view(np.uint16), want.view(np.uint16)), (K, N)
+
+
+def _unpack_nibbles(rhs_bytes, signed):
+    """[N, K, N0, K0 / 2] bytes -> [N, K, N0, K0] integers: low nibble first (mmt4d_tile_generic.c:11-50, 108-143)."""
+    lo = (rhs_bytes & 0xF).astype(np.int32)
+    hi = (rhs_bytes >> 4).astype(np.int32)
+    if signed:
+        lo = np.where(lo >= 8, lo - 16, lo)
+        hi = np.where(hi >= 8, hi - 16, hi)
+    return np.stack([lo, hi], axis=-1).reshape(rhs_bytes.shape[:-1] + (rhs_bytes.shape[-1] * 2,))
+
+
+@pytest.mark.parametrize("type_flag,ldt,rdt,tile", [
+    (rt.UK_MMT4D_F32F32F32, np.float32, np.float32, (16, 16, 1)), (rt.UK_MMT4D_F32F32F32, np.float32, np.float32, (3, 5, 7)),
+    (rt.UK_MMT4D_S16S16S32, np.int16, np.int16, (16, 16, 2)), (rt.UK_MMT4D_S16S8S32, np.int16, np.int8, (4, 8, 3)),
+    (rt.UK_MMT4D_S16U4S32, np.int16, np.uint8, (1, 32, 8)), (rt.UK_MMT4D_S8S4S32, np.int8, np.uint8, (4, 16, 2)),
+    (rt.UK_MMT4D_S8S4S32, np.int8, np.uint8, (3, 5, 6))])
+def test_mmt4d_types_without_a_tensor_core_kernel(ctx, type_flag, ldt, rdt, tile):
+    """f32f32f32 and the s16 / 4-bit types (exported_bits.h:29-42) through the one-thread-per-element kernel:
+    integer types exact against a numpy restatement of the reference's generic tile functions (4-bit
+    right-hand sides: two elements per byte, low nibble first, unsigned for u4 and sign-extended for s4),
+    f32 within tolerance; with and without ACCUMULATE."""
+    m0, n0, k0 = tile
+    rng = np.random.default_rng(type_flag * 7 + m0)
+    four_bit = type_flag in (rt.UK_MMT4D_S16U4S32, rt.UK_MMT4D_S8S4S32)
+    for (M, N, K) in [(1, 1, 1), (2, 3, 5), (7, 9, 33)]:
+        if ldt == np.float32:
+            lhs = rng.standard_normal((M, K, m0, k0)).astype(np.float32)
+            rhs = rng.standard_normal((N, K, n0, k0)).astype(np.float32)
+            acc = rng.standard_normal((M, N, m0, n0)).astype(np.float32)
+            l64, r64 = lhs.astype(np.float64), rhs.astype(np.float64)
+        else:
+            info = np.iinfo(ldt)
+            lhs = rng.integers(info.min, info.max + 1, (M, K, m0, k0)).astype(ldt)
+            if four_bit:
+                rhs = rng.integers(0, 256, (N, K, n0, k0 // 2)).astype(np.uint8)
+                r64 = _unpack_nibbles(rhs, signed=(type_flag == rt.UK_MMT4D_S8S4S32)).astype(np.int64)
+            else:
+                rinfo = np.iinfo(rdt)
+                rhs = rng.integers(rinfo.min, rinfo.max + 1, (N, K, n0, k0)).astype(rdt)
+                r64 = rhs.astype(np.int64)
+            acc = rng.integers(-10 ** 6, 10 ** 6, (M, N, m0, n0)).astype(np.int32)
+            l64 = lhs.astype(np.int64)
+        prod = np.einsum("mkac,nkbc->mnab", l64, r64)
+        for with_acc in (False, True):
+            got = rt.mmt4d_numpy(ctx, type_flag, lhs, rhs, acc if with_acc else None)
+            want = prod + (acc if with_acc else 0)
+            if ldt == np.float32:
+                assert np.allclose(got, want, rtol=1e-4, atol=1e-4), (M, N, K, with_acc)
+            else:
+                # 32-bit wrap-around like the reference's int32 accumulator
+                assert np.array_equal(got, (want & 0xFFFFFFFF).astype(np.uint32).view(np.int32)), (M, N, K, with_acc)
+                assert np.array_equal(got, oracle.mmt4d_int_types_port(type_flag, lhs, rhs, acc if with_acc else None))
+            if oracle.have_ref():  # the reference's own ukernel (its generic tile functions) on the same operands
+                ref = oracle.mmt4d_ref(type_flag, lhs, rhs, acc if with_acc else None)
+                if ldt == np.float32:
+                    assert np.allclose(got, ref, rtol=1e-4, atol=1e-4), (M, N, K, with_acc, "reference")
+                else:
+                    assert np.array_equal(got, ref), (M, N, K, with_acc, "reference")

@@ -252,3 +252,29 @@ def test_conversion_difference_zone_is_outside_the_benchmark_data(built):
     assert ((mag == 0) | (mag >= 2.0 ** -14)).all()
     out = oracle.w4a16(a, wq, s).astype(np.float32)
     assert np.abs(out).max() < 65520.0 and ((np.abs(out) == 0) | (np.abs(out) >= 2.0 ** -14)).mean() > 0.999
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="the reference's ukernels were not built")
+@pytest.mark.parametrize("t,ldt,rdt,tile", [(oracle.TYPE_S16S16S32, np.int16, np.int16, (16, 16, 2)),
+                                            (oracle.TYPE_S16S8S32, np.int16, np.int8, (4, 8, 3)),
+                                            (oracle.TYPE_S16U4S32, np.int16, np.uint8, (1, 32, 8)),
+                                            (oracle.TYPE_S8S4S32, np.int8, np.uint8, (4, 16, 2)),
+                                            (oracle.TYPE_S8S4S32, np.int8, np.uint8, (3, 5, 6))])
+def test_integer_mmt4d_types_restatement_equals_the_reference_ukernel(t, ldt, rdt, tile):
+    """The s16 / 4-bit element types: the numpy restatement against iree_uk_mmt4d itself (generic tile
+    functions and, where the host has them, the architecture-specific ones), with and without ACCUMULATE."""
+    m0, n0, k0 = tile
+    rng = np.random.default_rng(t)
+    four_bit = t in (oracle.TYPE_S16U4S32, oracle.TYPE_S8S4S32)
+    for (M, N, K) in [(1, 1, 1), (2, 3, 5), (5, 4, 17)]:
+        li = np.iinfo(ldt)
+        lhs = rng.integers(li.min, li.max + 1, (M, K, m0, k0)).astype(ldt)
+        if four_bit:
+            rhs = rng.integers(0, 256, (N, K, n0, k0 // 2)).astype(np.uint8)
+        else:
+            ri = np.iinfo(rdt)
+            rhs = rng.integers(ri.min, ri.max + 1, (N, K, n0, k0)).astype(rdt)
+        acc = rng.integers(-10 ** 6, 10 ** 6, (M, N, m0, n0)).astype(np.int32)
+        for a in (None, acc):
+            for mode in (0, 1):   # generic tile functions only / what the host CPU offers
+                assert np.array_equal(oracle.mmt4d_int_types_port(t, lhs, rhs, a), oracle.mmt4d_ref(t, lhs, rhs, a, cpu_mode=mode))

@@ -280,6 +280,38 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command
                                                            const void* send_device_ptr, void* recv_device_ptr,
                                                            size_t element_count);
 
+/* iree_hal_command_buffer_collective for the other kinds (hal/command_buffer.h:215-335; submitted as
+ * the reference's NCCL channel does, drivers/cuda/nccl_channel.c:327-500). `kind` and `reduction` take the
+ * reference's enum values. `param`: the root rank (BROADCAST, REDUCE), the peer (SEND, RECV), or for
+ * SEND_RECV the rank to send to in the low and the rank to receive from in the high 16 bits. element_count:
+ * per rank for ALL_GATHER and REDUCE_SCATTER (what a rank contributes / receives), the whole buffer for
+ * ALL_REDUCE, ALL_TO_ALL (count / ranks elements per peer), BROADCAST, REDUCE, SEND, RECV. Not recordable
+ * into a graph. */
+enum {
+  IREE_HAL_B200_COLLECTIVE_ALL_GATHER = 0,
+  IREE_HAL_B200_COLLECTIVE_ALL_REDUCE = 1,
+  IREE_HAL_B200_COLLECTIVE_ALL_TO_ALL = 2,
+  IREE_HAL_B200_COLLECTIVE_BROADCAST = 3,
+  IREE_HAL_B200_COLLECTIVE_REDUCE = 4,
+  IREE_HAL_B200_COLLECTIVE_REDUCE_SCATTER = 5,
+  IREE_HAL_B200_COLLECTIVE_SEND = 6,
+  IREE_HAL_B200_COLLECTIVE_RECV = 7,
+  IREE_HAL_B200_COLLECTIVE_SEND_RECV = 8,
+};
+enum {
+  IREE_HAL_B200_REDUCTION_NONE = 0,
+  IREE_HAL_B200_REDUCTION_SUM = 1,
+  IREE_HAL_B200_REDUCTION_PRODUCT = 2,
+  IREE_HAL_B200_REDUCTION_MINIMUM = 3,
+  IREE_HAL_B200_REDUCTION_MAXIMUM = 4,
+  IREE_HAL_B200_REDUCTION_AVERAGE = 5,
+};
+iree_b200_status_t iree_hal_b200_command_buffer_collective(iree_hal_b200_command_buffer_t* command_buffer,
+                                                           iree_hal_b200_channel_t* channel, int32_t kind,
+                                                           int32_t reduction, int32_t element_type, uint32_t param,
+                                                           const void* send_device_ptr, void* recv_device_ptr,
+                                                           size_t element_count);
+
 /* Device memory of other ranks (processes) of the same node. `export` yields an opaque
  * IREE_HAL_B200_PEER_HANDLE_SIZE-byte handle for a buffer allocated here; the owner ships it to
  * its peers by any means and they `import` it, which gives a device pointer valid in the

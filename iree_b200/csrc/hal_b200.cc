@@ -225,6 +225,12 @@ struct NcclSymbols {
   int (*ncclGroupStart)() = nullptr;
   int (*ncclGroupEnd)() = nullptr;
   int (*ncclCommSplit)(ncclComm_t, int, int, ncclComm_t*, void*) = nullptr;  // optional (NCCL >= 2.18)
+  // optional: the collective kinds beyond all-gather
+  int (*ncclBroadcast)(const void*, void*, size_t, int, int, ncclComm_t, CUstream) = nullptr;
+  int (*ncclReduce)(const void*, void*, size_t, int, int, int, ncclComm_t, CUstream) = nullptr;
+  int (*ncclReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, CUstream) = nullptr;
+  int (*ncclSend)(const void*, size_t, int, int, ncclComm_t, CUstream) = nullptr;
+  int (*ncclRecv)(void*, size_t, int, int, ncclComm_t, CUstream) = nullptr;
   int (*ncclCommCount)(const ncclComm_t, int*) = nullptr;                   // optional
   int (*ncclCommUserRank)(const ncclComm_t, int*) = nullptr;                // optional
   const char* (*ncclGetErrorString)(int) = nullptr;
@@ -259,6 +265,11 @@ iree_b200_status_t ensure_nccl() {
       ok = load_sym(g_nccl.handle, "ncclAllGather", g_nccl.ncclAllGather) && ok;
       load_sym(g_nccl.handle, "ncclAllReduce", g_nccl.ncclAllReduce);
       load_sym(g_nccl.handle, "ncclCommSplit", g_nccl.ncclCommSplit);
+      load_sym(g_nccl.handle, "ncclBroadcast", g_nccl.ncclBroadcast);
+      load_sym(g_nccl.handle, "ncclReduce", g_nccl.ncclReduce);
+      load_sym(g_nccl.handle, "ncclReduceScatter", g_nccl.ncclReduceScatter);
+      load_sym(g_nccl.handle, "ncclSend", g_nccl.ncclSend);
+      load_sym(g_nccl.handle, "ncclRecv", g_nccl.ncclRecv);
       load_sym(g_nccl.handle, "ncclCommCount", g_nccl.ncclCommCount);
       load_sym(g_nccl.handle, "ncclCommUserRank", g_nccl.ncclCommUserRank);
       ok = load_sym(g_nccl.handle, "ncclGroupStart", g_nccl.ncclGroupStart) && ok;
@@ -1288,6 +1299,119 @@ iree_b200_status_t iree_hal_b200_command_buffer_all_gather(iree_hal_b200_command
   CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(command_buffer->device->context), "cuCtxSetCurrent");
   return all_gather_on(command_buffer, channel, element_type, send_device_ptr, recv_device_ptr, element_count,
                        command_buffer->device->stream);
+}
+
+// iree_hal_command_buffer_collective for every kind the reference's NCCL channel submits
+// (nccl_channel.c:327-500): one group per call, on the dispatch stream.
+iree_b200_status_t iree_hal_b200_command_buffer_collective(iree_hal_b200_command_buffer_t* command_buffer,
+                                                           iree_hal_b200_channel_t* channel, int32_t kind,
+                                                           int32_t reduction, int32_t element_type, uint32_t param,
+                                                           const void* send_device_ptr, void* recv_device_ptr,
+                                                           size_t element_count) {
+  if (!command_buffer || !channel) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  if (command_buffer->recording)
+    return fail(IREE_B200_STATUS_UNIMPLEMENTED, "collectives cannot be recorded into a graph");
+  B200_RETURN_IF_ERROR(ensure_nccl());
+  int type, elem_bytes;  // ncclDataType_t values: int8 0, int32 2, float16 6, float32 7, bfloat16 9
+  switch (element_type) {
+    case IREE_HAL_B200_ELEMENT_TYPE_I8: type = 0, elem_bytes = 1; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_I32: type = 2, elem_bytes = 4; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_F16: type = 6, elem_bytes = 2; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_F32: type = 7, elem_bytes = 4; break;
+    case IREE_HAL_B200_ELEMENT_TYPE_BF16: type = 9, elem_bytes = 2; break;
+    default: return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unsupported collective element type %d", element_type);
+  }
+  const bool reduces = kind == IREE_HAL_B200_COLLECTIVE_ALL_REDUCE || kind == IREE_HAL_B200_COLLECTIVE_REDUCE ||
+                       kind == IREE_HAL_B200_COLLECTIVE_REDUCE_SCATTER;
+  int op = 0;  // ncclRedOp_t: sum 0, prod 1, max 2, min 3, avg 4
+  if (reduces) {
+    switch (reduction) {
+      case IREE_HAL_B200_REDUCTION_SUM: op = 0; break;
+      case IREE_HAL_B200_REDUCTION_PRODUCT: op = 1; break;
+      case IREE_HAL_B200_REDUCTION_MINIMUM: op = 3; break;
+      case IREE_HAL_B200_REDUCTION_MAXIMUM: op = 2; break;
+      case IREE_HAL_B200_REDUCTION_AVERAGE: op = 4; break;
+      default: return fail(IREE_B200_STATUS_UNIMPLEMENTED, "unhandled reduction type for collective op");
+    }
+  }
+  const bool sends = kind != IREE_HAL_B200_COLLECTIVE_RECV, receives = kind != IREE_HAL_B200_COLLECTIVE_SEND;
+  if ((sends && !send_device_ptr) || (receives && !recv_device_ptr))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "buffer pointer is NULL");
+  iree_hal_b200_device_t* d = command_buffer->device;
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(d->context), "cuCtxSetCurrent");
+  const int peer = static_cast<int>(param & 0xffff), peer2 = static_cast<int>(param >> 16);
+  auto need = [&](bool have, const char* name) -> iree_b200_status_t {
+    return have ? IREE_B200_STATUS_OK : fail(IREE_B200_STATUS_UNAVAILABLE, "this NCCL has no %s", name);
+  };
+  B200_RETURN_IF_ERROR(nccl_check(g_nccl.ncclGroupStart(), "ncclGroupStart"));
+  iree_b200_status_t st = IREE_B200_STATUS_OK;
+  switch (kind) {
+    case IREE_HAL_B200_COLLECTIVE_ALL_GATHER:
+      st = nccl_check(g_nccl.ncclAllGather(send_device_ptr, recv_device_ptr, element_count, type, channel->comm, d->stream),
+                      "ncclAllGather");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_ALL_REDUCE:
+      st = need(g_nccl.ncclAllReduce, "ncclAllReduce");
+      if (!st)
+        st = nccl_check(g_nccl.ncclAllReduce(send_device_ptr, recv_device_ptr, element_count, type, op, channel->comm, d->stream),
+                        "ncclAllReduce");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_ALL_TO_ALL: {
+      // element_count is the whole send buffer: count / ranks elements go to, and come from, every rank
+      st = need(g_nccl.ncclSend && g_nccl.ncclRecv, "ncclSend / ncclRecv");
+      const size_t per_rank = element_count / channel->count;
+      for (int r = 0; r < channel->count && !st; ++r) {
+        st = nccl_check(g_nccl.ncclSend(static_cast<const uint8_t*>(send_device_ptr) + r * per_rank * elem_bytes, per_rank, type,
+                                        r, channel->comm, d->stream),
+                        "ncclSend");
+        if (!st)
+          st = nccl_check(g_nccl.ncclRecv(static_cast<uint8_t*>(recv_device_ptr) + r * per_rank * elem_bytes, per_rank, type, r,
+                                          channel->comm, d->stream),
+                          "ncclRecv");
+      }
+      break;
+    }
+    case IREE_HAL_B200_COLLECTIVE_BROADCAST:
+      st = need(g_nccl.ncclBroadcast, "ncclBroadcast");
+      if (!st)
+        st = nccl_check(g_nccl.ncclBroadcast(send_device_ptr, recv_device_ptr, element_count, type, peer, channel->comm, d->stream),
+                        "ncclBroadcast");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_REDUCE:
+      st = need(g_nccl.ncclReduce, "ncclReduce");
+      if (!st)
+        st = nccl_check(g_nccl.ncclReduce(send_device_ptr, recv_device_ptr, element_count, type, op, peer, channel->comm, d->stream),
+                        "ncclReduce");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_REDUCE_SCATTER:
+      // element_count is what every rank receives
+      st = need(g_nccl.ncclReduceScatter, "ncclReduceScatter");
+      if (!st)
+        st = nccl_check(g_nccl.ncclReduceScatter(send_device_ptr, recv_device_ptr, element_count, type, op, channel->comm, d->stream),
+                        "ncclReduceScatter");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_SEND:
+      st = need(g_nccl.ncclSend, "ncclSend");
+      if (!st) st = nccl_check(g_nccl.ncclSend(send_device_ptr, element_count, type, peer, channel->comm, d->stream), "ncclSend");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_RECV:
+      st = need(g_nccl.ncclRecv, "ncclRecv");
+      if (!st) st = nccl_check(g_nccl.ncclRecv(recv_device_ptr, element_count, type, peer, channel->comm, d->stream), "ncclRecv");
+      break;
+    case IREE_HAL_B200_COLLECTIVE_SEND_RECV:
+      // param: low 16 bits the rank to send to, high 16 bits the rank to receive from
+      st = need(g_nccl.ncclSend && g_nccl.ncclRecv, "ncclSend / ncclRecv");
+      if (!st) st = nccl_check(g_nccl.ncclSend(send_device_ptr, element_count, type, peer, channel->comm, d->stream), "ncclSend");
+      if (!st) st = nccl_check(g_nccl.ncclRecv(recv_device_ptr, element_count, type, peer2, channel->comm, d->stream), "ncclRecv");
+      break;
+    default:
+      st = fail(IREE_B200_STATUS_INVALID_ARGUMENT, "unknown collective kind %d", kind);
+  }
+  const iree_b200_status_t end = nccl_check(g_nccl.ncclGroupEnd(), "ncclGroupEnd");
+  if (st) return st;
+  if (end) return end;
+  command_buffer->barrier_pending = true;
+  return IREE_B200_STATUS_OK;
 }
 
 iree_b200_status_t iree_hal_b200_command_buffer_all_gather_overlapped(iree_hal_b200_command_buffer_t* command_buffer,

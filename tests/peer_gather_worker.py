@@ -70,6 +70,46 @@ def main() -> int:
         ok = ok and bool(sub2.value) and lib.iree_hal_b200_channel_count(sub2) == world - 1
         ok = ok and lib.iree_hal_b200_channel_rank(sub2) == rank
         lib.iree_hal_b200_channel_release(sub2)
+    # The other collective kinds through iree_hal_b200_command_buffer_collective (the reference's enum values).
+    def collective(kind, reduction, param, send, recv, count, etype=2):
+        rt.check(lib.iree_hal_b200_command_buffer_collective(
+            ctx.command_buffer, channel, C.c_int32(kind), C.c_int32(reduction), C.c_int32(etype), C.c_uint32(param),
+            C.c_void_p(send.ptr if send is not None else None), C.c_void_p(recv.ptr if recv is not None else None),
+            C.c_size_t(count)))
+        ctx.synchronize()
+    m = 1024
+    mine = (np.arange(m, dtype=np.int32) + 10 * rank).astype(np.int32)
+    every = [(np.arange(m, dtype=np.int32) + 10 * p).astype(np.int32) for p in range(world)]
+    src, dst = ctx.to_device(mine), ctx.alloc(m * 4 * world).fill(0)
+    collective(1, 1, 0, src, dst, m)                                   # ALL_REDUCE, SUM
+    ok = ok and np.array_equal(dst.download(np.int32, (m,)), sum(every))
+    collective(1, 4, 0, src, dst, m)                                   # ALL_REDUCE, MAXIMUM
+    ok = ok and np.array_equal(dst.download(np.int32, (m,)), every[-1])
+    collective(3, 0, world - 1, src, dst, m)                           # BROADCAST from the last rank
+    ok = ok and np.array_equal(dst.download(np.int32, (m,)), every[-1])
+    dst.fill(0)
+    collective(4, 1, 0, src, dst, m)                                   # REDUCE to rank 0
+    if rank == 0:
+        ok = ok and np.array_equal(dst.download(np.int32, (m,)), sum(every))
+    collective(5, 1, 0, src, dst, m // world)                          # REDUCE_SCATTER: m / world elements per rank
+    ok = ok and np.array_equal(dst.download(np.int32, (m // world,)), sum(every)[rank * (m // world):(rank + 1) * (m // world)])
+    collective(2, 0, 0, src, dst, m)                                   # ALL_TO_ALL: m / world elements per peer
+    want = np.concatenate([every[p][rank * (m // world):(rank + 1) * (m // world)] for p in range(world)])
+    ok = ok and np.array_equal(dst.download(np.int32, (m,)), want)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    collective(8, 0, nxt | (prv << 16), src, dst, m)                   # SEND_RECV around the ring
+    ok = ok and np.array_equal(dst.download(np.int32, (m,)), every[prv])
+    if world == 2:
+        dst.fill(0)
+        if rank == 0:
+            collective(6, 0, 1, src, None, m)                          # SEND to rank 1
+        else:
+            collective(7, 0, 0, None, dst, m)                          # RECV from rank 0
+            ok = ok and np.array_equal(dst.download(np.int32, (m,)), every[0])
+    f = ctx.to_device(np.full(m, 1.5 + rank, np.float32))
+    fd = ctx.alloc(m * 4)
+    collective(1, 5, 0, f, fd, m, etype=3)                             # ALL_REDUCE, AVERAGE, f32
+    ok = ok and np.allclose(fd.download(np.float32, (m,)), 1.5 + (world - 1) / 2)
     lib.iree_hal_b200_channel_release(channel)
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

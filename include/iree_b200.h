@@ -66,6 +66,7 @@ typedef struct iree_hal_b200_channel_t iree_hal_b200_channel_t;
 typedef struct iree_hal_b200_graph_t iree_hal_b200_graph_t;
 typedef struct iree_hal_b200_descriptor_set_layout_t iree_hal_b200_descriptor_set_layout_t;
 typedef struct iree_hal_b200_pipeline_layout_t iree_hal_b200_pipeline_layout_t;
+typedef struct iree_hal_b200_semaphore_t iree_hal_b200_semaphore_t;
 
 /* ---- device -------------------------------------------------------------------------------
  * Stands in for iree_hal_cuda_driver_create + device creation
@@ -245,6 +246,36 @@ iree_b200_status_t iree_hal_b200_command_buffer_end_graph(iree_hal_b200_command_
 iree_b200_status_t iree_hal_b200_graph_execute(iree_hal_b200_command_buffer_t* command_buffer,
                                                iree_hal_b200_graph_t* graph);
 void iree_hal_b200_graph_release(iree_hal_b200_graph_t* graph);
+
+/* ---- resources, semaphores, queue submission --------------------------------------------------------
+ * Executables, command buffers, channels and semaphores are reference counted like the reference's
+ * iree_hal_resource_t (runtime/src/iree/hal/resource.h; drivers/cuda/native_executable.c:21-25): created
+ * with one reference, `retain` adds one, `release` drops one and destroys the object with the last. */
+void iree_hal_b200_executable_retain(iree_hal_b200_executable_t* executable);
+void iree_hal_b200_command_buffer_retain(iree_hal_b200_command_buffer_t* command_buffer);
+void iree_hal_b200_channel_retain(iree_hal_b200_channel_t* channel);
+/* Timeline semaphores (runtime/src/iree/hal/semaphore.h:60-140): a 64-bit payload that only grows, advanced
+ * by the host (`signal`; OUT_OF_RANGE unless the value grows) or by the device when it passes the point
+ * behind which queue_execute queued the signal. `wait` returns OK once the payload is at least `value`,
+ * DEADLINE_EXCEEDED after timeout_ms (negative: no limit). */
+iree_b200_status_t iree_hal_b200_semaphore_create(iree_hal_b200_device_t* device, uint64_t initial_value,
+                                                  iree_hal_b200_semaphore_t** out_semaphore);
+void iree_hal_b200_semaphore_retain(iree_hal_b200_semaphore_t* semaphore);
+void iree_hal_b200_semaphore_release(iree_hal_b200_semaphore_t* semaphore);
+iree_b200_status_t iree_hal_b200_semaphore_query(iree_hal_b200_semaphore_t* semaphore, uint64_t* out_value);
+iree_b200_status_t iree_hal_b200_semaphore_signal(iree_hal_b200_semaphore_t* semaphore, uint64_t new_value);
+iree_b200_status_t iree_hal_b200_semaphore_wait(iree_hal_b200_semaphore_t* semaphore, uint64_t value, int64_t timeout_ms);
+/* iree_hal_device_queue_execute (runtime/src/iree/hal/device.h; drivers/cuda/cuda_device.c): once every wait
+ * semaphore has reached its value, the recorded graphs run in order on the dispatch stream, then every
+ * signal semaphore is advanced to its value. A wait on a value that a queued device signal will reach
+ * costs the host nothing (the stream waits for it); a wait only a later host signal can satisfy holds this
+ * call, for ten seconds at most (DEADLINE_EXCEEDED). With no graphs this is a queue barrier. */
+iree_b200_status_t iree_hal_b200_device_queue_execute(iree_hal_b200_device_t* device, size_t wait_count,
+                                                      iree_hal_b200_semaphore_t* const* wait_semaphores,
+                                                      const uint64_t* wait_values, size_t signal_count,
+                                                      iree_hal_b200_semaphore_t* const* signal_semaphores,
+                                                      const uint64_t* signal_values, size_t graph_count,
+                                                      iree_hal_b200_graph_t* const* graphs);
 
 /* ---- collective channel -------------------------------------------------------------------------
  * iree_hal_channel_create with explicit {id, rank, count}

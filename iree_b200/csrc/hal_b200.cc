@@ -14,8 +14,11 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+#include <chrono>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/iree_b200.h"
@@ -93,6 +96,7 @@ struct CudaSymbols {
   CU_FN(cuMemcpyDtoDAsync, CUdeviceptr, CUdeviceptr, size_t, CUstream)
   CU_FN(cuLaunchKernelEx, const CUlaunchConfig*, CUfunction, void**, void**)
   CU_FN(cuGraphAddDependencies_v2, CUgraph, const CUgraphNode*, const CUgraphNode*, const CUgraphEdgeData*, size_t)
+  CU_FN(cuEventQuery, CUevent)
   // optional (transfer commands)
   CU_FN(cuMemsetD16Async, CUdeviceptr, unsigned short, size_t, CUstream)
   CU_FN(cuMemsetD32Async, CUdeviceptr, unsigned int, size_t, CUstream)
@@ -173,6 +177,7 @@ iree_b200_status_t ensure_cuda() {
       load_sym(g_cu.handle, "cuMemcpyDtoDAsync_v2", g_cu.cuMemcpyDtoDAsync);
       load_sym(g_cu.handle, "cuLaunchKernelEx", g_cu.cuLaunchKernelEx);
       load_sym(g_cu.handle, "cuGraphAddDependencies_v2", g_cu.cuGraphAddDependencies_v2);
+      load_sym(g_cu.handle, "cuEventQuery", g_cu.cuEventQuery);
       load_sym(g_cu.handle, "cuMemsetD16Async", g_cu.cuMemsetD16Async);
       load_sym(g_cu.handle, "cuMemsetD32Async", g_cu.cuMemsetD32Async);
       load_sym(g_cu.handle, "cuGraphAddMemcpyNode", g_cu.cuGraphAddMemcpyNode);
@@ -439,6 +444,7 @@ struct iree_hal_b200_device_t {
 };
 
 struct iree_hal_b200_executable_t {
+  std::atomic<int> references{1};  // iree_hal_resource_t's count (native_executable.c:21-25)
   iree_hal_b200_device_t* device = nullptr;
   CUmodule module = nullptr;
   struct Entry {
@@ -458,6 +464,7 @@ struct iree_hal_b200_graph_t {
 };
 
 struct iree_hal_b200_command_buffer_t {
+  std::atomic<int> references{1};
   iree_hal_b200_device_t* device = nullptr;
   // Graph mode: dispatches become kernel nodes chained one after the other instead of launches.
   CUgraph recording = nullptr;
@@ -483,7 +490,22 @@ struct iree_hal_b200_pipeline_layout_t {
   uint32_t push_constant_count = 0;
 };
 
+// A timeline semaphore (hal/semaphore.h): a 64-bit payload that only grows. Values are reached by a host
+// signal or by the device passing an event that queue_execute recorded behind the work it submitted.
+struct iree_hal_b200_semaphore_t {
+  std::atomic<int> references{1};
+  iree_hal_b200_device_t* device = nullptr;
+  std::mutex mutex;
+  uint64_t value = 0;
+  struct Pending {
+    uint64_t value;
+    CUevent event;
+  };
+  std::vector<Pending> pending;  // in submission order: values grow
+};
+
 struct iree_hal_b200_channel_t {
+  std::atomic<int> references{1};
   iree_hal_b200_device_t* device = nullptr;
   ncclComm_t comm = nullptr;
   int32_t rank = 0, count = 1;
@@ -793,8 +815,11 @@ iree_b200_status_t iree_hal_b200_executable_create(iree_hal_b200_device_t* devic
   return IREE_B200_STATUS_OK;
 }
 
+void iree_hal_b200_executable_retain(iree_hal_b200_executable_t* executable) {
+  if (executable) executable->references.fetch_add(1);
+}
 void iree_hal_b200_executable_release(iree_hal_b200_executable_t* executable) {
-  if (!executable) return;
+  if (!executable || executable->references.fetch_sub(1) != 1) return;
   g_cu.cuCtxSetCurrent(executable->device->context);
   if (executable->module) g_cu.cuModuleUnload(executable->module);
   delete executable;
@@ -818,7 +843,12 @@ iree_b200_status_t iree_hal_b200_command_buffer_create(iree_hal_b200_device_t* d
   *out_command_buffer = cb;
   return IREE_B200_STATUS_OK;
 }
-void iree_hal_b200_command_buffer_release(iree_hal_b200_command_buffer_t* command_buffer) { delete command_buffer; }
+void iree_hal_b200_command_buffer_retain(iree_hal_b200_command_buffer_t* command_buffer) {
+  if (command_buffer) command_buffer->references.fetch_add(1);
+}
+void iree_hal_b200_command_buffer_release(iree_hal_b200_command_buffer_t* command_buffer) {
+  if (command_buffer && command_buffer->references.fetch_sub(1) == 1) delete command_buffer;
+}
 
 iree_b200_status_t iree_hal_b200_command_buffer_push_constants(iree_hal_b200_command_buffer_t* command_buffer,
                                                                size_t offset, const void* values,
@@ -1189,6 +1219,139 @@ void iree_hal_b200_graph_release(iree_hal_b200_graph_t* graph) {
   delete graph;
 }
 
+// ---- semaphores and queue submission ------------------------------------------------------------------
+iree_b200_status_t iree_hal_b200_semaphore_create(iree_hal_b200_device_t* device, uint64_t initial_value,
+                                                  iree_hal_b200_semaphore_t** out_semaphore) {
+  if (!device || !out_semaphore) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  auto* sem = new iree_hal_b200_semaphore_t();
+  sem->device = device;
+  sem->value = initial_value;
+  *out_semaphore = sem;
+  return IREE_B200_STATUS_OK;
+}
+void iree_hal_b200_semaphore_retain(iree_hal_b200_semaphore_t* semaphore) {
+  if (semaphore) semaphore->references.fetch_add(1);
+}
+void iree_hal_b200_semaphore_release(iree_hal_b200_semaphore_t* semaphore) {
+  if (!semaphore || semaphore->references.fetch_sub(1) != 1) return;
+  g_cu.cuCtxSetCurrent(semaphore->device->context);
+  for (auto& p : semaphore->pending) g_cu.cuEventDestroy(p.event);
+  delete semaphore;
+}
+
+// Retires the pending device signals the device has passed; the caller holds the mutex.
+static iree_b200_status_t semaphore_advance(iree_hal_b200_semaphore_t* sem) {
+  if (sem->pending.empty()) return IREE_B200_STATUS_OK;
+  if (!g_cu.cuEventQuery) return fail(IREE_B200_STATUS_UNAVAILABLE, "this CUDA driver has no cuEventQuery");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(sem->device->context), "cuCtxSetCurrent");
+  while (!sem->pending.empty()) {
+    const CUresult r = g_cu.cuEventQuery(sem->pending.front().event);
+    if (r == CUDA_ERROR_NOT_READY) break;
+    CU_RETURN_IF_ERROR(r, "cuEventQuery");
+    if (sem->pending.front().value > sem->value) sem->value = sem->pending.front().value;
+    g_cu.cuEventDestroy(sem->pending.front().event);
+    sem->pending.erase(sem->pending.begin());
+  }
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_semaphore_query(iree_hal_b200_semaphore_t* semaphore, uint64_t* out_value) {
+  if (!semaphore || !out_value) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL argument");
+  std::lock_guard<std::mutex> lock(semaphore->mutex);
+  B200_RETURN_IF_ERROR(semaphore_advance(semaphore));
+  *out_value = semaphore->value;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_semaphore_signal(iree_hal_b200_semaphore_t* semaphore, uint64_t new_value) {
+  if (!semaphore) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "semaphore is NULL");
+  std::lock_guard<std::mutex> lock(semaphore->mutex);
+  B200_RETURN_IF_ERROR(semaphore_advance(semaphore));
+  if (new_value <= semaphore->value)
+    return fail(IREE_B200_STATUS_OUT_OF_RANGE, "semaphore values must be monotonically increasing: %llu is not above %llu",
+                static_cast<unsigned long long>(new_value), static_cast<unsigned long long>(semaphore->value));
+  semaphore->value = new_value;
+  return IREE_B200_STATUS_OK;
+}
+
+iree_b200_status_t iree_hal_b200_semaphore_wait(iree_hal_b200_semaphore_t* semaphore, uint64_t value, int64_t timeout_ms) {
+  if (!semaphore) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "semaphore is NULL");
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
+  while (true) {
+    CUevent wait_on = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(semaphore->mutex);
+      B200_RETURN_IF_ERROR(semaphore_advance(semaphore));
+      if (semaphore->value >= value) return IREE_B200_STATUS_OK;
+      for (auto& p : semaphore->pending)
+        if (p.value >= value) {
+          wait_on = p.event;
+          break;
+        }
+    }
+    if (timeout_ms >= 0 && std::chrono::steady_clock::now() >= deadline)
+      return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "semaphore did not reach %llu in %lld ms",
+                  static_cast<unsigned long long>(value), static_cast<long long>(timeout_ms));
+    // A queued device signal will reach the value: sleep briefly between queries (the event is owned by the
+    // semaphore and may be retired by another thread, so it is not waited on directly). Otherwise only a host
+    // signal can: poll for it.
+    (void)wait_on;
+    std::this_thread::sleep_for(std::chrono::microseconds(wait_on ? 20 : 200));
+  }
+}
+
+iree_b200_status_t iree_hal_b200_device_queue_execute(iree_hal_b200_device_t* device, size_t wait_count,
+                                                      iree_hal_b200_semaphore_t* const* wait_semaphores,
+                                                      const uint64_t* wait_values, size_t signal_count,
+                                                      iree_hal_b200_semaphore_t* const* signal_semaphores,
+                                                      const uint64_t* signal_values, size_t graph_count,
+                                                      iree_hal_b200_graph_t* const* graphs) {
+  if (!device) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "device is NULL");
+  if ((wait_count && (!wait_semaphores || !wait_values)) || (signal_count && (!signal_semaphores || !signal_values)) ||
+      (graph_count && !graphs))
+    return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "NULL list");
+  CU_RETURN_IF_ERROR(g_cu.cuCtxSetCurrent(device->context), "cuCtxSetCurrent");
+  // Waits: a value already reached needs nothing; one a queued device signal will reach is waited for by the
+  // stream; one only the host can still signal holds this call (at most ten seconds).
+  for (size_t i = 0; i < wait_count; ++i) {
+    iree_hal_b200_semaphore_t* sem = wait_semaphores[i];
+    if (!sem) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "wait semaphore %zu is NULL", i);
+    bool satisfied = false;
+    {
+      std::lock_guard<std::mutex> lock(sem->mutex);
+      B200_RETURN_IF_ERROR(semaphore_advance(sem));
+      if (sem->value >= wait_values[i]) satisfied = true;
+      for (auto& p : sem->pending)
+        if (!satisfied && p.value >= wait_values[i]) {
+          CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(device->stream, p.event, 0), "cuStreamWaitEvent");
+          satisfied = true;
+        }
+    }
+    if (!satisfied) B200_RETURN_IF_ERROR(iree_hal_b200_semaphore_wait(sem, wait_values[i], 10000));
+  }
+  for (size_t i = 0; i < graph_count; ++i) {
+    if (!graphs[i]) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "command buffer %zu is NULL", i);
+    CU_RETURN_IF_ERROR(g_cu.cuGraphLaunch(graphs[i]->exec, device->stream), "cuGraphLaunch");
+  }
+  for (size_t i = 0; i < signal_count; ++i) {
+    iree_hal_b200_semaphore_t* sem = signal_semaphores[i];
+    if (!sem) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "signal semaphore %zu is NULL", i);
+    std::lock_guard<std::mutex> lock(sem->mutex);
+    const uint64_t last = sem->pending.empty() ? sem->value : sem->pending.back().value;
+    if (signal_values[i] <= last)
+      return fail(IREE_B200_STATUS_OUT_OF_RANGE, "semaphore values must be monotonically increasing");
+    CUevent ev = nullptr;
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&ev, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+    const CUresult r = g_cu.cuEventRecord(ev, device->stream);
+    if (r != CUDA_SUCCESS) {
+      g_cu.cuEventDestroy(ev);
+      CU_RETURN_IF_ERROR(r, "cuEventRecord");
+    }
+    sem->pending.push_back({signal_values[i], ev});
+  }
+  return IREE_B200_STATUS_OK;
+}
+
 // ---- channel ------------------------------------------------------------------------------------------
 iree_b200_status_t iree_hal_b200_channel_create_id(void* out_id, size_t id_capacity) {
   if (!out_id || id_capacity < IREE_HAL_B200_CHANNEL_ID_SIZE)
@@ -1259,8 +1422,11 @@ iree_b200_status_t iree_hal_b200_channel_split(iree_hal_b200_channel_t* base_cha
   return IREE_B200_STATUS_OK;
 }
 
+void iree_hal_b200_channel_retain(iree_hal_b200_channel_t* channel) {
+  if (channel) channel->references.fetch_add(1);
+}
 void iree_hal_b200_channel_release(iree_hal_b200_channel_t* channel) {
-  if (!channel) return;
+  if (!channel || channel->references.fetch_sub(1) != 1) return;
   if (channel->comm) g_nccl.ncclCommDestroy(channel->comm);
   if (channel->barrier_word) iree_hal_b200_buffer_free(channel->device, channel->barrier_word);
   delete channel;

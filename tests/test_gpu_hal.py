@@ -115,3 +115,69 @@ def test_dispatch_through_a_pipeline_layout_of_two_sets(ctx, graph):
     assert e.value.code_name == "INVALID_ARGUMENT"
     for x in (da, db, out0, out1):
         x.free()
+
+
+def test_semaphores_and_queue_execute(ctx):
+    """Timeline semaphores advanced by the device behind queued graphs and by the host; waits that the
+    stream serves, a wait only the host can satisfy, the monotonic rule and a wait that runs out
+    (hal/semaphore.h:60-140; iree_hal_device_queue_execute)."""
+    import threading
+    import time
+    lib = ib.library()
+    dev = ctx.device
+    n = 1 << 20
+    a, b = ctx.alloc(n).fill(0), ctx.alloc(n).fill(0)
+
+    def graph_of(record):
+        ctx.begin_graph()
+        record()
+        g = ctx.end_graph()
+        return g
+
+    g1 = graph_of(lambda: ctx.fill_buffer(a, 0, n, bytes([0x5A])))
+    g2 = graph_of(lambda: ctx.copy_buffer(a, 0, b, 0, n))
+    sem, host_sem = C.c_void_p(), C.c_void_p()
+    rt.check(lib.iree_hal_b200_semaphore_create(dev, C.c_uint64(0), C.byref(sem)))
+    rt.check(lib.iree_hal_b200_semaphore_create(dev, C.c_uint64(5), C.byref(host_sem)))
+
+    def execute(waits, signals, graphs):
+        ws = (C.c_void_p * max(len(waits), 1))(*[w[0].value for w in waits])
+        wv = (C.c_uint64 * max(len(waits), 1))(*[w[1] for w in waits])
+        ss = (C.c_void_p * max(len(signals), 1))(*[s[0].value for s in signals])
+        sv = (C.c_uint64 * max(len(signals), 1))(*[s[1] for s in signals])
+        gs = (C.c_void_p * max(len(graphs), 1))(*[g.handle.value for g in graphs])
+        rt.check(lib.iree_hal_b200_device_queue_execute(dev, C.c_size_t(len(waits)), ws, wv, C.c_size_t(len(signals)), ss, sv,
+                                                        C.c_size_t(len(graphs)), gs))
+
+    # fill signals 1; the copy waits for 1 (served by the stream) and signals 2; a barrier submission signals 3
+    execute([], [(sem, 1)], [g1])
+    execute([(sem, 1)], [(sem, 2)], [g2])
+    execute([(sem, 2)], [(sem, 3)], [])
+    rt.check(lib.iree_hal_b200_semaphore_wait(sem, C.c_uint64(3), C.c_int64(5000)))
+    value = C.c_uint64()
+    rt.check(lib.iree_hal_b200_semaphore_query(sem, C.byref(value)))
+    assert value.value == 3
+    assert (b.download(np.uint8, (n,)) == 0x5A).all()
+
+    # a wait only the host can satisfy: the submission is held until another thread signals
+    a.fill(0); b.fill(0)
+    t = threading.Thread(target=lambda: (time.sleep(0.05), rt.check(lib.iree_hal_b200_semaphore_signal(host_sem, C.c_uint64(6)))))
+    t.start()
+    execute([(host_sem, 6)], [(sem, 4)], [g1, g2])
+    t.join()
+    rt.check(lib.iree_hal_b200_semaphore_wait(sem, C.c_uint64(4), C.c_int64(5000)))
+    assert (b.download(np.uint8, (n,)) == 0x5A).all()
+
+    assert lib.iree_hal_b200_semaphore_signal(sem, C.c_uint64(4)) == 11            # OUT_OF_RANGE: values only grow
+    assert lib.iree_hal_b200_semaphore_wait(sem, C.c_uint64(100), C.c_int64(30)) == 4  # DEADLINE_EXCEEDED
+    with pytest.raises(ib.IreeB200Error) as e:
+        execute([], [(sem, 2)], [])                                                # a signal below the payload
+    assert e.value.code_name == "OUT_OF_RANGE"
+    lib.iree_hal_b200_semaphore_retain(sem)
+    lib.iree_hal_b200_semaphore_release(sem)
+    rt.check(lib.iree_hal_b200_semaphore_query(sem, C.byref(value)))              # still alive: one reference left
+    assert value.value == 4
+    lib.iree_hal_b200_semaphore_release(sem)
+    lib.iree_hal_b200_semaphore_release(host_sem)
+    g1.release(); g2.release()
+    a.free(); b.free()

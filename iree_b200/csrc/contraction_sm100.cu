@@ -353,7 +353,20 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
     if (lane == 0) {
       const uint32_t b_major = (s.b_layout == kBLayoutKN) ? 1u : 0u;
       const uint32_t idesc = make_instr_desc(T::kCFormat, T::kFormat, T::kFormat, 0u, b_major, kBM, s.bn);
-      uint32_t it = 0, local_tile = 0;
+      // This thread's instruction stream must stay shorter than the MMAs it issues (a tile 64 or 128 wide
+      // finishes a K block's four MMAs in 128-256 cycles), so nothing per block is a division or a
+      // descriptor construction: stage and phase are running values, and a descriptor differs from the
+      // first stage's only in its address field (16-byte units).
+      // A (K-major, 128-byte swizzle): 8-row groups 1024 bytes apart; K advances 32 bytes per MMA.
+      // B as [N,K]: the same. B as [K,N] (MN-major): rows of K are 128 bytes apart, 8-row groups 1024 bytes
+      // apart (stride offset), the next chunk of columns starts kBK rows later (leading offset); K advances
+      // kUmmaK rows per MMA.
+      const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
+      const uint64_t b_desc0 = s.b_layout == kBLayoutNK ? make_smem_desc(smem_base + kAStageBytes, 16, 1024)
+                                                        : make_smem_desc(smem_base + kAStageBytes, kBK * kRowBytes, 1024);
+      const uint32_t b_step = s.b_layout == kBLayoutNK ? 2u : static_cast<uint32_t>(kUmmaK * kRowBytes) >> 4;
+      constexpr uint32_t kStageUnits = kStageBytes >> 4;
+      uint32_t it = 0, local_tile = 0, st = 0, ph = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x, ++local_tile) {
         int t, kb0, kb1;
@@ -368,8 +381,6 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kMaxBN;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int st = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(full_bar(st), ph, abort_flag)) {
             report(ws, kStatusTimeoutFull, it);
             *abort_flag = 1;
@@ -377,28 +388,25 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_src = smem_base + st * kStageBytes;
-          const uint32_t b_src = a_src + kAStageBytes;
+          const uint64_t a_desc = a_desc0 + st * kStageUnits, b_desc = b_desc0 + st * kStageUnits;
+          if constexpr (KIND == kI8) {
+            mma_i8_ss(d_tmem, a_desc, b_desc, idesc, kb > kb0 ? 1u : 0u);
+          } else {
+            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, kb > kb0 ? 1u : 0u);
+          }
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            // A (K-major, 128-byte swizzle): 8-row groups 1024 bytes apart; K advances 32 bytes.
-            const uint64_t a_desc = make_smem_desc(a_src + k * 32, 16, 1024);
-            uint64_t b_desc;
-            if (s.b_layout == kBLayoutNK) {
-              b_desc = make_smem_desc(b_src + k * 32, 16, 1024);
-            } else {
-              // B (MN-major): rows of K are 128 bytes apart, 8-row groups 1024 bytes apart (stride
-              // offset); the next chunk of columns starts kBK rows later (leading offset).
-              b_desc = make_smem_desc(b_src + k * (kUmmaK * kRowBytes), kBK * kRowBytes, 1024);
-            }
-            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
+          for (int k = 1; k < kBK / kUmmaK; ++k) {
             if constexpr (KIND == kI8) {
-              mma_i8_ss(d_tmem, a_desc, b_desc, idesc, acc);
+              mma_i8_ss_more(d_tmem, a_desc + 2 * k, b_desc + b_step * k, idesc);
             } else {
-              mma_f16_ss(d_tmem, a_desc, b_desc, idesc, acc);
+              mma_f16_ss_more(d_tmem, a_desc + 2 * k, b_desc + b_step * k, idesc);
             }
           }
           tc_commit(empty_bar(st));  // the stage is free once these MMAs have read it
+          if (++st == kStages) {
+            st = 0;
+            ph ^= 1;
+          }
         }
         if (ok) tc_commit(tmem_full_bar(buf));
       }

@@ -42,11 +42,13 @@ namespace b200 {
 
 constexpr int kWtWRows = 128;                             // weight rows per tile = TMEM lanes (MMA M)
 constexpr int kWtARows = 256;                             // activation rows per tile (MMA N)
-constexpr int kWtActStages = 4;
+constexpr int kWtActStagesLog2 = 2;
+constexpr int kWtActStages = 1 << kWtActStagesLog2;
 constexpr int kWtActStageBytes = kWtARows * 128;          // 32 KiB: 256 rows x 64 f16
 constexpr int kWtRawStages = 6;
 constexpr int kWtRawStageBytes = kWtWRows * 64;           // 8 KiB: 128 rows x 128 int4 = one scale group
-constexpr int kWtAStages = 8;                             // expanded-weight stages in tensor memory
+constexpr int kWtAStagesLog2 = 3;
+constexpr int kWtAStages = 1 << kWtAStagesLog2;                             // expanded-weight stages in tensor memory
 constexpr int kWtAStageColumns = 32;                      // 64 K as f16 pairs
 constexpr int kWtOutRows = 64;                            // result rows per staged piece
 constexpr int kWtOutStageBytes = kWtOutRows * kWtWRows * 2;  // 16 KiB
@@ -127,7 +129,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
       mbar_init(raw_empty(i), 8);  // a raw stage holds two K blocks: the four warps of each block's group
     }
     for (int i = 0; i < kWtAStages; ++i) {
-      mbar_init(a_full(i), 4);     // the four warps of the group that expanded the K block
+      mbar_init(a_full(i), 5);     // the four warps of the group that expanded the K block + the activation tile's expect_tx
       mbar_init(a_empty(i), 1);
     }
     mbar_init(d_full, 1);
@@ -176,10 +178,15 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(act_full(st), a_rows * 128);
-          tma_load_3d(smem_base + st * act_pitch, ws->map_a, act_full(st), kb * 64, tm * a_rows, 0);
-          if (a_rows > 128)
-            tma_load_3d(smem_base + st * act_pitch + 128 * 128, ws->map_a, act_full(st), kb * 64, tm * a_rows + 128, 0);
+          // The activation tile reports to the barrier of the block's expanded-weight stage: the issuing
+          // thread then waits once per K block, for both operands (its loop period, not the tensor pipe, is
+          // what bounds this kernel: every barrier wait costs it ~125 cycles even when the phase is long
+          // complete). That barrier's previous phase, block it - 8, completed before block it - act_stages'
+          // MMAs, which this thread has just waited for.
+          const uint32_t full = a_full(it % kWtAStages);
+          mbar_arrive_expect_tx(full, a_rows * 128);
+          tma_load_3d(smem_base + st * act_pitch, ws->map_a, full, kb * 64, tm * a_rows, 0);
+          if (a_rows > 128) tma_load_3d(smem_base + st * act_pitch + 128 * 128, ws->map_a, full, kb * 64, tm * a_rows + 128, 0);
         }
       }
     }
@@ -209,6 +216,13 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
     // -------- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_instr_desc(1u, 0u, 0u, 0u, 0u, kWtWRows, a_rows);
+      // This thread's instruction stream is what a K block waits for (measured: ~700 cycles per block with
+      // divisions by the run-time stage count and four descriptor constructions in it, against 512 of
+      // MMA), so everything per block is an add, a shift or a mask: the stage counts are powers of two,
+      // and a descriptor differs from the first stage's only in its address field (16-byte units).
+      const uint32_t act_mask = static_cast<uint32_t>(act_stages) - 1u;
+      const uint64_t desc0 = make_smem_desc(smem_base, 16, 1024);
+      const uint32_t stage_units = act_pitch >> 4;
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
@@ -219,25 +233,21 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         }
         tc_fence_after_sync();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int st = it % act_stages, as = it % kWtAStages;
-          if (!mbar_wait(act_full(st), (it / act_stages) & 1, abort_flag)) {
-            wt_report(ws, kStatusTimeoutFull, it);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          if (!mbar_wait(a_full(as), (it / kWtAStages) & 1, abort_flag)) {
+          const uint32_t st = it & act_mask, as = it & (kWtAStages - 1);
+          if (!mbar_wait(a_full(as), (it >> kWtAStagesLog2) & 1, abort_flag)) {  // expanded weights and activation tile
             wt_report(ws, kStatusTimeoutDequant, it);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t b_src = smem_base + st * act_pitch;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts(tmem_base, tmem_a + as * kWtAStageColumns + k * 8, make_smem_desc(b_src + k * 32, 16, 1024), idesc,
-                       (kb > 0 || k > 0) ? 1u : 0u);
+          const uint64_t bd = desc0 + st * stage_units;          // + 2 per 32 bytes of K
+          const uint32_t a_t = tmem_a + as * kWtAStageColumns;   // + 8 columns per 16 K
+          if (kb == 0) mma_f16_ts_first(tmem_base, a_t, bd, idesc);
+          else mma_f16_ts_more(tmem_base, a_t, bd, idesc);
+          mma_f16_ts_more(tmem_base, a_t + 8, bd + 2, idesc);
+          mma_f16_ts_more(tmem_base, a_t + 16, bd + 4, idesc);
+          mma_f16_ts_more(tmem_base, a_t + 24, bd + 6, idesc);
           tc_commit(a_empty(as));
         }
         if (ok) tc_commit(d_full);

@@ -48,11 +48,12 @@ constexpr int kWtActStageBytes = kWtARows * 128;          // 32 KiB: 256 rows x 
 constexpr int kWtRawStages = 6;
 constexpr int kWtRawStageBytes = kWtWRows * 64;           // 8 KiB: 128 rows x 128 int4 = one scale group
 constexpr int kWtAStagesLog2 = 3;
-constexpr int kWtAStages = 1 << kWtAStagesLog2;                             // expanded-weight stages in tensor memory
+constexpr int kWtAStages = 1 << kWtAStagesLog2;
+constexpr int kWtPairStages = kWtAStages / 2;             // pairs of K blocks (128 K) in flight: one barrier pair each                             // expanded-weight stages in tensor memory
 constexpr int kWtAStageColumns = 32;                      // 64 K as f16 pairs
 constexpr int kWtOutRows = 64;                            // result rows per staged piece
 constexpr int kWtOutStageBytes = kWtOutRows * kWtWRows * 2;  // 16 KiB
-constexpr int kWtDequantGroups = 2;
+constexpr int kWtDequantGroups = 2;                       // = K blocks per pair: group g expands the pair's block g
 constexpr int kWtThreads = 256 + kWtDequantGroups * 128;
 constexpr int kWtMaxDestinations = 8;
 constexpr int kWtBarrierBytes = 512;
@@ -87,7 +88,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   uint8_t* bars_gen = smem_gen + (bars - smem_base);
   // barriers: act full (eight slots, four in use with 256-row tiles; an activation stage comes back through
   // the A-stage barrier of the K block that held it), raw full / empty, A-stage full / empty, accumulator full / empty
-  auto act_full = [&](int i) { return bars + 8u * i; };
+  auto act_early = [&](int i) { return bars + 8u * i; };  // "the first block of a pair is done with activation stage i"
   auto raw_full = [&](int i) { return bars + 8u * (2 * kWtActStages + i); };
   auto raw_empty = [&](int i) { return bars + 8u * (2 * kWtActStages + kWtRawStages + i); };
   auto a_full = [&](int i) { return bars + 8u * (2 * kWtActStages + 2 * kWtRawStages + i); };
@@ -115,6 +116,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
   // 128 rows finishes its MMAs in half the time, so it needs twice the stages in flight).
   const int act_stages = a_rows == 128 ? 2 * kWtActStages : kWtActStages;
   const uint32_t act_pitch = static_cast<uint32_t>(a_rows) * 128u;
+  const bool early_release = act_stages == kWtActStages;  // four stages: hand an activation stage back per block, not per pair
   const int tiles_m = (M + a_rows - 1) / a_rows;
   const int tiles_n = (N + kWtWRows - 1) / kWtWRows;
   const int num_tiles = tiles_m * tiles_n;
@@ -122,14 +124,14 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2 * kWtActStages; ++i) {  // 128-row tiles run eight half-size activation stages
-      mbar_init(act_full(i), 1);
+      mbar_init(act_early(i), 1);
     }
     for (int i = 0; i < kWtRawStages; ++i) {
       mbar_init(raw_full(i), 1);
       mbar_init(raw_empty(i), 8);  // a raw stage holds two K blocks: the four warps of each block's group
     }
-    for (int i = 0; i < kWtAStages; ++i) {
-      mbar_init(a_full(i), 5);     // the four warps of the group that expanded the K block + the activation tile's expect_tx
+    for (int i = 0; i < kWtPairStages; ++i) {
+      mbar_init(a_full(i), 9);     // the eight dequant warps (four per K block of the pair) + the activation tiles' expect_tx
       mbar_init(a_empty(i), 1);
     }
     mbar_init(d_full, 1);
@@ -160,33 +162,53 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
     // -------- TMA producer of the activation tiles ------------------------------------------------
     if (lane == 0) {
       tensormap_fence_acquire(ws->map_a);
+      const uint32_t act_mask = static_cast<uint32_t>(act_stages) - 1u, act_pairs = static_cast<uint32_t>(act_stages) >> 1;
+      const uint32_t act_shift = act_stages == 2 * kWtActStages ? kWtActStagesLog2 + 1 : kWtActStagesLog2;
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, tm, tn);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int st = it % act_stages;
-          // The stage's previous tenant was K block it - 4; its MMAs' completion is reported once, on
-          // the barrier that also hands the block's A stage back to the dequant warps (a commit
-          // costs the tensor pipe about as long as a small MMA, so there is one per block, not two).
-          const uint32_t prev = it - act_stages;
-          if (it >= static_cast<uint32_t>(act_stages) &&
-              !mbar_wait(a_empty(prev % kWtAStages), (prev / kWtAStages) & 1, abort_flag)) {
+        // Two K blocks (one scale group, 128 K) at a time: the pair shares one "full" and one "empty" barrier
+        // (slot pair % kWtPairStages of a_full / a_empty), so the issuing thread waits and commits once per
+        // eight MMAs. Its loop period, not the tensor pipe, is what bounds this kernel: a wait costs it ~125
+        // cycles even when the phase is long complete, a commit ~46, an MMA ~75. The activation tiles of the
+        // pair report to the pair's "full" barrier next to the dequant warps' arrivals.
+        for (int kb = 0; kb < num_kb; kb += 2, it += 2) {
+          const uint32_t pair = it >> 1;
+          // The two activation stages' previous tenants were the blocks of pair - act_pairs; their MMAs'
+          // completion is what the pair's "empty" barrier reports.
+          // With four stages (256-row tiles) a pair's lead would be one pair of MMAs, less than a load takes:
+          // there the issuing thread reports the first block's MMAs on a barrier of their own (act_early), so
+          // that each stage is refilled as soon as its block is done, four blocks ahead as before.
+          const uint32_t prev = pair - act_pairs;
+          const uint32_t full = a_full(pair % kWtPairStages);
+          bool waited = true;
+          if (pair >= act_pairs && early_release) {
+            const uint32_t prev_block = it - act_stages;
+            waited = mbar_wait(act_early(prev_block & act_mask), (prev_block >> act_shift) & 1, abort_flag);
+          } else if (pair >= act_pairs) {
+            waited = mbar_wait(a_empty(prev % kWtPairStages), (prev / kWtPairStages) & 1, abort_flag);
+          }
+          if (waited) {
+            mbar_arrive_expect_tx(full, 2 * a_rows * 128);
+            const uint32_t dst = smem_base + (it & act_mask) * act_pitch;
+            tma_load_3d(dst, ws->map_a, full, kb * 64, tm * a_rows, 0);
+            if (a_rows > 128) tma_load_3d(dst + 128 * 128, ws->map_a, full, kb * 64, tm * a_rows + 128, 0);
+            if (pair >= act_pairs && early_release)
+              waited = mbar_wait(a_empty(prev % kWtPairStages), (prev / kWtPairStages) & 1, abort_flag);
+          }
+          if (!waited) {
             wt_report(ws, kStatusTimeoutEmpty, it);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          // The activation tile reports to the barrier of the block's expanded-weight stage: the issuing
-          // thread then waits once per K block, for both operands (its loop period, not the tensor pipe, is
-          // what bounds this kernel: every barrier wait costs it ~125 cycles even when the phase is long
-          // complete). That barrier's previous phase, block it - 8, completed before block it - act_stages'
-          // MMAs, which this thread has just waited for.
-          const uint32_t full = a_full(it % kWtAStages);
-          mbar_arrive_expect_tx(full, a_rows * 128);
-          tma_load_3d(smem_base + st * act_pitch, ws->map_a, full, kb * 64, tm * a_rows, 0);
-          if (a_rows > 128) tma_load_3d(smem_base + st * act_pitch + 128 * 128, ws->map_a, full, kb * 64, tm * a_rows + 128, 0);
+          {
+            const uint32_t dst = smem_base + ((it + 1) & act_mask) * act_pitch;
+            tma_load_3d(dst, ws->map_a, full, (kb + 1) * 64, tm * a_rows, 0);
+            if (a_rows > 128) tma_load_3d(dst + 128 * 128, ws->map_a, full, (kb + 1) * 64, tm * a_rows + 128, 0);
+          }
         }
       }
     }
@@ -232,23 +254,27 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
           break;
         }
         tc_fence_after_sync();
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t st = it & act_mask, as = it & (kWtAStages - 1);
-          if (!mbar_wait(a_full(as), (it >> kWtAStagesLog2) & 1, abort_flag)) {  // expanded weights and activation tile
+        for (int kb = 0; kb < num_kb; kb += 2, it += 2) {
+          const uint32_t pair = it >> 1, ps = pair & (kWtPairStages - 1);
+          if (!mbar_wait(a_full(ps), (pair / kWtPairStages) & 1, abort_flag)) {  // both blocks' weights and activations
             wt_report(ws, kStatusTimeoutDequant, it);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint64_t bd = desc0 + st * stage_units;          // + 2 per 32 bytes of K
-          const uint32_t a_t = tmem_a + as * kWtAStageColumns;   // + 8 columns per 16 K
-          if (kb == 0) mma_f16_ts_first(tmem_base, a_t, bd, idesc);
-          else mma_f16_ts_more(tmem_base, a_t, bd, idesc);
-          mma_f16_ts_more(tmem_base, a_t + 8, bd + 2, idesc);
-          mma_f16_ts_more(tmem_base, a_t + 16, bd + 4, idesc);
-          mma_f16_ts_more(tmem_base, a_t + 24, bd + 6, idesc);
-          tc_commit(a_empty(as));
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint64_t bd = desc0 + ((it + h) & act_mask) * stage_units;                    // + 2 per 32 bytes of K
+            const uint32_t a_t = tmem_a + ((it + h) & (kWtAStages - 1)) * kWtAStageColumns;     // + 8 columns per 16 K
+            if (kb == 0 && h == 0) mma_f16_ts_first(tmem_base, a_t, bd, idesc);
+            else mma_f16_ts_more(tmem_base, a_t, bd, idesc);
+            mma_f16_ts_more(tmem_base, a_t + 8, bd + 2, idesc);
+            mma_f16_ts_more(tmem_base, a_t + 16, bd + 4, idesc);
+            mma_f16_ts_more(tmem_base, a_t + 24, bd + 6, idesc);
+            if (h == 0 && early_release) tc_commit(act_early(it & act_mask));
+          }
+          tc_commit(a_empty(ps));
         }
         if (ok) tc_commit(d_full);
       }
@@ -379,7 +405,8 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
           }
         }
         const int as = it % kWtAStages;
-        if (!__all_sync(0xffffffffu, mbar_wait(a_empty(as), ((it / kWtAStages) & 1) ^ 1, abort_flag))) {
+        const uint32_t pair = it >> 1, ps = pair % kWtPairStages;  // the pair this block belongs to (block = 2 * pair + grp)
+        if (!__all_sync(0xffffffffu, mbar_wait(a_empty(ps), ((pair / kWtPairStages) & 1) ^ 1, abort_flag))) {
           if (lane == 0) {
             wt_report(ws, kStatusTimeoutEmpty, 0x20000u | it);
             *abort_flag = 1;
@@ -410,7 +437,7 @@ __device__ __forceinline__ void wt_body(const __half* __restrict__ scales, WtWor
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(a_full(as));
+          mbar_arrive(a_full(ps));
           mbar_arrive(raw_empty(rs));
         }
       }

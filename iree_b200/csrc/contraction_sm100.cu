@@ -31,10 +31,10 @@ constexpr int kStageBytes = kAStageBytes + kBStageBytes;
 // Few-row variant (M <= 32 and tiles at most 128 wide): such a product only streams B, so the bound
 // is HBM and what matters is bytes in flight. The A box shrinks to 32 rows (4 KiB; the tensor
 // core still reads 128 rows of shared memory, the rest is whatever follows in the ring and lands
-// in accumulator rows nobody reads) and the ring grows to nine stages of 20 KiB.
+// in accumulator rows nobody reads) and the ring grows to ten stages of 20 KiB (no epilogue staging).
 constexpr int kFewRows = 32;
 constexpr int kFewRowsMaxBN = 128;
-constexpr int kFewRowsStages = 9;
+constexpr int kFewRowsStages = 10;   // five pairs: the few-rows variant hands K blocks over two at a time
 __host__ __device__ constexpr bool few_rows_variant(int M, int bn) { return M <= kFewRows && bn <= kFewRowsMaxBN; }
 constexpr int kThreads = 256;
 constexpr int kTmemColumns = 512;
@@ -217,7 +217,14 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   constexpr int kStages = FEW_ROWS ? kFewRowsStages : b200::kStages;
   constexpr int kAStageBytes = (FEW_ROWS ? kFewRows : kBM) * kRowBytes;
   constexpr int kStageBytes = kAStageBytes + (FEW_ROWS ? kFewRowsMaxBN : kMaxBN) * kRowBytes;
-  static_assert(1024 + kStages * kStageBytes + kOutStageBytes + 256 <= kGemmSmemBytes, "ring exceeds the export's shared memory");
+  // K blocks per hand-over between producer, issuing thread and back: the issuing thread's loop period (a
+  // barrier wait ~125 cycles, a commit ~46, an MMA ~75) must stay below the MMAs' time; a 128-wide tile's
+  // four MMAs take 256 cycles, so the few-rows variant waits and commits once per two blocks.
+  constexpr int kGroup = FEW_ROWS ? 2 : 1;
+  constexpr int kGroupStages = kStages / kGroup;
+  static_assert(kStages % kGroup == 0, "whole groups");
+  constexpr int kOutStageBytesHere = FEW_ROWS ? 0 : kOutStageBytes;  // the few-rows variant stores from registers
+  static_assert(1024 + kStages * kStageBytes + kOutStageBytesHere + 256 <= kGemmSmemBytes, "ring exceeds the export's shared memory");
   static_assert(!FEW_ROWS || (kStages - 1) * kStageBytes + kBM * kRowBytes <= kStages * kStageBytes,
                 "the 128-row operand read of the last stage must stay inside the ring");
   using T = KindTraits<KIND>;
@@ -230,7 +237,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   __shared__ alignas(128) uint8_t out_map_stage[128];  // where the result's tensor map is assembled
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t out_stage = smem_base + kStages * kStageBytes;  // epilogue staging (many-rows variant only)
-  const uint32_t bars = out_stage + kOutStageBytes;
+  const uint32_t bars = out_stage + kOutStageBytesHere;
   // barrier slots (8 bytes each): full[0..3], empty[4..7], tmem_full[8..9], tmem_empty[10..11]
   auto full_bar = [&](int i) { return bars + 8u * i; };
   auto empty_bar = [&](int i) { return bars + 8u * (kStages + i); };
@@ -239,12 +246,12 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
   const uint32_t tmem_slot = bars + 8u * (2 * kStages + 4);
   uint8_t* smem_generic = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* abort_flag =
-      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytes + 8 * (2 * kStages + 4) + 4);
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytesHere + 8 * (2 * kStages + 4) + 4);
   // Written by the epilogue warps only, before the barrier at which all four read it: they leave together.
   volatile uint32_t* epilogue_abort =
-      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytes + 8 * (2 * kStages + 4) + 8);
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytesHere + 8 * (2 * kStages + 4) + 8);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytes + 8 * (2 * kStages + 4));
+      reinterpret_cast<volatile uint32_t*>(smem_generic + kStages * kStageBytes + kOutStageBytesHere + 8 * (2 * kStages + 4));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -324,26 +331,29 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
         int t, kb0, kb1, b, tm, tn;
         item_coords(w, t, kb0, kb1);
         tile_coords(t, b, tm, tn);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int st = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(empty_bar(st), ph ^ 1, abort_flag)) {
+        for (int kb = kb0; kb < kb1; kb += kGroup, ++it) {   // `it` counts hand-overs (groups of kGroup K blocks)
+          const int gs = it % kGroupStages;
+          const uint32_t ph = (it / kGroupStages) & 1;
+          if (!mbar_wait(empty_bar(gs), ph ^ 1, abort_flag)) {
             report(ws, kStatusTimeoutEmpty, it);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          const uint32_t a_dst = smem_base + st * kStageBytes;
-          const uint32_t b_dst = a_dst + kAStageBytes;
-          mbar_arrive_expect_tx(full_bar(st), stage_tx);
-          tma_load_3d(a_dst, ws->map_a, full_bar(st), kb * kBK, tm * kBM, b);  // box rows: kBM, or kFewRows
-          if (s.b_layout == kBLayoutNK) {
-            tma_load_3d(b_dst, ws->map_b, full_bar(st), kb * kBK, tn * s.bn, b);
-          } else {
-            // [K,N] tile: one box of (kChunkN columns x kBK rows) per 128-byte column chunk.
-            for (int c = 0; c < s.bn / kChunkN; ++c)
-              tma_load_3d(b_dst + c * (kBK * kRowBytes), ws->map_b, full_bar(st), tn * s.bn + c * kChunkN, kb * kBK,
-                          b);
+          const int blocks = kb1 - kb < kGroup ? kb1 - kb : kGroup;   // an item's last group may be short
+          mbar_arrive_expect_tx(full_bar(gs), blocks * stage_tx);
+          for (int j = 0; j < blocks; ++j) {
+            const uint32_t a_dst = smem_base + (gs * kGroup + j) * kStageBytes;
+            const uint32_t b_dst = a_dst + kAStageBytes;
+            tma_load_3d(a_dst, ws->map_a, full_bar(gs), (kb + j) * kBK, tm * kBM, b);  // box rows: kBM, or kFewRows
+            if (s.b_layout == kBLayoutNK) {
+              tma_load_3d(b_dst, ws->map_b, full_bar(gs), (kb + j) * kBK, tn * s.bn, b);
+            } else {
+              // [K,N] tile: one box of (kChunkN columns x kBK rows) per 128-byte column chunk.
+              for (int c = 0; c < s.bn / kChunkN; ++c)
+                tma_load_3d(b_dst + c * (kBK * kRowBytes), ws->map_b, full_bar(gs), tn * s.bn + c * kChunkN,
+                            (kb + j) * kBK, b);
+            }
           }
         }
       }
@@ -380,7 +390,7 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kMaxBN;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; kb += kGroup, ++it) {
           if (!mbar_wait(full_bar(st), ph, abort_flag)) {
             report(ws, kStatusTimeoutFull, it);
             *abort_flag = 1;
@@ -388,22 +398,28 @@ __device__ __forceinline__ void gemm_body(void* __restrict__ c_ptr, const float*
             break;
           }
           tc_fence_after_sync();
-          const uint64_t a_desc = a_desc0 + st * kStageUnits, b_desc = b_desc0 + st * kStageUnits;
-          if constexpr (KIND == kI8) {
-            mma_i8_ss(d_tmem, a_desc, b_desc, idesc, kb > kb0 ? 1u : 0u);
-          } else {
-            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, kb > kb0 ? 1u : 0u);
-          }
+          const int blocks = kb1 - kb < kGroup ? kb1 - kb : kGroup;
 #pragma unroll
-          for (int k = 1; k < kBK / kUmmaK; ++k) {
-            if constexpr (KIND == kI8) {
-              mma_i8_ss_more(d_tmem, a_desc + 2 * k, b_desc + b_step * k, idesc);
-            } else {
-              mma_f16_ss_more(d_tmem, a_desc + 2 * k, b_desc + b_step * k, idesc);
+          for (int j = 0; j < kGroup; ++j) {
+            if (j < blocks) {
+              const uint64_t a_desc = a_desc0 + (st * kGroup + j) * kStageUnits, b_desc = b_desc0 + (st * kGroup + j) * kStageUnits;
+              if constexpr (KIND == kI8) {
+                mma_i8_ss(d_tmem, a_desc, b_desc, idesc, (kb + j) > kb0 ? 1u : 0u);
+              } else {
+                mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb + j) > kb0 ? 1u : 0u);
+              }
+#pragma unroll
+              for (int k = 1; k < kBK / kUmmaK; ++k) {
+                if constexpr (KIND == kI8) {
+                  mma_i8_ss_more(d_tmem, a_desc + 2 * k, b_desc + b_step * k, idesc);
+                } else {
+                  mma_f16_ss_more(d_tmem, a_desc + 2 * k, b_desc + b_step * k, idesc);
+                }
+              }
             }
           }
-          tc_commit(empty_bar(st));  // the stage is free once these MMAs have read it
-          if (++st == kStages) {
+          tc_commit(empty_bar(st));  // the group's stages are free once these MMAs have read them
+          if (++st == kGroupStages) {
             st = 0;
             ph ^= 1;
           }

@@ -102,6 +102,7 @@ struct CudaSymbols {
   CU_FN(cuMemsetD32Async, CUdeviceptr, unsigned int, size_t, CUstream)
   CU_FN(cuGraphAddMemcpyNode, CUgraphNode*, CUgraph, const CUgraphNode*, size_t, const CUDA_MEMCPY3D*, CUcontext)
   CU_FN(cuGraphAddMemsetNode, CUgraphNode*, CUgraph, const CUgraphNode*, size_t, const CUDA_MEMSET_NODE_PARAMS*, CUcontext)
+  CU_FN(cuMemcpy2DAsync, const CUDA_MEMCPY2D*, CUstream)
   CU_FN(cuGetErrorName, CUresult, const char**)
   CU_FN(cuGetErrorString, CUresult, const char**)
   CU_FN(cuTensorMapEncodeTiled, CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -182,6 +183,7 @@ iree_b200_status_t ensure_cuda() {
       load_sym(g_cu.handle, "cuMemsetD32Async", g_cu.cuMemsetD32Async);
       load_sym(g_cu.handle, "cuGraphAddMemcpyNode", g_cu.cuGraphAddMemcpyNode);
       load_sym(g_cu.handle, "cuGraphAddMemsetNode", g_cu.cuGraphAddMemsetNode);
+      load_sym(g_cu.handle, "cuMemcpy2DAsync_v2", g_cu.cuMemcpy2DAsync);
       if (!ok) {
         g_cu.error = "CUDA driver library is missing required symbols";
         g_cu.handle = nullptr;
@@ -439,6 +441,8 @@ struct iree_hal_b200_device_t {
   // host-buffer entry points (created on first use).
   CUstream readback_stream = nullptr;
   CUevent readback_ready = nullptr;
+  CUstream upload_stream = nullptr;  // host -> device copies that run beside the dispatch stream's kernels
+  CUevent upload_ready = nullptr;
   int sm_count = 0, cc = 0, max_smem = 0;
   char name[128] = {0};
 };
@@ -583,6 +587,11 @@ void iree_hal_b200_device_release(iree_hal_b200_device_t* device) {
     g_cu.cuStreamSynchronize(device->readback_stream);
     g_cu.cuStreamDestroy(device->readback_stream);
     g_cu.cuEventDestroy(device->readback_ready);
+  }
+  if (device->upload_stream) {
+    g_cu.cuStreamSynchronize(device->upload_stream);
+    g_cu.cuStreamDestroy(device->upload_stream);
+    g_cu.cuEventDestroy(device->upload_ready);
   }
   if (device->stream) {
     g_cu.cuStreamSynchronize(device->stream);
@@ -2541,15 +2550,14 @@ static iree_b200_status_t encode_output_map(const void* device_ptr, uint32_t col
 // Workspace of b200_w4a16_gemm_wt: operand maps, zeroed status words, one output map per destination and
 // (several ranks) the pointers to every rank's arrival words. 512 + 1024 + 64 bytes.
 constexpr size_t kWtWorkspaceBytes = 512 + kWtMaxDestinations * 128 + kWtMaxDestinations * 8;
-static iree_b200_status_t w4_prepare_wt(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
-                                        const void* a, const void* wq, void* const* results, void* const* flags,
-                                        int32_t world, void* workspace) {
+static iree_b200_status_t w4_encode_wt(const iree_b200_w4a16_params_t* params, const void* a, const void* wq,
+                                       void* const* results, void* const* flags, int32_t world,
+                                       uint8_t host[kWtWorkspaceBytes]) {
   if (world < 1 || world > kWtMaxDestinations)
     return fail(IREE_B200_STATUS_OUT_OF_RANGE, "1 to %d destinations", kWtMaxDestinations);
   if (params->n_offset % 8)
     return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "n_offset must be a multiple of 8 (TMA stores start on 16-byte boundaries)");
-  uint8_t host[kWtWorkspaceBytes];
-  memset(host, 0, sizeof host);
+  memset(host, 0, kWtWorkspaceBytes);
   B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, 128, a, params->K,
                                   params->M, 1, 64, 128, host));
   B200_RETURN_IF_ERROR(encode_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, CU_TENSOR_MAP_SWIZZLE_64B, 64, wq, params->K / 2,
@@ -2565,6 +2573,13 @@ static iree_b200_status_t w4_prepare_wt(iree_b200_context_t* context, const iree
       memcpy(host + 512 + kWtMaxDestinations * 128 + 8 * p, &f, 8);
     }
   }
+  return IREE_B200_STATUS_OK;
+}
+static iree_b200_status_t w4_prepare_wt(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                        const void* a, const void* wq, void* const* results, void* const* flags,
+                                        int32_t world, void* workspace) {
+  uint8_t host[kWtWorkspaceBytes];
+  B200_RETURN_IF_ERROR(w4_encode_wt(params, a, wq, results, flags, world, host));
   return iree_hal_b200_transfer_h2d(context->device, host, workspace, sizeof host);
 }
 
@@ -2796,6 +2811,138 @@ iree_b200_status_t iree_b200_w4a16(iree_b200_context_t* context, const iree_b200
   return iree_b200_w4a16_run(context, params, a, wq, scales, out, workspace, variant, tile_n);
 }
 
+// A many-rows product whose operands and result are tens of megabytes spends its time on the bus. It is
+// cut into units that follow the operands' arrival: blocks of activation rows and blocks of weight rows go
+// up in turn (by bytes), and every new block is multiplied at once with all the blocks of the other operand
+// that are on the device - a rectangle of the result per unit - so results start to leave after a few
+// percent of the operands have arrived and the rectangles grow as fast as the link allows. Uploads run on a
+// stream of their own, each unit's dispatch waits for its upload, and its rectangle returns by a pitched
+// copy on the readback stream: both directions of the link are busy for most of the call. (Letting the
+// kernel's TMA stores write page-locked host memory directly was measured too: 42-48 GB/s against the copy
+// engine's 55, and it slowed the uploads.)
+constexpr int kHostMaxColBlocks = 16, kHostMaxRowBlocks = 8, kHostMaxUnits = kHostMaxColBlocks + kHostMaxRowBlocks;
+constexpr size_t kHostUnitWorkspace = (kWtWorkspaceBytes + 255) & ~static_cast<size_t>(255);
+static bool w4_host_in_units(const iree_b200_w4a16_params_t* p, size_t w_bytes, size_t c_bytes) {
+  return g_cu.cuMemcpy2DAsync && p->variant == IREE_B200_W4A16_AUTO && p->group_size == 128 && p->K % 128 == 0 &&
+         p->M >= 256 && p->N >= 2048 && p->ldo == p->N && p->n_offset == 0 && w_bytes + c_bytes >= (static_cast<size_t>(32) << 20);
+}
+static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                        const uint8_t* a, const uint8_t* wq, const uint8_t* scales, uint8_t* out,
+                                        uint8_t* ws, uint8_t* da, uint8_t* dw, uint8_t* ds, uint8_t* dc) {
+  if (!a || !wq || !scales || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
+  auto* d = context->device;
+  if (!d->readback_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->readback_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->readback_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  if (!d->upload_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->upload_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->upload_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  const int64_t M = params->M, N = params->N, K = params->K;
+  int col_blocks = static_cast<int>(N / 1024 < kHostMaxColBlocks ? N / 1024 : kHostMaxColBlocks);
+  const int64_t block_cols = ((N + col_blocks - 1) / col_blocks + 255) / 256 * 256;
+  col_blocks = static_cast<int>((N + block_cols - 1) / block_cols);
+  int row_blocks = static_cast<int>(M / 512 < kHostMaxRowBlocks ? M / 512 : kHostMaxRowBlocks);
+  if (row_blocks < 1) row_blocks = 1;
+  const int64_t block_rows = ((M + row_blocks - 1) / row_blocks + 255) / 256 * 256;
+  row_blocks = static_cast<int>((M + block_rows - 1) / block_rows);
+  const size_t w_pitch = static_cast<size_t>(K / 2), s_pitch = static_cast<size_t>(K / 128) * 2, a_pitch = static_cast<size_t>(K) * 2;
+  // A unit: the rectangle [row0, row0 + rows) x [col0, col0 + cols) of the result, after the upload of one
+  // block of weight rows (new_cols), of activation rows (new_rows), or - the first - of both.
+  struct Unit {
+    int64_t row0, rows, col0, cols;
+    bool new_rows, new_cols;
+  } units[kHostMaxUnits];
+  int count = 0, rows_up = 1, cols_up = 1;
+  auto rows_to = [&](int blocks) { return blocks * block_rows < M ? blocks * block_rows : M; };
+  auto cols_to = [&](int blocks) { return blocks * block_cols < N ? blocks * block_cols : N; };
+  units[count++] = {0, rows_to(1), 0, cols_to(1), true, true};
+  while (rows_up < row_blocks || cols_up < col_blocks) {
+    const bool weights_next = cols_up < col_blocks && (rows_up == row_blocks || cols_to(cols_up) * (w_pitch + s_pitch) <= rows_to(rows_up) * a_pitch);
+    if (weights_next) {
+      units[count++] = {0, rows_to(rows_up), cols_to(cols_up), cols_to(cols_up + 1) - cols_to(cols_up), false, true};
+      ++cols_up;
+    } else {
+      units[count++] = {rows_to(rows_up), rows_to(rows_up + 1) - rows_to(rows_up), 0, cols_to(cols_up), true, false};
+      ++rows_up;
+    }
+  }
+  // every unit's header (operand and result maps) is encoded first and uploaded in one copy
+  std::vector<uint8_t> headers(static_cast<size_t>(count) * kHostUnitWorkspace, 0);
+  iree_b200_w4a16_params_t up[kHostMaxUnits];
+  for (int u = 0; u < count; ++u) {
+    up[u] = *params;
+    up[u].variant = IREE_B200_W4A16_GEMM_WT;
+    up[u].M = static_cast<int32_t>(units[u].rows);
+    up[u].N = static_cast<int32_t>(units[u].cols);
+    up[u].n_offset = static_cast<int32_t>(units[u].col0);
+    void* results[1] = {dc + static_cast<size_t>(units[u].row0) * N * 2};
+    B200_RETURN_IF_ERROR(w4_encode_wt(&up[u], da + static_cast<size_t>(units[u].row0) * a_pitch,
+                                      dw + static_cast<size_t>(units[u].col0) * w_pitch, results, nullptr, 1,
+                                      headers.data() + static_cast<size_t>(u) * kHostUnitWorkspace));
+  }
+  B200_RETURN_IF_ERROR(iree_hal_b200_transfer_h2d(d, headers.data(), ws, headers.size()));
+  // uploads start after whatever the dispatch stream still runs on the arena
+  CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->upload_ready, d->stream), "cuEventRecord");
+  CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->upload_stream, d->upload_ready, 0), "cuStreamWaitEvent");
+  auto upload = [&](const uint8_t* src, uint8_t* dst, size_t bytes) -> iree_b200_status_t {
+    CU_RETURN_IF_ERROR(g_cu.cuMemcpyHtoDAsync(reinterpret_cast<CUdeviceptr>(dst), src, bytes, d->upload_stream),
+                       "cuMemcpyHtoDAsync");
+    return IREE_B200_STATUS_OK;
+  };
+  for (int u = 0; u < count; ++u) {
+    const Unit& t = units[u];
+    if (t.new_cols) {  // a block of weight rows with its scales
+      B200_RETURN_IF_ERROR(upload(wq + static_cast<size_t>(t.col0) * w_pitch, dw + static_cast<size_t>(t.col0) * w_pitch,
+                                  static_cast<size_t>(t.cols) * w_pitch));
+      B200_RETURN_IF_ERROR(upload(scales + static_cast<size_t>(t.col0) * s_pitch, ds + static_cast<size_t>(t.col0) * s_pitch,
+                                  static_cast<size_t>(t.cols) * s_pitch));
+    }
+    if (t.new_rows)  // a block of activation rows
+      B200_RETURN_IF_ERROR(upload(a + static_cast<size_t>(t.row0) * a_pitch, da + static_cast<size_t>(t.row0) * a_pitch,
+                                  static_cast<size_t>(t.rows) * a_pitch));
+    CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->upload_ready, d->upload_stream), "cuEventRecord");
+    CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->stream, d->upload_ready, 0), "cuStreamWaitEvent");
+    uint8_t* unit_out = dc + static_cast<size_t>(t.row0) * N * 2;
+    B200_RETURN_IF_ERROR(w4_run_wt(context, &up[u], ds + static_cast<size_t>(t.col0) * s_pitch, unit_out,
+                                   ws + static_cast<size_t>(u) * kHostUnitWorkspace, 1, 0, 0));
+    CU_RETURN_IF_ERROR(g_cu.cuEventRecord(d->readback_ready, d->stream), "cuEventRecord");
+    CU_RETURN_IF_ERROR(g_cu.cuStreamWaitEvent(d->readback_stream, d->readback_ready, 0), "cuStreamWaitEvent");
+    CUDA_MEMCPY2D copy;
+    memset(&copy, 0, sizeof copy);
+    copy.srcMemoryType = CU_MEMORYTYPE_DEVICE;
+    copy.srcDevice = reinterpret_cast<CUdeviceptr>(unit_out + static_cast<size_t>(t.col0) * 2);
+    copy.srcPitch = static_cast<size_t>(N) * 2;
+    copy.dstMemoryType = CU_MEMORYTYPE_HOST;
+    copy.dstHost = out + (static_cast<size_t>(t.row0) * N + static_cast<size_t>(t.col0)) * 2;
+    copy.dstPitch = static_cast<size_t>(N) * 2;
+    copy.WidthInBytes = static_cast<size_t>(t.cols) * 2;
+    copy.Height = static_cast<size_t>(t.rows);
+    CU_RETURN_IF_ERROR(g_cu.cuMemcpy2DAsync(&copy, d->readback_stream), "cuMemcpy2DAsync");
+  }
+  // one read of every unit's status words, then wait for the dispatch and readback streams
+  uint32_t status[kHostMaxUnits][2];
+  CUDA_MEMCPY2D words;
+  memset(&words, 0, sizeof words);
+  words.srcMemoryType = CU_MEMORYTYPE_DEVICE;
+  words.srcDevice = reinterpret_cast<CUdeviceptr>(ws + 384);
+  words.srcPitch = kHostUnitWorkspace;
+  words.dstMemoryType = CU_MEMORYTYPE_HOST;
+  words.dstHost = status;
+  words.dstPitch = sizeof status[0];
+  words.WidthInBytes = sizeof status[0];
+  words.Height = static_cast<size_t>(count);
+  CU_RETURN_IF_ERROR(g_cu.cuMemcpy2DAsync(&words, d->stream), "cuMemcpy2DAsync");
+  B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
+  CU_RETURN_IF_ERROR(g_cu.cuStreamSynchronize(d->readback_stream), "cuStreamSynchronize");
+  for (int u = 0; u < count; ++u) {
+    if (status[u][0] == 5) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "kernel rejected its arguments (shape / alignment)");
+    if (status[u][0]) return fail(IREE_B200_STATUS_DEADLINE_EXCEEDED, "kernel wait %u ran out at iteration %u", status[u][0], status[u][1]);
+  }
+  return IREE_B200_STATUS_OK;
+}
+
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out) {
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
@@ -2807,7 +2954,8 @@ iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree
   if (!params->M || !params->N) return IREE_B200_STATUS_OK;
   auto* d = context->device;
   auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
-  const size_t ws_bytes = iree_b200_w4a16_workspace_bytes(params->N);
+  const bool in_units = w4_host_in_units(params, w_bytes, c_bytes);
+  const size_t ws_bytes = in_units ? kHostMaxUnits * kHostUnitWorkspace : iree_b200_w4a16_workspace_bytes(params->N);
   const size_t need = up(ws_bytes) + up(a_bytes) + up(w_bytes) + up(s_bytes) + up(c_bytes);
   if (need > context->arena_size) {
     B200_RETURN_IF_ERROR(iree_hal_b200_device_synchronize(d));
@@ -2823,6 +2971,10 @@ iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree
   void* dw = static_cast<uint8_t*>(da) + up(a_bytes);
   void* ds = static_cast<uint8_t*>(dw) + up(w_bytes);
   void* dc = static_cast<uint8_t*>(ds) + up(s_bytes);
+  if (in_units)
+    return w4_host_units(context, params, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(wq),
+                         static_cast<const uint8_t*>(scales), static_cast<uint8_t*>(out), base, static_cast<uint8_t*>(da),
+                         static_cast<uint8_t*>(dw), static_cast<uint8_t*>(ds), static_cast<uint8_t*>(dc));
   // The decode scratch (K > 4096) must start at zero; the kernel leaves it zero afterwards, but the arena
   // is shared with other entry points, so it is cleared on every call here (a few hundred KiB).
   B200_RETURN_IF_ERROR(iree_hal_b200_fill_buffer(d, ws, ws_bytes, 0));

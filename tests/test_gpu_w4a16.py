@@ -180,6 +180,30 @@ def test_c4_w4a16(ctx, M):
         np.testing.assert_allclose(got[rows].astype(np.float32), want.astype(np.float32), rtol=RTOL, atol=ATOL)
 
 
+def test_host_call_in_units_equals_the_single_dispatch(ctx):
+    """A many-rows product of tens of megabytes goes through the host-buffer call as units (growing
+    rectangles of the result, computed as blocks of activation rows and of weight rows arrive), uploads and
+    dispatches overlapping, the rectangles returning by pitched copies into a pageable or a page-locked
+    result. Ragged row and column blocks; either way the result must equal, bit for bit, what the one
+    dispatch of the same kernel leaves, and the oracle on a sample."""
+    rng = np.random.default_rng(77)
+    M, N, K = 1100, 4400, 12288
+    a, wq, s = exact_case(rng, M, N, K)
+    one = w4a16_numpy(ctx, a, wq, s, variant=ib.W4A16_GEMM_WT)           # explicit variant: one dispatch
+    rows, cols = np.arange(0, M, 97), np.arange(0, N, 53)
+    assert (one[np.ix_(rows, cols)] == oracle.w4a16(a[rows], wq[cols], s[cols], threads=THREADS)).all()
+    pageable = np.full((M, N), 7.0, np.float16)
+    w4a16_numpy(ctx, a, wq, s, out=pageable)                             # AUTO: in units
+    assert (pageable == one).all(), np.argwhere(pageable != one)[:4]
+    locked = ctx.pinned_empty((M, N), np.float16)
+    try:
+        locked[...] = 7.0
+        w4a16_numpy(ctx, a, wq, s, out=locked)
+        assert (locked == one).all(), np.argwhere(locked != one)[:4]
+    finally:
+        ib.runtime.library().iree_hal_b200_host_free(ctx.device, ib.runtime._vp(locked))
+
+
 @pytest.mark.parametrize("M", [16, 4096])
 def test_c5_w4a16_70b_shape(ctx, M):
     a, wq, s = workloads.c5_w4a16_sharded(M)

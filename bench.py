@@ -59,15 +59,48 @@ from bench_workloads import (DEFAULT_WORKLOAD, algorithmic, describe, local_n, m
 
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML in this process
+    (a thread polling every 2 ms, plus one sample taken by the timing code itself right after the launch),
+    or, where NVML cannot be loaded, with an nvidia-smi child at 50 ms. Read-only queries."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # bits of nvmlDeviceGetCurrentClocksEventReasons, in the order of the four names of summary()
+    REASON_BITS = (0x8, 0x40, 0x20, 0x4)
 
     def __init__(self, index):
-        self.index, self.lines, self.proc = index, [], None
+        self.index, self.lines, self.proc, self.nvml, self.handle = index, [], None, None, None
+        self.stop = threading.Event()
+
+    def _nvml_line(self):
+        n, h = self.nvml, self.handle
+        sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = int(get(h))
+        flags = ["Active" if bits & b else "Not Active" for b in self.REASON_BITS]
+        return ",".join([str(self.index), str(sm), str(mx), "", hex(bits)] + flags)
+
+    def sample_now(self):
+        """One sample taken by the caller's thread (so that even a region of a few milliseconds has one)."""
+        if self.nvml is not None:
+            try:
+                self.lines.append((time.time(), self._nvml_line()))
+            except Exception:
+                pass
 
     def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml = pynvml
+            self._nvml_line()
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
                                           "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
@@ -78,11 +111,22 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def _poll(self):
+        while not self.stop.is_set():
+            try:
+                self.lines.append((time.time(), self._nvml_line()))
+            except Exception:
+                return
+            self.stop.wait(0.002)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
     def __exit__(self, *exc):
+        self.stop.set()
+        if self.nvml is not None:
+            self.thread.join(timeout=1)
         if self.proc:
             self.proc.terminate()
             try:
@@ -354,6 +398,7 @@ def measure(ctx, wl, rank, world, local, channel, steps, warmup, verify, peaks, 
         if channel is not None:
             rt.check(lib.iree_hal_b200_command_buffer_join_collectives(ctx.command_buffer))
         e1 = ctx.event().record()
+        clocks.sample_now()      # the steps are in flight: submission returns before they finish
         ms = e0.elapsed_ms(e1)
         ctx.synchronize()
         t_end = time.time()

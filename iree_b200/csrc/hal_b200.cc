@@ -2824,7 +2824,8 @@ constexpr int kHostMaxColBlocks = 16, kHostMaxRowBlocks = 8, kHostMaxUnits = kHo
 constexpr size_t kHostUnitWorkspace = (kWtWorkspaceBytes + 255) & ~static_cast<size_t>(255);
 static bool w4_host_in_units(const iree_b200_w4a16_params_t* p, size_t w_bytes, size_t c_bytes) {
   return g_cu.cuMemcpy2DAsync && p->variant == IREE_B200_W4A16_AUTO && p->group_size == 128 && p->K % 128 == 0 &&
-         p->M >= 256 && p->N >= 2048 && p->ldo == p->N && p->n_offset == 0 && w_bytes + c_bytes >= (static_cast<size_t>(32) << 20);
+         p->M >= 256 && p->N >= 2048 && p->N % 8 == 0 && p->ldo == p->N && p->n_offset == 0 &&
+         w_bytes + c_bytes >= (static_cast<size_t>(32) << 20);  // N % 8: the result rows are TMA-stored (16-byte pitch)
 }
 static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const uint8_t* a, const uint8_t* wq, const uint8_t* scales, uint8_t* out,

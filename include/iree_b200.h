@@ -559,6 +559,11 @@ iree_b200_status_t iree_b200_w4a16_wait_arrivals(iree_b200_context_t* context, c
  * dispatch's. Page-locked host buffers (iree_hal_b200_host_allocate) make the copies asynchronous. */
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out);
+/* The dispatches iree_b200_w4a16_host cuts `params` into (needs no device): writes up to `capacity` records
+ * {row0, rows, col0, cols, uploads_rows, uploads_cols} - the rectangle of the result a dispatch computes and
+ * which operand block goes up before it - and returns their number; 0 when the product runs as one dispatch,
+ * -1 for invalid params. No counterpart in the reference (its HAL leaves transfers to the program). */
+int32_t iree_b200_w4a16_host_plan(const iree_b200_w4a16_params_t* params, int32_t* out_units, int32_t capacity);
 
 /* ---- sequences of dispatches ----------------------------------------------------------------------
  * `count` dispatches over rotating operand sets issued by one call, i.e. what the reference does

@@ -2823,25 +2823,22 @@ iree_b200_status_t iree_b200_w4a16(iree_b200_context_t* context, const iree_b200
 constexpr int kHostMaxColBlocks = 16, kHostMaxRowBlocks = 8, kHostMaxUnits = kHostMaxColBlocks + kHostMaxRowBlocks;
 constexpr size_t kHostUnitWorkspace = (kWtWorkspaceBytes + 255) & ~static_cast<size_t>(255);
 static bool w4_host_in_units(const iree_b200_w4a16_params_t* p, size_t w_bytes, size_t c_bytes) {
-  return g_cu.cuMemcpy2DAsync && p->variant == IREE_B200_W4A16_AUTO && p->group_size == 128 && p->K % 128 == 0 &&
+  return p->variant == IREE_B200_W4A16_AUTO && p->group_size == 128 && p->K % 128 == 0 &&
          p->M >= 256 && p->N >= 2048 && p->N % 8 == 0 && p->ldo == p->N && p->n_offset == 0 &&
          w_bytes + c_bytes >= (static_cast<size_t>(32) << 20);  // N % 8: the result rows are TMA-stored (16-byte pitch)
 }
-static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
-                                        const uint8_t* a, const uint8_t* wq, const uint8_t* scales, uint8_t* out,
-                                        uint8_t* ws, uint8_t* da, uint8_t* dw, uint8_t* ds, uint8_t* dc) {
-  if (!a || !wq || !scales || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
-  auto* d = context->device;
-  if (!d->readback_stream) {
-    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->readback_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
-    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->readback_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
-  }
-  if (!d->upload_stream) {
-    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->upload_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
-    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->upload_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
-  }
+// A unit: the rectangle [row0, row0 + rows) x [col0, col0 + cols) of the result, computed after the upload
+// of one block of weight rows (new_cols), of activation rows (new_rows), or - the first - of both.
+struct HostUnit {
+  int64_t row0, rows, col0, cols;
+  bool new_rows, new_cols;
+};
+// At most 8 blocks of activation rows (multiples of 256 rows) and 16 of weight rows (multiples of 256);
+// the operand that has fewer bytes on the device so far gets the next block.
+static int w4_plan_units(const iree_b200_w4a16_params_t* params, HostUnit* units) {
   const int64_t M = params->M, N = params->N, K = params->K;
   int col_blocks = static_cast<int>(N / 1024 < kHostMaxColBlocks ? N / 1024 : kHostMaxColBlocks);
+  if (col_blocks < 1) col_blocks = 1;
   const int64_t block_cols = ((N + col_blocks - 1) / col_blocks + 255) / 256 * 256;
   col_blocks = static_cast<int>((N + block_cols - 1) / block_cols);
   int row_blocks = static_cast<int>(M / 512 < kHostMaxRowBlocks ? M / 512 : kHostMaxRowBlocks);
@@ -2849,12 +2846,6 @@ static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree
   const int64_t block_rows = ((M + row_blocks - 1) / row_blocks + 255) / 256 * 256;
   row_blocks = static_cast<int>((M + block_rows - 1) / block_rows);
   const size_t w_pitch = static_cast<size_t>(K / 2), s_pitch = static_cast<size_t>(K / 128) * 2, a_pitch = static_cast<size_t>(K) * 2;
-  // A unit: the rectangle [row0, row0 + rows) x [col0, col0 + cols) of the result, after the upload of one
-  // block of weight rows (new_cols), of activation rows (new_rows), or - the first - of both.
-  struct Unit {
-    int64_t row0, rows, col0, cols;
-    bool new_rows, new_cols;
-  } units[kHostMaxUnits];
   int count = 0, rows_up = 1, cols_up = 1;
   auto rows_to = [&](int blocks) { return blocks * block_rows < M ? blocks * block_rows : M; };
   auto cols_to = [&](int blocks) { return blocks * block_cols < N ? blocks * block_cols : N; };
@@ -2869,6 +2860,25 @@ static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree
       ++rows_up;
     }
   }
+  return count;
+}
+static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
+                                        const uint8_t* a, const uint8_t* wq, const uint8_t* scales, uint8_t* out,
+                                        uint8_t* ws, uint8_t* da, uint8_t* dw, uint8_t* ds, uint8_t* dc) {
+  if (!a || !wq || !scales || !out) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "operand pointer is NULL");
+  auto* d = context->device;
+  if (!d->readback_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->readback_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->readback_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  if (!d->upload_stream) {
+    CU_RETURN_IF_ERROR(g_cu.cuStreamCreate(&d->upload_stream, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    CU_RETURN_IF_ERROR(g_cu.cuEventCreate(&d->upload_ready, CU_EVENT_DISABLE_TIMING), "cuEventCreate");
+  }
+  const int64_t N = params->N, K = params->K;
+  const size_t w_pitch = static_cast<size_t>(K / 2), s_pitch = static_cast<size_t>(K / 128) * 2, a_pitch = static_cast<size_t>(K) * 2;
+  HostUnit units[kHostMaxUnits];
+  const int count = w4_plan_units(params, units);
   // every unit's header (operand and result maps) is encoded first and uploaded in one copy
   std::vector<uint8_t> headers(static_cast<size_t>(count) * kHostUnitWorkspace, 0);
   iree_b200_w4a16_params_t up[kHostMaxUnits];
@@ -2893,7 +2903,7 @@ static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree
     return IREE_B200_STATUS_OK;
   };
   for (int u = 0; u < count; ++u) {
-    const Unit& t = units[u];
+    const HostUnit& t = units[u];
     if (t.new_cols) {  // a block of weight rows with its scales
       B200_RETURN_IF_ERROR(upload(wq + static_cast<size_t>(t.col0) * w_pitch, dw + static_cast<size_t>(t.col0) * w_pitch,
                                   static_cast<size_t>(t.cols) * w_pitch));
@@ -2944,6 +2954,22 @@ static iree_b200_status_t w4_host_units(iree_b200_context_t* context, const iree
   return IREE_B200_STATUS_OK;
 }
 
+int32_t iree_b200_w4a16_host_plan(const iree_b200_w4a16_params_t* params, int32_t* out_units, int32_t capacity) {
+  if (!params || w4_validate(params) != IREE_B200_STATUS_OK) return -1;
+  const size_t w_bytes = static_cast<size_t>(params->N) * (params->K / 2);
+  const size_t c_bytes = static_cast<size_t>(params->M) * params->ldo * 2;
+  if (!params->M || !params->N || !w4_host_in_units(params, w_bytes, c_bytes)) return 0;
+  HostUnit units[kHostMaxUnits];
+  const int count = w4_plan_units(params, units);
+  for (int u = 0; u < count && u < capacity && out_units; ++u) {
+    int32_t* o = out_units + 6 * u;
+    o[0] = static_cast<int32_t>(units[u].row0), o[1] = static_cast<int32_t>(units[u].rows);
+    o[2] = static_cast<int32_t>(units[u].col0), o[3] = static_cast<int32_t>(units[u].cols);
+    o[4] = units[u].new_rows, o[5] = units[u].new_cols;
+  }
+  return count;
+}
+
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out) {
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
@@ -2955,7 +2981,7 @@ iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree
   if (!params->M || !params->N) return IREE_B200_STATUS_OK;
   auto* d = context->device;
   auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
-  const bool in_units = w4_host_in_units(params, w_bytes, c_bytes);
+  const bool in_units = g_cu.cuMemcpy2DAsync && w4_host_in_units(params, w_bytes, c_bytes);
   const size_t ws_bytes = in_units ? kHostMaxUnits * kHostUnitWorkspace : iree_b200_w4a16_workspace_bytes(params->N);
   const size_t need = up(ws_bytes) + up(a_bytes) + up(w_bytes) + up(s_bytes) + up(c_bytes);
   if (need > context->arena_size) {

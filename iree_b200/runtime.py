@@ -345,6 +345,16 @@ class Context:
         check(library().iree_b200_w4a16_host(self.handle, C.byref(params), _vp(a), _vp(wq), _vp(scales), _vp(out)))
 
     @staticmethod
+    def w4a16_host_plan(params: W4A16Params):
+        """The dispatches ``w4a16_host`` cuts a product into: a list of (row0, rows, col0, cols, uploads_rows,
+        uploads_cols); empty when it runs as one dispatch. Needs no device."""
+        units = (C.c_int32 * (6 * 32))()
+        n = library().iree_b200_w4a16_host_plan(C.byref(params), units, C.c_int32(32))
+        if n < 0:
+            raise ValueError("invalid W4A16 parameters")
+        return [tuple(units[6 * u:6 * u + 6]) for u in range(n)]
+
+    @staticmethod
     def _ptr_array(items):
         arr = (C.c_void_p * len(items))()
         for i, x in enumerate(items):

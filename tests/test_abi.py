@@ -124,6 +124,47 @@ def test_command_buffer_argument_checks(built):
     assert lib.iree_b200_matmul(None, None, None, None, None, None, None, None) == 3
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 28672, 8192), (2048, 11008, 4096), (1100, 4400, 12288), (256, 2048, 32768),
+                                   (5000, 40000, 4096)])
+def test_host_call_plan_covers_the_result_once_and_uploads_before_use(built, M, N, K):
+    """The units of the host-buffer W4A16 call (planned without a device): their rectangles tile the
+    [M, N] result exactly once, every rectangle only needs rows and columns whose upload precedes it, every
+    operand block goes up exactly once, and block edges keep the kernel's alignment (256 rows / columns)."""
+    p = runtime.W4A16Params(M, N, K, 128, N, 0, runtime.W4A16_AUTO, 0)
+    units = runtime.Context.w4a16_host_plan(p)
+    assert 2 <= len(units) <= 24
+    covered = np.zeros((M, N), np.uint8)
+    rows_up = np.zeros(M, bool)
+    cols_up = np.zeros(N, bool)
+    for (r0, rows, c0, cols, new_rows, new_cols) in units:
+        assert rows > 0 and cols > 0 and r0 % 256 == 0 and c0 % 256 == 0
+        if new_rows:
+            assert not rows_up[r0:r0 + rows].any()
+            rows_up[r0:r0 + rows] = True
+        if new_cols:
+            assert not cols_up[c0:c0 + cols].any()
+            cols_up[c0:c0 + cols] = True
+        assert new_rows or new_cols
+        assert rows_up[r0:r0 + rows].all() and cols_up[c0:c0 + cols].all()
+        covered[r0:r0 + rows, c0:c0 + cols] += 1
+    assert (covered == 1).all() and rows_up.all() and cols_up.all()
+    # the first result leaves after a part of the operands has arrived (a fifth at most on the large shapes)
+    first = units[0]
+    if M >= 2048:
+        assert first[1] * K * 2 + first[3] * (K // 2 + K // 64) <= 0.2 * (M * K * 2 + N * (K // 2 + K // 64))
+
+
+def test_host_call_plan_leaves_small_and_unsuitable_products_alone(built):
+    plan = runtime.Context.w4a16_host_plan
+    assert plan(runtime.W4A16Params(16, 28672, 8192, 128, 28672, 0, runtime.W4A16_AUTO, 0)) == []      # few rows
+    assert plan(runtime.W4A16Params(512, 2048, 1024, 128, 2048, 0, runtime.W4A16_AUTO, 0)) == []        # small
+    assert plan(runtime.W4A16Params(4096, 28676, 8192, 128, 28676, 0, runtime.W4A16_AUTO, 0)) == []     # N % 8
+    assert plan(runtime.W4A16Params(4096, 28672, 8192, 128, 28672, 0, runtime.W4A16_GEMM, 0)) == []     # explicit variant
+    assert plan(runtime.W4A16Params(4096, 14336, 8192, 128, 28672, 14336, runtime.W4A16_AUTO, 0)) == [] # a column slice
+    with pytest.raises(ValueError):
+        plan(runtime.W4A16Params(4096, 28672, 100, 128, 28672, 0, runtime.W4A16_AUTO, 0))
+
+
 def _has_gpu():
     try:
         c = iree_b200.Context(0)

@@ -60,7 +60,9 @@ from bench_workloads import (DEFAULT_WORKLOAD, algorithmic, describe, local_n, m
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
     """Samples SM clocks and throttle reasons while the timed region runs: through NVML in this process
-    (a thread polling every 2 ms, plus one sample taken by the timing code itself right after the launch),
+    (one sample taken by the timing code itself right after the last launch, while the steps run, plus - with
+    one rank, where the steps are one graph launch - a thread polling every 25 ms; several ranks launch step
+    by step and NVML queries take driver locks that launches need too, so they are not polled),
     or, where NVML cannot be loaded, with an nvidia-smi child at 50 ms. Read-only queries."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -68,9 +70,10 @@ class ClockSampler:
     # bits of nvmlDeviceGetCurrentClocksEventReasons, in the order of the four names of summary()
     REASON_BITS = (0x8, 0x40, 0x20, 0x4)
 
-    def __init__(self, index):
-        self.index, self.lines, self.proc, self.nvml, self.handle = index, [], None, None, None
+    def __init__(self, index, poll=True):
+        self.index, self.lines, self.proc, self.nvml, self.handle, self.poll = index, [], None, None, None, poll
         self.stop = threading.Event()
+        self.period = float(os.environ.get("IREE_B200_CLOCK_POLL_MS", "25")) / 1e3
 
     def _nvml_line(self):
         n, h = self.nvml, self.handle
@@ -96,8 +99,10 @@ class ClockSampler:
             self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
             self.nvml = pynvml
             self._nvml_line()
-            self.thread = threading.Thread(target=self._poll, daemon=True)
-            self.thread.start()
+            self.thread = None
+            if self.poll:
+                self.thread = threading.Thread(target=self._poll, daemon=True)
+                self.thread.start()
             return self
         except Exception:
             self.nvml = None
@@ -117,7 +122,7 @@ class ClockSampler:
                 self.lines.append((time.time(), self._nvml_line()))
             except Exception:
                 return
-            self.stop.wait(0.002)
+            self.stop.wait(self.period)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -125,7 +130,7 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         self.stop.set()
-        if self.nvml is not None:
+        if self.nvml is not None and self.thread is not None:
             self.thread.join(timeout=1)
         if self.proc:
             self.proc.terminate()
@@ -386,7 +391,7 @@ def measure(ctx, wl, rank, world, local, channel, steps, warmup, verify, peaks, 
         ctx.synchronize()
     dist_barrier(world)
     launches0 = ctx.launch_count
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local, poll=world == 1) as clocks:
         time.sleep(0.06)
         t_begin = time.time()
         e0 = ctx.event().record()

@@ -554,7 +554,7 @@ iree_b200_status_t iree_b200_w4a16_wait_arrivals(iree_b200_context_t* context, c
 /* Host-buffer form (copies in, runs, copies out, waits). With ldo != N the existing contents of
  * `out` are uploaded first so that columns outside the slice survive. A many-rows product of tens of
  * megabytes (variant AUTO, M >= 256, N >= 2048 and a multiple of 8, group 128, ldo == N, weights +
- * result >= 32 MB) is run as up to 24 dispatches that follow the operands' arrival, with uploads,
+ * result >= 32 MB) is run as up to 11 dispatches that follow the operands' arrival, with uploads,
  * kernels and pitched readbacks on three streams; the result is bit-identical to the single
  * dispatch's. Page-locked host buffers (iree_hal_b200_host_allocate) make the copies asynchronous. */
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,

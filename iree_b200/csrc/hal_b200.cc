@@ -2337,6 +2337,9 @@ iree_b200_status_t iree_b200_matmul_host(iree_b200_context_t* context, const ire
                                          const void* lhs, const void* rhs, void* out, const float* row_scale,
                                          const float* col_scale) {
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  // The host-buffer calls copy on the streams themselves and wait: they cannot become nodes of a graph.
+  if (context->command_buffer->recording)
+    return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "a host-buffer call cannot be recorded into a graph");
   B200_RETURN_IF_ERROR(validate(params));
   const size_t es = elem_bytes_of(params->kind);
   const size_t os = params->epilogue == IREE_B200_EPILOGUE_ACCUMULATOR ? 4 : 2;
@@ -2975,6 +2978,8 @@ int32_t iree_b200_w4a16_host_plan(const iree_b200_w4a16_params_t* params, int32_
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out) {
   if (!context) return fail(IREE_B200_STATUS_INVALID_ARGUMENT, "context is NULL");
+  if (context->command_buffer->recording)
+    return fail(IREE_B200_STATUS_FAILED_PRECONDITION, "a host-buffer call cannot be recorded into a graph");
   B200_RETURN_IF_ERROR(w4_validate(params));
   const size_t a_bytes = static_cast<size_t>(params->M) * params->K * 2;
   const size_t w_bytes = static_cast<size_t>(params->N) * (params->K / 2);

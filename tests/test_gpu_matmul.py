@@ -297,6 +297,9 @@ def test_graph_mode_replays_recorded_dispatches(ctx):
     before = ctx.launch_count
     ctx.begin_graph()
     ctx.matmul_run(p, da, db, c1, ws, bn)
+    with pytest.raises(ib.IreeB200Error) as e:                # a host-buffer call copies and waits: not recordable
+        ctx.matmul_host(p, a, b, np.empty((M, N), np.float16))
+    assert e.value.code_name == "FAILED_PRECONDITION"
     ctx.matmul_run(p, da, db, c2, ws, bn)
     graph = ctx.end_graph()
     ctx.synchronize()

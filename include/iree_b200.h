@@ -556,7 +556,8 @@ iree_b200_status_t iree_b200_w4a16_wait_arrivals(iree_b200_context_t* context, c
  * megabytes (variant AUTO, M >= 256, N >= 2048 and a multiple of 8, group 128, ldo == N, weights +
  * result >= 32 MB) is run as up to 11 dispatches that follow the operands' arrival, with uploads,
  * kernels and pitched readbacks on three streams; the result is bit-identical to the single
- * dispatch's. Page-locked host buffers (iree_hal_b200_host_allocate) make the copies asynchronous. */
+ * dispatch's. Page-locked host buffers (iree_hal_b200_host_allocate) make the copies asynchronous. The
+ * host-buffer calls copy and wait themselves: FAILED_PRECONDITION while a graph is being recorded. */
 iree_b200_status_t iree_b200_w4a16_host(iree_b200_context_t* context, const iree_b200_w4a16_params_t* params,
                                         const void* a, const void* wq, const void* scales, void* out);
 /* The dispatches iree_b200_w4a16_host cuts `params` into (needs no device): writes up to `capacity` records
